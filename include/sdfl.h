@@ -1,0 +1,197 @@
+/* sdfl -- Stable-Diffusion fused layer kernels for NVIDIA B200 (sm_100a): C ABI.
+ *
+ * Drop-in boundary for the fused-layer path of the reference app (its OpenCL C kernels and the
+ * C++ operator classes that enqueue them).  Each entry point names the reference interface it
+ * replaces; paths are inside the reference project:
+ *   K/  = app/src/main/assets/kernel/        NN/ = app/src/main/cpp/modules/nn/
+ *   M/  = app/src/main/cpp/modules/
+ *
+ * Conventions
+ *   - All tensor pointers are CUDA device pointers owned by the caller unless a name starts with
+ *     h_.  `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream).  Calls
+ *     only enqueue work; ordering is the stream's (the reference returned cl_events instead).
+ *   - dtype: SDFL_F32 or SDFL_F16 storage; arithmetic is always fp32; weights (gamma, beta) are
+ *     always fp32, as in the reference.
+ *   - Return value: 0 on success, a negative SDFL_ERR_* otherwise.  Nothing throws, nothing
+ *     aborts.  The reference returned cl_int (0 = CL_SUCCESS) and threw std::runtime_error on
+ *     contract violations (NN/GroupNorm.cpp:83-93); those cases are SDFL_ERR_INVALID_VALUE here.
+ *   - out == in is allowed wherever the reference allows it (GroupNorm, LayerNorm, activations:
+ *     NN/ResBlock.cpp:222, NN/ResBlock.cpp:136-137); partial overlap is SDFL_ERR_OVERLAP.
+ *   - The library keeps no mutable host state per call and may be driven from several host
+ *     threads, one CUDA device each.
+ */
+#ifndef SDFL_H_
+#define SDFL_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum { SDFL_F32 = 0, SDFL_F16 = 1 };
+
+enum {
+    SDFL_OK = 0,
+    SDFL_ERR_INVALID_VALUE = -1,   /* bad size / shape / enum */
+    SDFL_ERR_INVALID_POINTER = -2, /* NULL where a buffer is required */
+    SDFL_ERR_UNSUPPORTED = -3,     /* shape outside what any kernel path handles */
+    SDFL_ERR_CUDA = -4,            /* a CUDA call failed; see sdfl_last_cuda_error() */
+    SDFL_ERR_OVERLAP = -5,         /* input and output partially overlap */
+    SDFL_ERR_WORKSPACE = -6,       /* scratch buffer missing or too small */
+    SDFL_ERR_DEVICE_FLAG = -7      /* a kernel raised its device-side status word */
+};
+
+/* GroupNorm path selection for sdfl_groupnorm_forward_ex (tests and sweeps). */
+enum { SDFL_GN_AUTO = 0, SDFL_GN_RESIDENT = 1, SDFL_GN_SPLIT = 2 };
+
+const char *sdfl_version(void);
+const char *sdfl_status_string(int status);
+/* cudaError_t of the most recent failing CUDA call on this host thread, and its text. */
+int sdfl_last_cuda_error(void);
+const char *sdfl_last_cuda_error_string(void);
+/* Number of kernels this library has enqueued since load (all threads). */
+long long sdfl_launch_count(void);
+
+/* ------------------------------------------------------------------------------------------
+ * Fused operators (one launch where the reference needs three or four)
+ * ---------------------------------------------------------------------------------------- */
+
+/* GroupNorm with optional fused SiLU on an NCHW tensor [batch, channels, hw].
+ * Replaces GroupNorm::forward (NN/GroupNorm.cpp:68-170: local_reduction_mean +
+ * local_reduction_variance + group_norm, K/group_norm.cl:1-76) and, with fuse_silu != 0, the
+ * silu launch that follows it at every call site (K/util.cl:124-134; NN/ResBlock.cpp:125-142,
+ * M/UNetModel.cpp:1797-1809, M/Decoder.cpp:523-536).
+ * Same group semantics (group g of an image = channels [g*C/G, (g+1)*C/G), biased variance,
+ * eps inside the square root).  Added: the batch dimension (the reference is batch-1 and would
+ * index gamma out of range on a batched buffer, K/group_norm.cl:71).
+ * The reference demands group size % 64 == 0 (NN/GroupNorm.cpp:89-93); this does not.
+ * workspace: scratch of at least sdfl_groupnorm_workspace_bytes() bytes (may be NULL when that
+ * is 0, i.e. when the shared-memory-resident path applies). */
+int sdfl_groupnorm_forward(const void *in, void *out, const float *gamma, const float *beta,
+                           int64_t batch, int64_t channels, int64_t hw, int64_t num_groups,
+                           float eps, int fuse_silu, int dtype, void *workspace,
+                           size_t workspace_bytes, void *stream);
+
+size_t sdfl_groupnorm_workspace_bytes(int64_t batch, int64_t channels, int64_t hw,
+                                      int64_t num_groups, int dtype);
+
+/* Same, with the device path and cluster size (resident) / chunk count (split) forced;
+ * 0 = automatic.  A forced path that cannot run the shape returns SDFL_ERR_UNSUPPORTED.
+ * The workspace must then hold sdfl_groupnorm_workspace_bytes_ex() bytes. */
+int sdfl_groupnorm_forward_ex(const void *in, void *out, const float *gamma, const float *beta,
+                              int64_t batch, int64_t channels, int64_t hw, int64_t num_groups,
+                              float eps, int fuse_silu, int dtype, void *workspace,
+                              size_t workspace_bytes, int path, int cluster_or_splits, void *stream);
+
+size_t sdfl_groupnorm_workspace_bytes_ex(int64_t batch, int64_t channels, int64_t hw,
+                                         int64_t num_groups, int dtype, int path,
+                                         int cluster_or_splits);
+
+/* Which path sdfl_groupnorm_forward would take for 16-byte aligned buffers:
+ * plan[0] = path, [1] = cluster size, [2] = threads per CTA, [3] = chunks per slab (split),
+ * [4] = dynamic shared memory bytes per CTA, [5] = workspace bytes. */
+int sdfl_groupnorm_plan(int64_t batch, int64_t channels, int64_t hw, int64_t num_groups, int dtype,
+                        int path, int cluster_or_splits, int64_t plan[6]);
+
+/* LayerNorm over the last dimension of [rows, dim].
+ * Replaces LayerNorm::forward (NN/LayerNorm.cpp:66-162; K/layer_norm.cl:1-78).  eps is an
+ * argument; the reference fixes it at 1e-5 (K/layer_norm.cl:58).  The reference demands
+ * dim % 64 == 0 (NN/LayerNorm.cpp:61-63); this does not. */
+int sdfl_layernorm_forward(const void *in, void *out, const float *gamma, const float *beta,
+                           int64_t rows, int64_t dim, float eps, int dtype, void *stream);
+
+/* Token + position embedding: out[b,t,:] = table[ids[b,t],:] + pos[t,:].
+ * Replaces TextEncoder::createTokenEmbeddingBuffer (M/TextEncoder.cpp:105-125, a host loop
+ * over a host-resident table) followed by elemwise_add with the positional table
+ * (M/TextEncoder.cpp:141-151).  ids are int64 like the reference's std::vector<long>.
+ * d_status (device int, may be NULL): bit 0 is raised if an id is outside [0, vocab); such rows
+ * are written as zeros (the reference reads out of bounds instead). */
+int sdfl_token_embedding(const int64_t *ids, const void *table, const void *pos, void *out,
+                         int64_t batch, int64_t seq_len, int64_t dim, int64_t vocab, int dtype,
+                         int *d_status, void *stream);
+
+/* Sinusoidal timestep embedding: out[n, :] = [cos(t[n] * f_i) | sin(t[n] * f_i)],
+ * f_i = exp(-log(max_period) * i / (dim/2)).
+ * Replaces UNetModel::createTimestepEmbedding (M/UNetModel.cpp:1935-1958; host code, one
+ * timestep); here t is a device array of `batch` int64 timesteps. */
+int sdfl_timestep_embedding(const int64_t *t, void *out, int64_t batch, int64_t dim,
+                            float max_period, int dtype, void *stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Per-kernel entry points: one per reference __kernel, same pointer order; NDRange extents
+ * become trailing integer arguments and the __local scratch argument is dropped.
+ * ---------------------------------------------------------------------------------------- */
+
+/* K/group_norm.cl:1-27 and K/layer_norm.cl:1-27  local_reduction_mean(input, output, scratch,
+ * reductionSize) over `groups` work-groups: output[g] = mean of input[g*n, (g+1)*n) with
+ * n = group_elems (= 64 * reductionSize in the reference). */
+int sdfl_local_reduction_mean(const void *input, float *output, int64_t groups, int64_t group_elems,
+                              int dtype, void *stream);
+
+/* K/group_norm.cl:29-57  local_reduction_variance(input, mean, output, scratch, reductionSize):
+ * biased variance around the given mean. */
+int sdfl_local_reduction_variance(const void *input, const float *mean, float *output,
+                                  int64_t groups, int64_t group_elems, int dtype, void *stream);
+
+/* K/group_norm.cl:59-76  group_norm(input, mean, variance, weight, bias, groupSize,
+ * channelSize, epsilon, output) over n work-items.  weight/bias index = (i / channelSize) %
+ * num_channels, which equals the reference's i / channelSize for a single image. */
+int sdfl_group_norm(const void *input, const float *mean, const float *variance,
+                    const float *weight, const float *bias, int64_t groupSize, int64_t channelSize,
+                    float epsilon, void *output, int64_t n, int64_t num_channels, int dtype,
+                    void *stream);
+
+/* K/layer_norm.cl:63-78  layer_norm(input, mean, variance, weight, bias, chunkSize, output)
+ * over n work-items; epsilon is the kernel file's constant in the reference. */
+int sdfl_layer_norm(const void *input, const float *mean, const float *variance,
+                    const float *weight, const float *bias, int64_t chunkSize, void *output,
+                    int64_t n, float epsilon, int dtype, void *stream);
+
+/* K/geglu.cl:1-25  gelu_multiply(AB, dst) over the 2-D range {rows, D} (NN/GEGLU.cpp:71-77):
+ * dst[r, j] = AB[r, j] * gelu_erf(AB[r, D + j]); AB is [rows, 2D], dst is [rows, D]. */
+int sdfl_gelu_multiply(const void *AB, void *dst, int64_t rows, int64_t D, int dtype, void *stream);
+
+/* K/util.cl:104-122  gelu(src, dst): x * 0.5 * (1 + erf(x / sqrt 2)) over n work-items. */
+int sdfl_gelu(const void *src, void *dst, int64_t n, int dtype, void *stream);
+
+/* K/util.cl:124-134  silu(src, dst): x / (1 + exp(-x)) over n work-items. */
+int sdfl_silu(const void *src, void *dst, int64_t n, int dtype, void *stream);
+
+/* x / (1 + exp(-1.702 x)).  The reference has no quick_gelu kernel; this follows silu's form. */
+int sdfl_quick_gelu(const void *src, void *dst, int64_t n, int dtype, void *stream);
+
+/* K/util.cl:1-12  elemwise_add(A, B, C): C = A + B over n work-items. */
+int sdfl_elemwise_add(const void *A, const void *B, void *C, int64_t n, int dtype, void *stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Device status and host-buffer convenience path
+ * ---------------------------------------------------------------------------------------- */
+
+/* Reads (and, if clear != 0, clears) the sticky status word of the GroupNorm kernels on the
+ * current device.  Bit 0: a bounded wait on a bulk copy ran out -- results of that launch are
+ * not valid.  Synchronises `stream`. */
+int sdfl_device_status(unsigned int *value, int clear, void *stream);
+
+/* Host-buffer GroupNorm(+SiLU): what a caller holding host tensors uses (the reference's
+ * models take and return std::vector<float>, JNI boundary).  A pipeline object owns `depth`
+ * device staging slots and streams, created once; forward_host copies image slabs in,
+ * normalises, and copies out, overlapping the three, and returns when h_out is complete.
+ * Host buffers should be page-locked (sdfl_host_alloc) for the copies to overlap. */
+typedef struct sdfl_host_pipeline sdfl_host_pipeline;
+
+int sdfl_host_pipeline_create(sdfl_host_pipeline **pipe, size_t max_slot_bytes, int depth);
+int sdfl_host_pipeline_destroy(sdfl_host_pipeline *pipe);
+int sdfl_groupnorm_forward_host(sdfl_host_pipeline *pipe, const void *h_in, void *h_out,
+                                const float *gamma, const float *beta, int64_t batch,
+                                int64_t channels, int64_t hw, int64_t num_groups, float eps,
+                                int fuse_silu, int dtype);
+int sdfl_host_alloc(void **h_ptr, size_t bytes);
+int sdfl_host_free(void *h_ptr);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* SDFL_H_ */

@@ -1,0 +1,385 @@
+// The C ABI of include/sdfl.h: argument validation, status codes, and the host-buffer
+// pipeline.  No kernel lives here.
+#include "../../include/sdfl.h"
+
+#include "common.cuh"
+#include "kernels.h"
+
+#include <vector>
+
+namespace sdfl {
+std::atomic<long long> g_launches{0};
+}
+
+namespace {
+
+thread_local cudaError_t tl_last_cuda = cudaSuccess;
+
+inline int cuda_fail(cudaError_t e) {
+    tl_last_cuda = e;
+    (void)cudaGetLastError();   // clear the sticky-free error so the next call starts clean
+    return SDFL_ERR_CUDA;
+}
+
+inline int wrap(cudaError_t e) { return e == cudaSuccess ? SDFL_OK : cuda_fail(e); }
+
+inline bool dtype_ok(int dtype) { return dtype == SDFL_F32 || dtype == SDFL_F16; }
+inline int64_t esize(int dtype) { return dtype == SDFL_F16 ? 2 : 4; }
+inline cudaStream_t as_stream(void *s) { return static_cast<cudaStream_t>(s); }
+
+// 0: disjoint or identical; 1: partial overlap.
+inline bool partial_overlap(const void *a, int64_t abytes, const void *b, int64_t bbytes) {
+    if (a == b) return false;
+    const uintptr_t a0 = reinterpret_cast<uintptr_t>(a), b0 = reinterpret_cast<uintptr_t>(b);
+    return a0 < b0 + static_cast<uintptr_t>(bbytes) && b0 < a0 + static_cast<uintptr_t>(abytes);
+}
+
+// Any overlap at all (for ops whose in and out have different shapes).
+inline bool any_overlap(const void *a, int64_t abytes, const void *b, int64_t bbytes) {
+    const uintptr_t a0 = reinterpret_cast<uintptr_t>(a), b0 = reinterpret_cast<uintptr_t>(b);
+    return a0 < b0 + static_cast<uintptr_t>(bbytes) && b0 < a0 + static_cast<uintptr_t>(abytes);
+}
+
+int gn_validate(const void *in, const void *out, const float *gamma, const float *beta,
+                int64_t batch, int64_t channels, int64_t hw, int64_t groups, float eps, int dtype) {
+    if (!dtype_ok(dtype)) return SDFL_ERR_INVALID_VALUE;
+    if (batch < 0 || channels <= 0 || hw < 0 || groups <= 0) return SDFL_ERR_INVALID_VALUE;
+    if (channels % groups != 0) return SDFL_ERR_INVALID_VALUE;   // NN/GroupNorm.cpp:83-87
+    if (!(eps >= 0.f)) return SDFL_ERR_INVALID_VALUE;
+    if (hw >= (1ll << 31) || channels >= (1ll << 31)) return SDFL_ERR_UNSUPPORTED;
+    if ((channels / groups) * hw >= (1ll << 31)) return SDFL_ERR_UNSUPPORTED;
+    if (batch * groups >= (1ll << 27)) return SDFL_ERR_UNSUPPORTED;
+    if (batch == 0 || hw == 0) return SDFL_OK;
+    if (!in || !out || !gamma || !beta) return SDFL_ERR_INVALID_POINTER;
+    const int64_t bytes = batch * channels * hw * esize(dtype);
+    if (partial_overlap(in, bytes, out, bytes)) return SDFL_ERR_OVERLAP;
+    return SDFL_OK;
+}
+
+int gn_forward(const void *in, void *out, const float *gamma, const float *beta, int64_t batch,
+               int64_t channels, int64_t hw, int64_t groups, float eps, int fuse_silu, int dtype,
+               void *workspace, size_t workspace_bytes, int path, int cluster, cudaStream_t stream) {
+    int rc = gn_validate(in, out, gamma, beta, batch, channels, hw, groups, eps, dtype);
+    if (rc != SDFL_OK) return rc;
+    if (batch == 0 || hw == 0) return SDFL_OK;
+    if (path < SDFL_GN_AUTO || path > SDFL_GN_SPLIT || cluster < 0) return SDFL_ERR_INVALID_VALUE;
+    sdfl::GnShape s{batch, channels, hw, groups, dtype, eps,
+                    fuse_silu ? sdfl::kActSilu : sdfl::kActNone};
+    sdfl::GnPlan plan;
+    cudaError_t e = sdfl::gn_make_plan(s, in, out, path, cluster, &plan);
+    if (e == cudaErrorInvalidConfiguration || e == cudaErrorInvalidValue) return SDFL_ERR_UNSUPPORTED;
+    if (e != cudaSuccess) return cuda_fail(e);
+    if (plan.path == sdfl::kGnSplit && (workspace == nullptr || workspace_bytes < plan.workspace))
+        return SDFL_ERR_WORKSPACE;
+    return wrap(sdfl::gn_launch(s, plan, in, out, gamma, beta, workspace, stream));
+}
+
+int unary(int act, const void *src, void *dst, int64_t n, int dtype, void *stream) {
+    if (!dtype_ok(dtype) || n < 0) return SDFL_ERR_INVALID_VALUE;
+    if (n == 0) return SDFL_OK;
+    if (!src || !dst) return SDFL_ERR_INVALID_POINTER;
+    if (partial_overlap(src, n * esize(dtype), dst, n * esize(dtype))) return SDFL_ERR_OVERLAP;
+    return wrap(sdfl::act_launch(act, src, dst, n, dtype, as_stream(stream)));
+}
+
+}  // namespace
+
+struct sdfl_host_pipeline {
+    struct Slot {
+        void *d_in = nullptr;
+        void *d_out = nullptr;
+        void *d_ws = nullptr;
+        cudaStream_t stream = nullptr;
+    };
+    std::vector<Slot> slots;
+    size_t slot_bytes = 0;
+    size_t ws_bytes = 0;
+    int device = 0;
+};
+
+extern "C" {
+
+const char *sdfl_version(void) { return "sdfl 0.1 (sm_100a)"; }
+
+const char *sdfl_status_string(int status) {
+    switch (status) {
+        case SDFL_OK: return "ok";
+        case SDFL_ERR_INVALID_VALUE: return "invalid value";
+        case SDFL_ERR_INVALID_POINTER: return "invalid (null) pointer";
+        case SDFL_ERR_UNSUPPORTED: return "unsupported shape";
+        case SDFL_ERR_CUDA: return "CUDA error";
+        case SDFL_ERR_OVERLAP: return "input and output partially overlap";
+        case SDFL_ERR_WORKSPACE: return "workspace missing or too small";
+        case SDFL_ERR_DEVICE_FLAG: return "device status word raised";
+        default: return "unknown status";
+    }
+}
+
+int sdfl_last_cuda_error(void) { return static_cast<int>(tl_last_cuda); }
+const char *sdfl_last_cuda_error_string(void) { return cudaGetErrorString(tl_last_cuda); }
+long long sdfl_launch_count(void) { return sdfl::g_launches.load(); }
+
+int sdfl_groupnorm_forward(const void *in, void *out, const float *gamma, const float *beta,
+                           int64_t batch, int64_t channels, int64_t hw, int64_t num_groups,
+                           float eps, int fuse_silu, int dtype, void *workspace,
+                           size_t workspace_bytes, void *stream) {
+    return gn_forward(in, out, gamma, beta, batch, channels, hw, num_groups, eps, fuse_silu, dtype,
+                      workspace, workspace_bytes, SDFL_GN_AUTO, 0, as_stream(stream));
+}
+
+int sdfl_groupnorm_forward_ex(const void *in, void *out, const float *gamma, const float *beta,
+                              int64_t batch, int64_t channels, int64_t hw, int64_t num_groups,
+                              float eps, int fuse_silu, int dtype, void *workspace,
+                              size_t workspace_bytes, int path, int cluster_or_splits, void *stream) {
+    return gn_forward(in, out, gamma, beta, batch, channels, hw, num_groups, eps, fuse_silu, dtype,
+                      workspace, workspace_bytes, path, cluster_or_splits, as_stream(stream));
+}
+
+int sdfl_groupnorm_plan(int64_t batch, int64_t channels, int64_t hw, int64_t num_groups, int dtype,
+                        int path, int cluster_or_splits, int64_t plan[6]) {
+    if (!plan) return SDFL_ERR_INVALID_POINTER;
+    for (int i = 0; i < 6; ++i) plan[i] = 0;
+    if (!dtype_ok(dtype) || batch < 0 || channels <= 0 || hw < 0 || num_groups <= 0 ||
+        channels % num_groups != 0 || path < SDFL_GN_AUTO || path > SDFL_GN_SPLIT ||
+        cluster_or_splits < 0)
+        return SDFL_ERR_INVALID_VALUE;
+    if (hw >= (1ll << 31) || (channels / num_groups) * hw >= (1ll << 31) ||
+        batch * num_groups >= (1ll << 27))
+        return SDFL_ERR_UNSUPPORTED;
+    if (batch == 0 || hw == 0) return SDFL_OK;
+    sdfl::GnShape s{batch, channels, hw, num_groups, dtype, 0.f, sdfl::kActNone};
+    sdfl::GnPlan p;
+    // a 16-byte aligned stand-in address: only its alignment is looked at
+    const void *aligned = reinterpret_cast<const void *>(static_cast<uintptr_t>(256));
+    cudaError_t e = sdfl::gn_make_plan(s, aligned, aligned, path, cluster_or_splits, &p);
+    if (e == cudaErrorInvalidConfiguration || e == cudaErrorInvalidValue) return SDFL_ERR_UNSUPPORTED;
+    if (e != cudaSuccess) return cuda_fail(e);
+    plan[0] = p.path; plan[1] = p.cluster; plan[2] = p.threads; plan[3] = p.splits;
+    plan[4] = static_cast<int64_t>(p.smem); plan[5] = static_cast<int64_t>(p.workspace);
+    return SDFL_OK;
+}
+
+size_t sdfl_groupnorm_workspace_bytes_ex(int64_t batch, int64_t channels, int64_t hw,
+                                         int64_t num_groups, int dtype, int path,
+                                         int cluster_or_splits) {
+    // Sized for the split path whatever the automatic choice would be: the choice depends on
+    // pointer alignment, which is only known at the call.
+    if (!dtype_ok(dtype) || batch <= 0 || channels <= 0 || hw <= 0 || num_groups <= 0 ||
+        channels % num_groups != 0 || (channels / num_groups) * hw >= (1ll << 31))
+        return 0;
+    sdfl::GnShape s{batch, channels, hw, num_groups, dtype, 0.f, sdfl::kActNone};
+    sdfl::GnPlan p;
+    const void *aligned = reinterpret_cast<const void *>(static_cast<uintptr_t>(256));
+    const int splits = path == SDFL_GN_SPLIT ? cluster_or_splits : 0;
+    if (sdfl::gn_make_plan(s, aligned, aligned, SDFL_GN_SPLIT, splits, &p) != cudaSuccess) return 0;
+    return p.workspace;
+}
+
+size_t sdfl_groupnorm_workspace_bytes(int64_t batch, int64_t channels, int64_t hw,
+                                      int64_t num_groups, int dtype) {
+    return sdfl_groupnorm_workspace_bytes_ex(batch, channels, hw, num_groups, dtype, SDFL_GN_AUTO, 0);
+}
+
+int sdfl_layernorm_forward(const void *in, void *out, const float *gamma, const float *beta,
+                           int64_t rows, int64_t dim, float eps, int dtype, void *stream) {
+    if (!dtype_ok(dtype) || rows < 0 || dim <= 0 || !(eps >= 0.f)) return SDFL_ERR_INVALID_VALUE;
+    if (dim >= (1ll << 31)) return SDFL_ERR_UNSUPPORTED;
+    if (rows == 0) return SDFL_OK;
+    if (!in || !out || !gamma || !beta) return SDFL_ERR_INVALID_POINTER;
+    const int64_t bytes = rows * dim * esize(dtype);
+    if (partial_overlap(in, bytes, out, bytes)) return SDFL_ERR_OVERLAP;
+    return wrap(sdfl::ln_launch(in, out, gamma, beta, rows, dim, eps, dtype, as_stream(stream)));
+}
+
+int sdfl_token_embedding(const int64_t *ids, const void *table, const void *pos, void *out,
+                         int64_t batch, int64_t seq_len, int64_t dim, int64_t vocab, int dtype,
+                         int *d_status, void *stream) {
+    if (!dtype_ok(dtype) || batch < 0 || seq_len < 0 || dim < 0 || vocab <= 0)
+        return SDFL_ERR_INVALID_VALUE;
+    if (batch == 0 || seq_len == 0 || dim == 0) return SDFL_OK;
+    if (!ids || !table || !pos || !out) return SDFL_ERR_INVALID_POINTER;
+    return wrap(sdfl::token_embedding_launch(ids, table, pos, out, batch, seq_len, dim, vocab, dtype,
+                                             d_status, as_stream(stream)));
+}
+
+int sdfl_timestep_embedding(const int64_t *t, void *out, int64_t batch, int64_t dim,
+                            float max_period, int dtype, void *stream) {
+    if (!dtype_ok(dtype) || batch < 0 || dim < 0 || !(max_period > 0.f)) return SDFL_ERR_INVALID_VALUE;
+    if (batch * (dim / 2) >= (1ll << 31)) return SDFL_ERR_UNSUPPORTED;
+    if (batch == 0 || dim == 0) return SDFL_OK;
+    if (!t || !out) return SDFL_ERR_INVALID_POINTER;
+    return wrap(sdfl::timestep_embedding_launch(t, out, batch, dim, max_period, dtype, as_stream(stream)));
+}
+
+int sdfl_local_reduction_mean(const void *input, float *output, int64_t groups, int64_t group_elems,
+                              int dtype, void *stream) {
+    if (!dtype_ok(dtype) || groups < 0 || group_elems <= 0) return SDFL_ERR_INVALID_VALUE;
+    if (groups >= (1ll << 31)) return SDFL_ERR_UNSUPPORTED;
+    if (groups == 0) return SDFL_OK;
+    if (!input || !output) return SDFL_ERR_INVALID_POINTER;
+    return wrap(sdfl::stats_mean_launch(input, output, groups, group_elems, dtype, as_stream(stream)));
+}
+
+int sdfl_local_reduction_variance(const void *input, const float *mean, float *output,
+                                  int64_t groups, int64_t group_elems, int dtype, void *stream) {
+    if (!dtype_ok(dtype) || groups < 0 || group_elems <= 0) return SDFL_ERR_INVALID_VALUE;
+    if (groups >= (1ll << 31)) return SDFL_ERR_UNSUPPORTED;
+    if (groups == 0) return SDFL_OK;
+    if (!input || !mean || !output) return SDFL_ERR_INVALID_POINTER;
+    return wrap(sdfl::stats_var_launch(input, mean, output, groups, group_elems, dtype, as_stream(stream)));
+}
+
+int sdfl_group_norm(const void *input, const float *mean, const float *variance,
+                    const float *weight, const float *bias, int64_t groupSize, int64_t channelSize,
+                    float epsilon, void *output, int64_t n, int64_t num_channels, int dtype,
+                    void *stream) {
+    if (!dtype_ok(dtype) || n < 0 || groupSize <= 0 || channelSize <= 0 || num_channels <= 0)
+        return SDFL_ERR_INVALID_VALUE;
+    if (n == 0) return SDFL_OK;
+    if (!input || !mean || !variance || !weight || !bias || !output) return SDFL_ERR_INVALID_POINTER;
+    if (partial_overlap(input, n * esize(dtype), output, n * esize(dtype))) return SDFL_ERR_OVERLAP;
+    return wrap(sdfl::gn_apply_launch(input, mean, variance, weight, bias, groupSize, channelSize,
+                                      epsilon, output, n, num_channels, dtype, as_stream(stream)));
+}
+
+int sdfl_layer_norm(const void *input, const float *mean, const float *variance,
+                    const float *weight, const float *bias, int64_t chunkSize, void *output,
+                    int64_t n, float epsilon, int dtype, void *stream) {
+    if (!dtype_ok(dtype) || n < 0 || chunkSize <= 0) return SDFL_ERR_INVALID_VALUE;
+    if (n == 0) return SDFL_OK;
+    if (!input || !mean || !variance || !weight || !bias || !output) return SDFL_ERR_INVALID_POINTER;
+    if (partial_overlap(input, n * esize(dtype), output, n * esize(dtype))) return SDFL_ERR_OVERLAP;
+    return wrap(sdfl::ln_apply_launch(input, mean, variance, weight, bias, chunkSize, epsilon, output,
+                                      n, dtype, as_stream(stream)));
+}
+
+int sdfl_gelu_multiply(const void *AB, void *dst, int64_t rows, int64_t D, int dtype, void *stream) {
+    if (!dtype_ok(dtype) || rows < 0 || D < 0) return SDFL_ERR_INVALID_VALUE;
+    if (rows == 0 || D == 0) return SDFL_OK;
+    if (!AB || !dst) return SDFL_ERR_INVALID_POINTER;
+    if (any_overlap(AB, rows * 2 * D * esize(dtype), dst, rows * D * esize(dtype)))
+        return SDFL_ERR_OVERLAP;
+    return wrap(sdfl::geglu_launch(AB, dst, rows, D, dtype, as_stream(stream)));
+}
+
+int sdfl_gelu(const void *src, void *dst, int64_t n, int dtype, void *stream) {
+    return unary(sdfl::kActGelu, src, dst, n, dtype, stream);
+}
+int sdfl_silu(const void *src, void *dst, int64_t n, int dtype, void *stream) {
+    return unary(sdfl::kActSilu, src, dst, n, dtype, stream);
+}
+int sdfl_quick_gelu(const void *src, void *dst, int64_t n, int dtype, void *stream) {
+    return unary(sdfl::kActQuickGelu, src, dst, n, dtype, stream);
+}
+
+int sdfl_elemwise_add(const void *A, const void *B, void *C, int64_t n, int dtype, void *stream) {
+    if (!dtype_ok(dtype) || n < 0) return SDFL_ERR_INVALID_VALUE;
+    if (n == 0) return SDFL_OK;
+    if (!A || !B || !C) return SDFL_ERR_INVALID_POINTER;
+    const int64_t bytes = n * esize(dtype);
+    if (partial_overlap(A, bytes, C, bytes) || partial_overlap(B, bytes, C, bytes))
+        return SDFL_ERR_OVERLAP;
+    return wrap(sdfl::add_launch(A, B, C, n, dtype, as_stream(stream)));
+}
+
+int sdfl_device_status(unsigned int *value, int clear, void *stream) {
+    if (!value) return SDFL_ERR_INVALID_POINTER;
+    return wrap(sdfl::gn_read_status(value, clear != 0, as_stream(stream)));
+}
+
+// ---- host-buffer pipeline ---------------------------------------------------------------------
+
+int sdfl_host_pipeline_create(sdfl_host_pipeline **pipe, size_t max_slot_bytes, int depth) {
+    if (!pipe) return SDFL_ERR_INVALID_POINTER;
+    *pipe = nullptr;
+    if (max_slot_bytes == 0 || depth < 1 || depth > 16) return SDFL_ERR_INVALID_VALUE;
+    auto *p = new (std::nothrow) sdfl_host_pipeline;
+    if (!p) return SDFL_ERR_INVALID_VALUE;
+    cudaError_t e = cudaGetDevice(&p->device);
+    p->slot_bytes = (max_slot_bytes + 255) / 256 * 256;
+    p->ws_bytes = 1 << 20;
+    p->slots.resize(static_cast<size_t>(depth));
+    for (auto &s : p->slots) {
+        if (e == cudaSuccess) e = cudaMalloc(&s.d_in, p->slot_bytes);
+        if (e == cudaSuccess) e = cudaMalloc(&s.d_out, p->slot_bytes);
+        if (e == cudaSuccess) e = cudaMalloc(&s.d_ws, p->ws_bytes);
+        if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking);
+    }
+    if (e != cudaSuccess) {
+        sdfl_host_pipeline_destroy(p);
+        return cuda_fail(e);
+    }
+    *pipe = p;
+    return SDFL_OK;
+}
+
+int sdfl_host_pipeline_destroy(sdfl_host_pipeline *pipe) {
+    if (!pipe) return SDFL_OK;
+    for (auto &s : pipe->slots) {
+        if (s.stream) { cudaStreamSynchronize(s.stream); cudaStreamDestroy(s.stream); }
+        if (s.d_in) cudaFree(s.d_in);
+        if (s.d_out) cudaFree(s.d_out);
+        if (s.d_ws) cudaFree(s.d_ws);
+    }
+    delete pipe;
+    return SDFL_OK;
+}
+
+int sdfl_groupnorm_forward_host(sdfl_host_pipeline *pipe, const void *h_in, void *h_out,
+                                const float *gamma, const float *beta, int64_t batch,
+                                int64_t channels, int64_t hw, int64_t num_groups, float eps,
+                                int fuse_silu, int dtype) {
+    if (!pipe) return SDFL_ERR_INVALID_POINTER;
+    int rc = gn_validate(h_in, h_out, gamma, beta, batch, channels, hw, num_groups, eps, dtype);
+    if (rc != SDFL_OK) return rc;
+    if (batch == 0 || hw == 0) return SDFL_OK;
+    // One pipeline step = a run of whole groups of one image, as many as fit a slot (and at
+    // most ~32 MiB so that copy-in, kernel and copy-out of different steps overlap).
+    const int64_t cpg = channels / num_groups;
+    const int64_t group_bytes = cpg * hw * esize(dtype);
+    int64_t limit = static_cast<int64_t>(pipe->slot_bytes);
+    if (limit > (32ll << 20)) limit = 32ll << 20;
+    int64_t gps = limit / group_bytes;            // groups per step
+    if (gps < 1) {
+        if (group_bytes > static_cast<int64_t>(pipe->slot_bytes)) return SDFL_ERR_WORKSPACE;
+        gps = 1;
+    }
+    if (gps > num_groups) gps = num_groups;
+    const char *src = static_cast<const char *>(h_in);
+    char *dst = static_cast<char *>(h_out);
+    size_t step = 0;
+    cudaError_t e = cudaSuccess;
+    for (int64_t n = 0; n < batch && rc == SDFL_OK && e == cudaSuccess; ++n) {
+        for (int64_t g0 = 0; g0 < num_groups; g0 += gps, ++step) {
+            const int64_t ng = g0 + gps <= num_groups ? gps : num_groups - g0;
+            auto &s = pipe->slots[step % pipe->slots.size()];
+            const size_t off = static_cast<size_t>((n * num_groups + g0) * group_bytes);
+            const size_t bytes = static_cast<size_t>(ng * group_bytes);
+            e = cudaMemcpyAsync(s.d_in, src + off, bytes, cudaMemcpyHostToDevice, s.stream);
+            if (e != cudaSuccess) break;
+            rc = gn_forward(s.d_in, s.d_out, gamma + g0 * cpg, beta + g0 * cpg, 1, ng * cpg, hw, ng,
+                            eps, fuse_silu, dtype, s.d_ws, pipe->ws_bytes, SDFL_GN_AUTO, 0, s.stream);
+            if (rc != SDFL_OK) break;
+            e = cudaMemcpyAsync(dst + off, s.d_out, bytes, cudaMemcpyDeviceToHost, s.stream);
+            if (e != cudaSuccess) break;
+        }
+    }
+    for (auto &s : pipe->slots) {
+        cudaError_t se = cudaStreamSynchronize(s.stream);
+        if (e == cudaSuccess) e = se;
+    }
+    if (rc != SDFL_OK) return rc;
+    return wrap(e);
+}
+
+int sdfl_host_alloc(void **h_ptr, size_t bytes) {
+    if (!h_ptr) return SDFL_ERR_INVALID_POINTER;
+    return wrap(cudaHostAlloc(h_ptr, bytes, cudaHostAllocDefault));
+}
+
+int sdfl_host_free(void *h_ptr) {
+    if (!h_ptr) return SDFL_OK;
+    return wrap(cudaFreeHost(h_ptr));
+}
+
+}  // extern "C"

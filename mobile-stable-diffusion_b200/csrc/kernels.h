@@ -1,0 +1,83 @@
+// Host-side launchers of the CUDA kernels; the C ABI (capi.cu) validates arguments and calls
+// these.  Every launcher returns the cudaError_t of its launch and adds the number of kernels
+// it enqueued to g_launches.
+#pragma once
+
+#include <atomic>
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace sdfl {
+
+extern std::atomic<long long> g_launches;
+
+// ---- GroupNorm (+SiLU) ------------------------------------------------------------------------
+// Two device paths:
+//   kGnResident  one thread-block cluster per (image, group) slab; the slab is staged in the
+//                cluster's shared memory by bulk-copy engine transfers, so statistics, affine
+//                and activation cost one HBM read and one HBM write.
+//   kGnSplit     two kernels with a caller-provided scratch of per-chunk (mean, M2) partials;
+//                any size, any alignment; one extra read of the tensor (mostly L2 for mid sizes).
+enum GnPath : int { kGnAuto = 0, kGnResident = 1, kGnSplit = 2 };
+
+struct GnPlan {
+    int path;          // kGnResident or kGnSplit
+    int cluster;       // CTAs per slab (resident) -- 1,2,4,8,16
+    int threads;       // threads per CTA
+    int splits;        // chunks per slab (split path)
+    size_t smem;       // dynamic shared memory per CTA (resident)
+    size_t workspace;  // scratch bytes the split path needs
+};
+
+struct GnShape {
+    int64_t batch, channels, hw, groups;
+    int dtype;         // kF32 / kF16
+    float eps;
+    int act;           // kActNone / kActSilu
+};
+
+// Decide the path.  `force_path` / `force_cluster` (0 = automatic) are for tests and sweeps.
+// in/out alignment matters for the resident path (16-byte bulk copies).
+cudaError_t gn_make_plan(const GnShape &s, const void *in, const void *out, int force_path,
+                         int force_cluster, GnPlan *plan);
+
+cudaError_t gn_launch(const GnShape &s, const GnPlan &plan, const void *in, void *out,
+                      const float *w, const float *b, void *workspace, cudaStream_t stream);
+
+// Sticky device-side status word of the GroupNorm kernels (bit 0: a bounded wait on a bulk
+// copy ran out).  Reads it, optionally clears it.
+cudaError_t gn_read_status(unsigned int *value, bool clear, cudaStream_t stream);
+
+// Stand-alone statistics / apply kernels that keep the reference's three-launch call sequence.
+cudaError_t stats_mean_launch(const void *in, float *out, int64_t groups, int64_t n, int dtype,
+                              cudaStream_t stream);
+cudaError_t stats_var_launch(const void *in, const float *mean, float *out, int64_t groups,
+                             int64_t n, int dtype, cudaStream_t stream);
+cudaError_t gn_apply_launch(const void *in, const float *mean, const float *var, const float *w,
+                            const float *b, int64_t group_size, int64_t channel_size, float eps,
+                            void *out, int64_t n, int64_t channels, int dtype, cudaStream_t stream);
+cudaError_t ln_apply_launch(const void *in, const float *mean, const float *var, const float *w,
+                            const float *b, int64_t dim, float eps, void *out, int64_t n, int dtype,
+                            cudaStream_t stream);
+
+// ---- LayerNorm --------------------------------------------------------------------------------
+cudaError_t ln_launch(const void *in, void *out, const float *w, const float *b, int64_t rows,
+                      int64_t dim, float eps, int dtype, cudaStream_t stream);
+
+// ---- Elementwise ------------------------------------------------------------------------------
+cudaError_t geglu_launch(const void *ab, void *dst, int64_t rows, int64_t d, int dtype,
+                         cudaStream_t stream);
+cudaError_t act_launch(int act, const void *src, void *dst, int64_t n, int dtype,
+                       cudaStream_t stream);
+cudaError_t add_launch(const void *a, const void *b, void *c, int64_t n, int dtype,
+                       cudaStream_t stream);
+
+// ---- Embeddings -------------------------------------------------------------------------------
+cudaError_t token_embedding_launch(const int64_t *ids, const void *table, const void *pos,
+                                   void *out, int64_t batch, int64_t t, int64_t d, int64_t vocab,
+                                   int dtype, int *d_status, cudaStream_t stream);
+cudaError_t timestep_embedding_launch(const int64_t *t, void *out, int64_t batch, int64_t dim,
+                                      float max_period, int dtype, cudaStream_t stream);
+
+}  // namespace sdfl

@@ -1,0 +1,281 @@
+"""Functional wrappers over the C ABI for torch CUDA tensors.
+
+torch is used for device memory and streams only; every operation below is one call into
+libsdfl.so.  Inputs must be contiguous CUDA tensors of dtype float32 or float16; gamma / beta
+are float32.  Nothing here computes on the host and nothing falls back to torch operators.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _capi
+from ._capi import F16, F32, GN_AUTO, GN_RESIDENT, GN_SPLIT, SdflError, check, lib
+
+__all__ = [
+    "groupnorm", "groupnorm_plan", "layernorm", "gelu_multiply", "silu", "gelu", "quick_gelu",
+    "elemwise_add", "token_embedding", "timestep_embedding", "local_reduction_mean",
+    "local_reduction_variance", "group_norm_apply", "layer_norm_apply", "device_status",
+    "launch_count", "HostPipeline", "GN_AUTO", "GN_RESIDENT", "GN_SPLIT",
+]
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return F32
+    if t.dtype == torch.float16:
+        return F16
+    raise TypeError(f"unsupported dtype {t.dtype}: float32 or float16 only")
+
+
+def _dev(t: torch.Tensor, name: str) -> int:
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise TypeError(f"{name} must be a CUDA tensor (the kernels have no host fallback)")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+    return t.data_ptr()
+
+
+def _f32(t: torch.Tensor, name: str) -> int:
+    if t.dtype != torch.float32:
+        raise TypeError(f"{name} must be float32")
+    return _dev(t, name)
+
+
+def _stream(stream) -> int:
+    s = stream if stream is not None else torch.cuda.current_stream()
+    return s.cuda_stream if hasattr(s, "cuda_stream") else int(s)
+
+
+_workspaces: dict[int, torch.Tensor] = {}
+
+
+def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
+    """A per-device scratch buffer, grown on demand and reused (stream-ordered by the caller)."""
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(max(nbytes, 1 << 16), dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def launch_count() -> int:
+    return int(lib.sdfl_launch_count())
+
+
+def device_status(clear: bool = True, stream=None) -> int:
+    v = C.c_uint(0)
+    check(lib.sdfl_device_status(C.byref(v), int(clear), _stream(stream)), "sdfl_device_status")
+    return int(v.value)
+
+
+def groupnorm_plan(batch: int, channels: int, hw: int, num_groups: int, dtype: torch.dtype,
+                   path: int = GN_AUTO, cluster_or_splits: int = 0) -> dict:
+    arr = (C.c_int64 * 6)()
+    code = F16 if dtype == torch.float16 else F32
+    check(lib.sdfl_groupnorm_plan(batch, channels, hw, num_groups, code, path, cluster_or_splits,
+                                  arr), "sdfl_groupnorm_plan")
+    keys = ("path", "cluster", "threads", "splits", "smem", "workspace")
+    return dict(zip(keys, (int(v) for v in arr)))
+
+
+def groupnorm(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor, num_groups: int,
+              eps: float = 1e-5, silu: bool = False, out: torch.Tensor | None = None,
+              path: int = GN_AUTO, cluster_or_splits: int = 0, stream=None) -> torch.Tensor:
+    """GroupNorm(+SiLU) on an NCHW tensor [B, C, ...]; out may be x itself."""
+    if x.dim() < 2:
+        raise ValueError("x must be [batch, channels, ...]")
+    out = torch.empty_like(x) if out is None else out
+    if out.shape != x.shape or out.dtype != x.dtype:
+        raise ValueError("out must match x in shape and dtype")
+    B, Cc = x.shape[0], x.shape[1]
+    hw = x.numel() // (B * Cc) if B * Cc else 0
+    code = _dtype_code(x)
+    nbytes = lib.sdfl_groupnorm_workspace_bytes_ex(B, Cc, hw, num_groups, code, path,
+                                                   cluster_or_splits)
+    ws = _workspace(x.device, nbytes)
+    with torch.cuda.device(x.device):
+        check(lib.sdfl_groupnorm_forward_ex(
+            _dev(x, "x"), _dev(out, "out"), _f32(gamma, "gamma"), _f32(beta, "beta"), B, Cc, hw,
+            num_groups, eps, int(silu), code, ws.data_ptr(), ws.numel(), path, cluster_or_splits,
+            _stream(stream)), "sdfl_groupnorm_forward")
+    return out
+
+
+def layernorm(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor, eps: float = 1e-5,
+              out: torch.Tensor | None = None, stream=None) -> torch.Tensor:
+    out = torch.empty_like(x) if out is None else out
+    D = x.shape[-1]
+    rows = x.numel() // D if D else 0
+    with torch.cuda.device(x.device):
+        check(lib.sdfl_layernorm_forward(_dev(x, "x"), _dev(out, "out"), _f32(gamma, "gamma"),
+                                         _f32(beta, "beta"), rows, D, eps, _dtype_code(x),
+                                         _stream(stream)), "sdfl_layernorm_forward")
+    return out
+
+
+def gelu_multiply(ab: torch.Tensor, out: torch.Tensor | None = None, stream=None) -> torch.Tensor:
+    """ab [..., 2D] -> [..., D]: value half times gelu(gate half)."""
+    D = ab.shape[-1] // 2
+    if ab.shape[-1] != 2 * D:
+        raise ValueError("last dimension must be even")
+    out = torch.empty(ab.shape[:-1] + (D,), dtype=ab.dtype, device=ab.device) if out is None else out
+    rows = ab.numel() // (2 * D) if D else 0
+    with torch.cuda.device(ab.device):
+        check(lib.sdfl_gelu_multiply(_dev(ab, "ab"), _dev(out, "out"), rows, D, _dtype_code(ab),
+                                     _stream(stream)), "sdfl_gelu_multiply")
+    return out
+
+
+def _unary(fn_name: str, x: torch.Tensor, out, stream) -> torch.Tensor:
+    out = torch.empty_like(x) if out is None else out
+    with torch.cuda.device(x.device):
+        check(getattr(lib, fn_name)(_dev(x, "x"), _dev(out, "out"), x.numel(), _dtype_code(x),
+                                    _stream(stream)), fn_name)
+    return out
+
+
+def silu(x, out=None, stream=None):
+    return _unary("sdfl_silu", x, out, stream)
+
+
+def gelu(x, out=None, stream=None):
+    return _unary("sdfl_gelu", x, out, stream)
+
+
+def quick_gelu(x, out=None, stream=None):
+    return _unary("sdfl_quick_gelu", x, out, stream)
+
+
+def elemwise_add(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, stream=None):
+    out = torch.empty_like(a) if out is None else out
+    if a.shape != b.shape or a.dtype != b.dtype:
+        raise ValueError("a and b must match")
+    with torch.cuda.device(a.device):
+        check(lib.sdfl_elemwise_add(_dev(a, "a"), _dev(b, "b"), _dev(out, "out"), a.numel(),
+                                    _dtype_code(a), _stream(stream)), "sdfl_elemwise_add")
+    return out
+
+
+def token_embedding(ids: torch.Tensor, table: torch.Tensor, pos: torch.Tensor,
+                    out: torch.Tensor | None = None, status: torch.Tensor | None = None,
+                    stream=None) -> torch.Tensor:
+    """ids [B, T] int64; table [vocab, D]; pos [T, D] -> [B, T, D] = table[ids] + pos."""
+    if ids.dtype != torch.int64:
+        raise TypeError("ids must be int64")
+    B, T = ids.shape
+    vocab, D = table.shape
+    if pos.shape != (T, D) or pos.dtype != table.dtype:
+        raise ValueError("pos must be [T, D] with the table's dtype")
+    out = torch.empty((B, T, D), dtype=table.dtype, device=table.device) if out is None else out
+    st = 0 if status is None else _dev(status, "status")
+    if status is not None and status.dtype != torch.int32:
+        raise TypeError("status must be int32")
+    with torch.cuda.device(table.device):
+        check(lib.sdfl_token_embedding(_dev(ids, "ids"), _dev(table, "table"), _dev(pos, "pos"),
+                                       _dev(out, "out"), B, T, D, vocab, _dtype_code(table), st,
+                                       _stream(stream)), "sdfl_token_embedding")
+    return out
+
+
+def timestep_embedding(t: torch.Tensor, dim: int, max_period: float = 10000.0,
+                       dtype: torch.dtype = torch.float32, out: torch.Tensor | None = None,
+                       stream=None) -> torch.Tensor:
+    if t.dtype != torch.int64:
+        raise TypeError("t must be int64")
+    B = t.numel()
+    out = torch.empty((B, dim), dtype=dtype, device=t.device) if out is None else out
+    with torch.cuda.device(t.device):
+        check(lib.sdfl_timestep_embedding(_dev(t, "t"), _dev(out, "out"), B, dim, max_period,
+                                          _dtype_code(out), _stream(stream)),
+              "sdfl_timestep_embedding")
+    return out
+
+
+# ---- the reference's three-launch sequence, kernel by kernel --------------------------------------
+
+def local_reduction_mean(x: torch.Tensor, groups: int, stream=None) -> torch.Tensor:
+    out = torch.empty(groups, dtype=torch.float32, device=x.device)
+    n = x.numel() // groups if groups else 0
+    with torch.cuda.device(x.device):
+        check(lib.sdfl_local_reduction_mean(_dev(x, "x"), out.data_ptr(), groups, n, _dtype_code(x),
+                                            _stream(stream)), "sdfl_local_reduction_mean")
+    return out
+
+
+def local_reduction_variance(x: torch.Tensor, mean: torch.Tensor, groups: int, stream=None):
+    out = torch.empty(groups, dtype=torch.float32, device=x.device)
+    n = x.numel() // groups if groups else 0
+    with torch.cuda.device(x.device):
+        check(lib.sdfl_local_reduction_variance(_dev(x, "x"), _f32(mean, "mean"), out.data_ptr(),
+                                                groups, n, _dtype_code(x), _stream(stream)),
+              "sdfl_local_reduction_variance")
+    return out
+
+
+def group_norm_apply(x, mean, var, weight, bias, group_size: int, channel_size: int, eps: float,
+                     num_channels: int, out=None, stream=None):
+    out = torch.empty_like(x) if out is None else out
+    with torch.cuda.device(x.device):
+        check(lib.sdfl_group_norm(_dev(x, "x"), _f32(mean, "mean"), _f32(var, "var"),
+                                  _f32(weight, "weight"), _f32(bias, "bias"), group_size,
+                                  channel_size, eps, _dev(out, "out"), x.numel(), num_channels,
+                                  _dtype_code(x), _stream(stream)), "sdfl_group_norm")
+    return out
+
+
+def layer_norm_apply(x, mean, var, weight, bias, chunk_size: int, eps: float = 1e-5, out=None,
+                     stream=None):
+    out = torch.empty_like(x) if out is None else out
+    with torch.cuda.device(x.device):
+        check(lib.sdfl_layer_norm(_dev(x, "x"), _f32(mean, "mean"), _f32(var, "var"),
+                                  _f32(weight, "weight"), _f32(bias, "bias"), chunk_size,
+                                  _dev(out, "out"), x.numel(), eps, _dtype_code(x),
+                                  _stream(stream)), "sdfl_layer_norm")
+    return out
+
+
+class HostPipeline:
+    """Host-buffer GroupNorm(+SiLU): page-locked host tensors in, page-locked host tensors out.
+
+    Owns the device staging slots and streams (sdfl_host_pipeline_create); `groupnorm` blocks
+    until the output is complete on the host.
+    """
+
+    def __init__(self, max_slot_bytes: int = 32 << 20, depth: int = 4, device: int | None = None):
+        self._h = C.c_void_p()
+        self.device = torch.cuda.current_device() if device is None else device
+        with torch.cuda.device(self.device):
+            check(lib.sdfl_host_pipeline_create(C.byref(self._h), max_slot_bytes, depth),
+                  "sdfl_host_pipeline_create")
+
+    def close(self) -> None:
+        if self._h:
+            with torch.cuda.device(self.device):
+                lib.sdfl_host_pipeline_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def groupnorm(self, h_x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor, num_groups: int,
+                  eps: float = 1e-5, silu: bool = False, h_out: torch.Tensor | None = None):
+        if h_x.is_cuda or not h_x.is_contiguous():
+            raise TypeError("h_x must be a contiguous host tensor")
+        h_out = torch.empty_like(h_x, pin_memory=h_x.is_pinned()) if h_out is None else h_out
+        B, Cc = h_x.shape[0], h_x.shape[1]
+        hw = h_x.numel() // (B * Cc) if B * Cc else 0
+        with torch.cuda.device(self.device):
+            check(lib.sdfl_groupnorm_forward_host(
+                self._h, h_x.data_ptr(), h_out.data_ptr(), _f32(gamma, "gamma"), _f32(beta, "beta"),
+                B, Cc, hw, num_groups, eps, int(silu), _dtype_code(h_x)),
+                "sdfl_groupnorm_forward_host")
+        return h_out
+
+
+_ = (_capi, SdflError)

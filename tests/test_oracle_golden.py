@@ -1,0 +1,54 @@
+"""The plain-C oracle against the golden vectors produced by the reference's own kernel
+source (tests/golden/reference_kernels.npz, written by tests/golden/make_golden.py).
+Bit equality: same operations in the same order, no contraction."""
+import os
+
+import numpy as np
+import pytest
+
+from conftest import assert_bit_equal
+
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "reference_kernels.npz")
+
+
+@pytest.fixture(scope="module")
+def golden():
+    return np.load(GOLDEN)
+
+
+def _names(golden, prefix):
+    return sorted({k.split(".")[0] for k in golden.files if k.startswith(prefix)})
+
+
+def test_golden_file_has_cases(golden):
+    assert len(_names(golden, "gn_")) >= 4 and len(_names(golden, "ln_")) >= 3
+
+
+def test_group_norm_matches_reference_kernels(golden, oracle_mod):
+    for name in _names(golden, "gn_"):
+        G, silu = (int(v) for v in golden[f"{name}.meta"])
+        eps = float(golden[f"{name}.eps"][0])
+        y, mean, var = oracle_mod.group_norm(golden[f"{name}.x"], golden[f"{name}.gamma"],
+                                             golden[f"{name}.beta"], G, eps, bool(silu),
+                                             return_stats=True)
+        assert_bit_equal(mean, golden[f"{name}.mean"], f"{name} mean")
+        assert_bit_equal(var, golden[f"{name}.var"], f"{name} var")
+        assert_bit_equal(y, golden[f"{name}.y"], f"{name} y")
+
+
+def test_layer_norm_matches_reference_kernels(golden, oracle_mod):
+    for name in _names(golden, "ln_"):
+        y, mean, var = oracle_mod.layer_norm(golden[f"{name}.x"], golden[f"{name}.gamma"],
+                                             golden[f"{name}.beta"], 1e-5, return_stats=True)
+        assert_bit_equal(mean, golden[f"{name}.mean"], f"{name} mean")
+        assert_bit_equal(var, golden[f"{name}.var"], f"{name} var")
+        assert_bit_equal(y, golden[f"{name}.y"], f"{name} y")
+
+
+def test_geglu_and_activations_match_reference_kernels(golden, oracle_mod):
+    assert_bit_equal(oracle_mod.gelu_multiply(golden["geglu_r5_d64.ab"]), golden["geglu_r5_d64.y"],
+                     "gelu_multiply")
+    x = golden["act.x"]
+    assert_bit_equal(oracle_mod.silu(x), golden["act.silu"], "silu")
+    assert_bit_equal(oracle_mod.gelu(x), golden["act.gelu"], "gelu")
+    assert_bit_equal(oracle_mod.elemwise_add(x, golden["act.other"]), golden["act.add"], "add")
