@@ -23,6 +23,9 @@
 
 #include <cooperative_groups.h>
 
+#include <map>
+#include <mutex>
+
 namespace cg = cooperative_groups;
 
 namespace sdfl {
@@ -455,61 +458,86 @@ inline int pow2_at_least(double x) {
     return c;
 }
 
+// Per-device, per-kernel-instance one-time attribute set-up (maximum dynamic shared memory and
+// the opt-in for 16-CTA clusters), so that launches themselves make no attribute calls.
+constexpr int kMaxDevices = 64;
+
+template <typename T, int ACT>
+cudaError_t ensure_resident_attrs() {
+    static std::atomic<bool> done[kMaxDevices];
+    int dev = 0;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess) return err;
+    if (dev >= 0 && dev < kMaxDevices && done[dev].load(std::memory_order_acquire)) return cudaSuccess;
+    auto kernel = gn_resident_kernel<T, ACT>;
+    err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(kHeaderBytes + kMaxPartBytes));
+    if (err != cudaSuccess) return err;
+    err = cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    if (err != cudaSuccess) return err;
+    if (dev >= 0 && dev < kMaxDevices) done[dev].store(true, std::memory_order_release);
+    return cudaSuccess;
+}
+
+inline void cluster_config(cudaLaunchConfig_t *cfg, cudaLaunchAttribute *attr, unsigned grid,
+                           int cluster, size_t smem, cudaStream_t stream) {
+    *cfg = cudaLaunchConfig_t{};
+    cfg->gridDim = dim3(grid);
+    cfg->blockDim = dim3(kResidentThreads);
+    cfg->dynamicSmemBytes = smem;
+    cfg->stream = stream;
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = static_cast<unsigned>(cluster);
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg->attrs = attr;
+    cfg->numAttrs = 1;
+}
+
 template <typename T, int ACT>
 cudaError_t launch_resident(const ResidentArgs &a, int64_t units, const GnPlan &plan,
                             cudaStream_t stream) {
-    auto kernel = gn_resident_kernel<T, ACT>;
-    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           static_cast<int>(plan.smem));
+    cudaError_t err = ensure_resident_attrs<T, ACT>();
     if (err != cudaSuccess) return err;
-    if (plan.cluster > 8) {
-        err = cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
-        if (err != cudaSuccess) return err;
-    }
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(static_cast<unsigned>(units * plan.cluster));
-    cfg.blockDim = dim3(kResidentThreads);
-    cfg.dynamicSmemBytes = plan.smem;
-    cfg.stream = stream;
+    cudaLaunchConfig_t cfg;
     cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = static_cast<unsigned>(plan.cluster);
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    err = cudaLaunchKernelEx(&cfg, kernel, a);
+    cluster_config(&cfg, attr, static_cast<unsigned>(units * plan.cluster), plan.cluster, plan.smem,
+                   stream);
+    err = cudaLaunchKernelEx(&cfg, gn_resident_kernel<T, ACT>, a);
     if (err == cudaSuccess) g_launches.fetch_add(1);
     return err;
 }
 
+// Can at least one cluster of this size and shared-memory footprint be resident (a 16-CTA
+// cluster needs a GPC with 16 free SMs)?  Asked of the driver once per (device, dtype,
+// cluster, shared-memory size in KiB) and remembered.
 template <typename T>
 cudaError_t resident_clusters_fit(const GnPlan &plan, int *fits) {
-    // Ask the driver whether at least one cluster of this size and shared-memory footprint can
-    // be resident (a 16-CTA cluster needs a GPC with 16 free SMs).
-    auto kernel = gn_resident_kernel<T, kActSilu>;
-    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           static_cast<int>(plan.smem));
+    static std::mutex mu;
+    static std::map<uint64_t, int> cache;
+    int dev = 0;
+    cudaError_t err = cudaGetDevice(&dev);
     if (err != cudaSuccess) return err;
-    if (plan.cluster > 8) {
-        err = cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
-        if (err != cudaSuccess) return err;
+    const uint64_t key = (static_cast<uint64_t>(dev) << 40) | (static_cast<uint64_t>(sizeof(T)) << 32) |
+                         (static_cast<uint64_t>(plan.cluster) << 24) | ((plan.smem + 1023) / 1024);
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        auto it = cache.find(key);
+        if (it != cache.end()) { *fits = it->second; return cudaSuccess; }
     }
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(static_cast<unsigned>(plan.cluster));
-    cfg.blockDim = dim3(kResidentThreads);
-    cfg.dynamicSmemBytes = plan.smem;
+    err = ensure_resident_attrs<T, kActSilu>();
+    if (err != cudaSuccess) return err;
+    cudaLaunchConfig_t cfg;
     cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = static_cast<unsigned>(plan.cluster);
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cluster_config(&cfg, attr, static_cast<unsigned>(plan.cluster), plan.cluster,
+                   ((plan.smem + 1023) / 1024) * 1024, nullptr);
     int n = 0;
-    err = cudaOccupancyMaxActiveClusters(&n, kernel, &cfg);
+    err = cudaOccupancyMaxActiveClusters(&n, gn_resident_kernel<T, kActSilu>, &cfg);
+    if (err != cudaSuccess) return err;
     *fits = n;
-    return err;
+    std::lock_guard<std::mutex> lock(mu);
+    cache[key] = n;
+    return cudaSuccess;
 }
 
 }  // namespace

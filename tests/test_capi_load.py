@@ -1,0 +1,81 @@
+"""The C-ABI library loads on a machine without a GPU, exports every symbol include/sdfl.h
+declares, and rejects bad arguments before touching CUDA.  No compute call is made here."""
+import ctypes as C
+import os
+import re
+
+import pytest
+
+from conftest import ROOT, load_package
+
+HEADER = os.path.join(ROOT, "include", "sdfl.h")
+
+
+def declared_symbols():
+    text = open(HEADER).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(sdfl_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_declares_the_reference_kernel_names():
+    names = declared_symbols()
+    for kernel in ("local_reduction_mean", "local_reduction_variance", "group_norm", "layer_norm",
+                   "gelu_multiply", "gelu", "silu", "elemwise_add"):
+        assert f"sdfl_{kernel}" in names
+    assert len(names) >= 25
+
+
+def test_library_exports_every_declared_symbol():
+    pkg = load_package()
+    lib = C.CDLL(pkg._capi.LIB_PATH)
+    for name in declared_symbols():
+        assert hasattr(lib, name), f"{name} declared in sdfl.h but not exported"
+    assert set(pkg._capi.SIGNATURES) == set(declared_symbols())
+
+
+def test_version_and_status_strings():
+    lib = load_package()._capi.lib
+    assert b"sm_100a" in lib.sdfl_version()
+    assert lib.sdfl_status_string(0) == b"ok"
+    assert lib.sdfl_status_string(-5) == b"input and output partially overlap"
+    assert lib.sdfl_launch_count() >= 0
+
+
+def test_argument_validation_needs_no_device():
+    cap = load_package()._capi
+    lib = cap.lib
+    A, B = 4096, 8192                      # stand-in addresses: rejected before any use
+    # channels not divisible by groups (the reference throws at nn/GroupNorm.cpp:83-87)
+    assert lib.sdfl_groupnorm_forward(A, B, A, A, 1, 30, 64, 32, 1e-5, 1, 0, None, 0, None) == cap.ERR_INVALID_VALUE
+    assert lib.sdfl_groupnorm_forward(A, B, A, A, 1, 32, 64, 32, 1e-5, 1, 7, None, 0, None) == cap.ERR_INVALID_VALUE
+    assert lib.sdfl_groupnorm_forward(None, B, A, A, 1, 32, 64, 32, 1e-5, 1, 0, None, 0, None) == cap.ERR_INVALID_POINTER
+    assert lib.sdfl_groupnorm_forward(A, A + 64, A, A, 1, 32, 64, 32, 1e-5, 1, 0, None, 0, None) == cap.ERR_OVERLAP
+    assert lib.sdfl_groupnorm_forward(A, B, A, A, 0, 32, 64, 32, 1e-5, 1, 0, None, 0, None) == cap.OK   # empty batch
+    assert lib.sdfl_layernorm_forward(A, B, A, A, 4, 0, 1e-5, 0, None) == cap.ERR_INVALID_VALUE
+    assert lib.sdfl_layernorm_forward(A, None, A, A, 4, 64, 1e-5, 0, None) == cap.ERR_INVALID_POINTER
+    assert lib.sdfl_layernorm_forward(A, B, A, A, 0, 64, 1e-5, 0, None) == cap.OK
+    assert lib.sdfl_gelu_multiply(A, A + 16, 4, 64, 0, None) == cap.ERR_OVERLAP
+    assert lib.sdfl_silu(A, A + 4, 64, 0, None) == cap.ERR_OVERLAP
+    assert lib.sdfl_silu(A, A, 0, 0, None) == cap.OK
+    assert lib.sdfl_silu(A, A, -1, 0, None) == cap.ERR_INVALID_VALUE
+    assert lib.sdfl_elemwise_add(A, B, None, 8, 0, None) == cap.ERR_INVALID_POINTER
+    assert lib.sdfl_token_embedding(A, A, A, B, 2, 77, 768, 0, 0, None, None) == cap.ERR_INVALID_VALUE
+    assert lib.sdfl_timestep_embedding(A, B, 2, 320, -1.0, 0, None) == cap.ERR_INVALID_VALUE
+    assert lib.sdfl_local_reduction_mean(A, B, 4, 0, 0, None) == cap.ERR_INVALID_VALUE
+    assert lib.sdfl_host_pipeline_create(None, 1024, 2) == cap.ERR_INVALID_POINTER
+
+
+def test_workspace_query_and_plan_without_device():
+    cap = load_package()._capi
+    lib = cap.lib
+    n = lib.sdfl_groupnorm_workspace_bytes(8, 128, 512 * 512, 32, 1)
+    assert n > 0 and n % 8 == 0
+    assert lib.sdfl_groupnorm_workspace_bytes(8, 130, 64, 32, 1) == 0     # invalid shape
+    plan = (C.c_int64 * 6)()
+    assert lib.sdfl_groupnorm_plan(2, 30, 64, 32, 0, 0, 0, plan) == cap.ERR_INVALID_VALUE
+
+
+def test_missing_library_is_a_loud_import_error(tmp_path):
+    cap = load_package()._capi
+    with pytest.raises(ImportError):
+        cap.load(str(tmp_path / "libsdfl.so"))

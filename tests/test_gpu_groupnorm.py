@@ -1,0 +1,195 @@
+"""GroupNorm(+SiLU) CUDA kernels against the CPU oracle, through the C ABI."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import TOL, assert_close, rng_for
+from gpu_util import Guarded, gn_inputs, oracle_group_norm, to_dev, to_np
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "reference_kernels.npz")
+
+
+def run_gn(sdfl, x, gamma, beta, G, eps, silu, **kw):
+    return to_np(sdfl.ops.groupnorm(to_dev(x), to_dev(gamma), to_dev(beta), G, eps, silu, **kw))
+
+
+def test_golden_vectors_from_the_reference_kernels(sdfl):
+    g = np.load(GOLDEN)
+    for name in sorted({k.split(".")[0] for k in g.files if k.startswith("gn_")}):
+        G, silu = (int(v) for v in g[f"{name}.meta"])
+        eps = float(g[f"{name}.eps"][0])
+        for path in (sdfl.ops.GN_AUTO, sdfl.ops.GN_SPLIT):
+            got = run_gn(sdfl, g[f"{name}.x"], g[f"{name}.gamma"], g[f"{name}.beta"], G, eps,
+                         bool(silu), path=path)
+            assert_close(got, g[f"{name}.y"], 1e-5, f"{name} path {path}")
+
+
+def test_config1_fp32_every_path_and_cluster_size(sdfl):
+    x, gamma, beta = gn_inputs(rng_for(1, 0), (1, 320, 64, 64), "float32")
+    want = oracle_group_norm(x, gamma, beta, 32, 1e-5, True)
+    plan = sdfl.ops.groupnorm_plan(1, 320, 4096, 32, torch.float32)
+    assert plan["path"] == sdfl.ops.GN_RESIDENT and plan["workspace"] == 0
+    assert_close(run_gn(sdfl, x, gamma, beta, 32, 1e-5, True), want, 1e-5, "auto")
+    for cluster in (1, 2, 4, 8, 16):
+        try:
+            got = run_gn(sdfl, x, gamma, beta, 32, 1e-5, True, path=sdfl.ops.GN_RESIDENT,
+                         cluster_or_splits=cluster)
+        except sdfl.SdflError as e:
+            # a 16-CTA cluster is an opt-in size: the device may not be able to host one
+            assert cluster == 16 and e.status == sdfl._capi.ERR_UNSUPPORTED
+            continue
+        assert_close(got, want, 1e-5, f"resident cluster {cluster}")
+    for splits in (0, 1, 3, 8):
+        got = run_gn(sdfl, x, gamma, beta, 32, 1e-5, True, path=sdfl.ops.GN_SPLIT,
+                     cluster_or_splits=splits)
+        assert_close(got, want, 1e-5, f"split {splits}")
+    assert sdfl.ops.device_status() == 0
+
+
+UNET_SHAPES = [(320, 64), (640, 32), (1280, 16), (1280, 8), (640, 64), (960, 64), (960, 32),
+               (1280, 32), (1920, 32), (1920, 16), (2560, 16), (2560, 8)]
+
+
+@pytest.mark.parametrize("C,H", UNET_SHAPES)
+def test_config3_unet_sweep_fp16_batch2(sdfl, C, H):
+    x, gamma, beta = gn_inputs(rng_for(3, UNET_SHAPES.index((C, H))), (2, C, H, H), "float16")
+    want = oracle_group_norm(x, gamma, beta, 32, 1e-5, True)
+    got = run_gn(sdfl, x, gamma, beta, 32, 1e-5, True)
+    assert got.dtype == np.float16
+    assert_close(got, want, TOL["float16"], f"{C}@{H}")
+
+
+@pytest.mark.parametrize("C,H", [(320, 64), (1280, 8), (2560, 16)])
+def test_unet_shapes_fp32_eps_and_no_silu(sdfl, C, H):
+    x, gamma, beta = gn_inputs(rng_for(3, 100 + C + H), (2, C, H, H), "float32")
+    for eps, silu in ((1e-5, True), (1e-6, False)):      # ResBlock norm / SpatialTransformer norm
+        want = oracle_group_norm(x, gamma, beta, 32, eps, silu)
+        assert_close(run_gn(sdfl, x, gamma, beta, 32, eps, silu), want, 1e-5, f"{C}@{H} {eps}")
+
+
+@pytest.mark.parametrize("shape", [(2, 512, 64, 64), (1, 512, 128, 128), (1, 256, 256, 256),
+                                   (1, 128, 512, 512)])
+def test_config5_vae_shapes_fp16(sdfl, shape):
+    x, gamma, beta = gn_inputs(rng_for(5, shape[1]), shape, "float16")
+    want = oracle_group_norm(x, gamma, beta, 32, 1e-6, True)
+    plan = sdfl.ops.groupnorm_plan(shape[0], shape[1], shape[2] * shape[3], 32, torch.float16)
+    assert plan["path"] in (sdfl.ops.GN_RESIDENT, sdfl.ops.GN_SPLIT), plan
+    got = run_gn(sdfl, x, gamma, beta, 32, 1e-6, True)
+    assert_close(got, want, TOL["float16"], f"{shape} automatic path {plan}")
+    got = run_gn(sdfl, x, gamma, beta, 32, 1e-6, True, path=sdfl.ops.GN_SPLIT)
+    assert_close(got, want, TOL["float16"], f"{shape} split")
+    assert sdfl.ops.device_status() == 0
+
+
+def test_vae_fp32_slab_beyond_cluster_capacity_takes_split_path(sdfl):
+    shape = (1, 128, 512, 512)                 # 4 MiB per group in fp32
+    plan = sdfl.ops.groupnorm_plan(1, 128, 512 * 512, 32, torch.float32)
+    assert plan["path"] == sdfl.ops.GN_SPLIT and plan["workspace"] > 0
+    x, gamma, beta = gn_inputs(rng_for(5, 99), shape, "float32")
+    want = oracle_group_norm(x, gamma, beta, 32, 1e-6, True)
+    assert_close(run_gn(sdfl, x, gamma, beta, 32, 1e-6, True), want, 1e-5, "fp32 4 MiB slabs")
+
+
+RAGGED = [((3, 6, 5, 7), 3), ((2, 12, 1, 1), 4), ((1, 4, 3, 3), 4), ((2, 10, 9, 11), 5),
+          ((1, 8, 2, 2), 1), ((5, 32, 1, 3), 32), ((1, 64, 33, 31), 8)]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "float16"])
+@pytest.mark.parametrize("shape,G", RAGGED)
+def test_ragged_shapes_the_reference_refuses(sdfl, shape, G, dtype):
+    """Group sizes that are not multiples of 64 (the reference throws) or of the vector width."""
+    x, gamma, beta = gn_inputs(rng_for(1, 200 + sum(shape)), shape, dtype)
+    for silu in (False, True):
+        want = oracle_group_norm(x, gamma, beta, G, 1e-5, silu)
+        out = Guarded(shape, getattr(torch, dtype))
+        sdfl.ops.groupnorm(to_dev(x), to_dev(gamma), to_dev(beta), G, 1e-5, silu, out=out.tensor)
+        out.check()
+        assert_close(to_np(out.tensor), want, TOL[dtype], f"{shape} G={G} silu={silu}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "float16"])
+def test_misaligned_buffers_and_guard_bands(sdfl, dtype):
+    shape = (2, 64, 16, 16)
+    x, gamma, beta = gn_inputs(rng_for(1, 300), shape, dtype)
+    want = oracle_group_norm(x, gamma, beta, 32, 1e-5, True)
+    for mis_in, mis_out in ((0, 0), (1, 0), (0, 3), (1, 1)):
+        xin = Guarded(shape, getattr(torch, dtype), misalign=mis_in)
+        xin.tensor.copy_(to_dev(x))
+        out = Guarded(shape, getattr(torch, dtype), misalign=mis_out)
+        sdfl.ops.groupnorm(xin.tensor, to_dev(gamma), to_dev(beta), 32, 1e-5, True, out=out.tensor)
+        out.check()
+        xin.check()
+        assert_close(to_np(out.tensor), want, TOL[dtype], f"misalign {mis_in},{mis_out}")
+
+
+@pytest.mark.parametrize("path", [1, 2])
+def test_in_place_as_the_reference_callers_do(sdfl, path):
+    """forward(buf, buf): nn/ResBlock.cpp:222, UNetModel.cpp:1797, Decoder.cpp:523."""
+    x, gamma, beta = gn_inputs(rng_for(1, 400), (2, 320, 32, 32), "float32")
+    want = oracle_group_norm(x, gamma, beta, 32, 1e-5, True)
+    buf = to_dev(x)
+    sdfl.ops.groupnorm(buf, to_dev(gamma), to_dev(beta), 32, 1e-5, True, out=buf, path=path)
+    assert_close(to_np(buf), want, 1e-5, f"in place path {path}")
+
+
+def test_large_mean_small_spread(sdfl):
+    """Statistics must not cancel: mean 10, std 0.5.  The fp32 mean of such data is itself
+    only good to ~1e-6, which the division by std doubles; the reference kernels carry the same
+    conditioning, so the bound here is 3e-5 instead of 1e-5."""
+    x, gamma, beta = gn_inputs(rng_for(1, 500), (2, 64, 32, 32), "float32", mean=10.0, std=0.5)
+    want = oracle_group_norm(x, gamma, beta, 32, 1e-5, True)
+    for path in (1, 2):
+        got = run_gn(sdfl, x, gamma, beta, 32, 1e-5, True, path=path)
+        assert_close(got, want, 3e-5, f"offset data path {path}")
+
+
+def test_batch_is_independent_runs_and_results_are_deterministic(sdfl):
+    x, gamma, beta = gn_inputs(rng_for(5, 600), (4, 512, 32, 32), "float16")
+    dx, dg, db = to_dev(x), to_dev(gamma), to_dev(beta)
+    full = sdfl.ops.groupnorm(dx, dg, db, 32, 1e-6, True)
+    again = sdfl.ops.groupnorm(dx, dg, db, 32, 1e-6, True)
+    assert torch.equal(full, again)
+    for n in range(4):
+        one = sdfl.ops.groupnorm(dx[n:n + 1].contiguous(), dg, db, 32, 1e-6, True)
+        assert torch.equal(one[0], full[n])
+
+
+def test_empty_batch_and_errors(sdfl):
+    g = to_dev(np.ones(32, np.float32))
+    out = sdfl.ops.groupnorm(torch.empty((0, 32, 8, 8), device="cuda"), g, g, 32)
+    assert out.shape == (0, 32, 8, 8)
+    x = torch.zeros((1, 30, 8, 8), device="cuda")
+    with pytest.raises(sdfl.SdflError) as e:
+        sdfl.ops.groupnorm(x, g, g, 32)
+    assert e.value.status == sdfl._capi.ERR_INVALID_VALUE
+    with pytest.raises(TypeError):
+        sdfl.ops.groupnorm(torch.zeros((1, 32, 8, 8)), g, g, 32)       # host tensor: no fallback
+
+
+def test_full_size_vae_tensor_properties(sdfl):
+    """[8,128,512,512] fp16 (1 GiB in, 1 GiB out): too big for the CPU oracle in a test, so
+    check what must hold at any size: with gamma = 1, beta = 0 and no activation every
+    (image, group) slab of the output has mean ~0 and variance ~1; image n of the batch equals
+    the single-image run bit for bit; the SiLU variant equals silu() of the plain output."""
+    B, C, H = 8, 128, 512
+    gen = torch.Generator(device="cuda").manual_seed(5005)
+    x = (torch.randn((B, C, H, H), device="cuda", generator=gen, dtype=torch.float32) * 1.5 + 0.5).half()
+    ones = torch.ones(C, device="cuda")
+    zeros = torch.zeros(C, device="cuda")
+    y = sdfl.ops.groupnorm(x, ones, zeros, 32, 1e-6, False)
+    mean = sdfl.ops.local_reduction_mean(y, B * 32)
+    var = sdfl.ops.local_reduction_variance(y, mean, B * 32)
+    assert float(mean.abs().max()) < 2e-3
+    assert float((var - 1).abs().max()) < 5e-3
+    one = sdfl.ops.groupnorm(x[3:4].contiguous(), ones, zeros, 32, 1e-6, False)
+    assert torch.equal(one[0], y[3])
+    del one
+    ys = sdfl.ops.groupnorm(x, ones, zeros, 32, 1e-6, True)
+    ref = sdfl.ops.silu(y)
+    diff = (ys.float() - ref.float()).abs()
+    assert float((diff - 2e-3 * ref.float().abs()).max()) <= 2e-3
+    assert sdfl.ops.device_status() == 0

@@ -1,0 +1,109 @@
+"""LayerNorm CUDA kernels against the CPU oracle, through the C ABI."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import TOL, assert_close, rng_for
+from gpu_util import NP_DTYPE, Guarded, to_dev, to_np
+
+import oracle
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "reference_kernels.npz")
+
+
+def ln_inputs(rng, rows, D, dtype, mean=0.0, std=1.0):
+    x = (rng.standard_normal((rows, D)) * std + mean).astype(np.float32).astype(NP_DTYPE[dtype])
+    gamma = (1.0 + 0.1 * rng.standard_normal(D)).astype(np.float32)
+    beta = (0.1 * rng.standard_normal(D)).astype(np.float32)
+    return x, gamma, beta
+
+
+def test_golden_vectors_from_the_reference_kernels(sdfl):
+    g = np.load(GOLDEN)
+    for name in sorted({k.split(".")[0] for k in g.files if k.startswith("ln_")}):
+        got = sdfl.ops.layernorm(to_dev(g[f"{name}.x"]), to_dev(g[f"{name}.gamma"]),
+                                 to_dev(g[f"{name}.beta"]), 1e-5)
+        assert_close(to_np(got), g[f"{name}.y"], 1e-5, name)
+
+
+# rows x D: config 2 (CLIP, 768 and the reference's own 1024), config 4 (UNet), every register
+# bucket of the row-in-registers kernel, and rows that force the block-per-row kernel.
+LN_SHAPES = [(154, 768), (77, 1024), (8192, 320), (1024, 640), (256, 1280), (64, 1280),
+             (5, 64), (3, 8), (7, 4096), (2, 8192), (3, 16384), (33, 100), (9, 7), (4, 1), (1, 330)]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "float16"])
+@pytest.mark.parametrize("rows,D", LN_SHAPES)
+def test_layernorm_matches_oracle(sdfl, rows, D, dtype):
+    x, gamma, beta = ln_inputs(rng_for(2, rows + D), rows, D, dtype)
+    want = oracle.layer_norm(x.astype(np.float32), gamma, beta, 1e-5)
+    out = Guarded((rows, D), getattr(torch, dtype))
+    sdfl.ops.layernorm(to_dev(x), to_dev(gamma), to_dev(beta), 1e-5, out=out.tensor)
+    out.check()
+    assert_close(to_np(out.tensor), want, TOL[dtype], f"LN {rows}x{D} {dtype}")
+
+
+def test_layernorm_eps_argument_in_place_and_3d(sdfl):
+    x, gamma, beta = ln_inputs(rng_for(4, 1), 2 * 64, 320, "float16")
+    x = x.reshape(2, 64, 320)
+    want = oracle.layer_norm(x.astype(np.float32), gamma, beta, 1e-3)
+    buf = to_dev(x)
+    sdfl.ops.layernorm(buf, to_dev(gamma), to_dev(beta), 1e-3, out=buf)
+    assert_close(to_np(buf), want, TOL["float16"], "in place, eps 1e-3")
+
+
+def test_layernorm_misaligned_rows(sdfl):
+    x, gamma, beta = ln_inputs(rng_for(2, 77), 16, 768, "float32")
+    want = oracle.layer_norm(x, gamma, beta, 1e-5)
+    xin = Guarded((16, 768), torch.float32, misalign=1)
+    xin.tensor.copy_(to_dev(x))
+    out = Guarded((16, 768), torch.float32, misalign=2)
+    sdfl.ops.layernorm(xin.tensor, to_dev(gamma), to_dev(beta), 1e-5, out=out.tensor)
+    out.check()
+    assert_close(to_np(out.tensor), want, 1e-5, "misaligned")
+
+
+def test_three_launch_sequence_kernel_by_kernel(sdfl):
+    """The reference's call sequence: mean, variance (both inspectable, nn/LayerNorm.cpp:
+    108-124), then layer_norm -- and the same for GroupNorm."""
+    x, gamma, beta = ln_inputs(rng_for(2, 5), 154, 768, "float32")
+    want, wmean, wvar = oracle.layer_norm(x, gamma, beta, 1e-5, return_stats=True)
+    dx = to_dev(x)
+    mean = sdfl.ops.local_reduction_mean(dx, 154)
+    var = sdfl.ops.local_reduction_variance(dx, mean, 154)
+    assert_close(to_np(mean), wmean, 1e-5, "row means")
+    assert_close(to_np(var), wvar, 1e-5, "row variances")
+    y = sdfl.ops.layer_norm_apply(dx, mean, var, to_dev(gamma), to_dev(beta), 768, 1e-5)
+    assert_close(to_np(y), want, 1e-5, "layer_norm kernel")
+
+    rng = rng_for(1, 5)
+    xg = rng.standard_normal((2, 64, 16, 16)).astype(np.float32)
+    g = (1 + 0.1 * rng.standard_normal(64)).astype(np.float32)
+    b = (0.1 * rng.standard_normal(64)).astype(np.float32)
+    wantg, gm, gv = oracle.group_norm(xg, g, b, 32, 1e-5, False, return_stats=True)
+    dxg = to_dev(xg)
+    mean = sdfl.ops.local_reduction_mean(dxg, 2 * 32)
+    var = sdfl.ops.local_reduction_variance(dxg, mean, 2 * 32)
+    assert_close(to_np(mean), gm, 1e-5, "group means")
+    assert_close(to_np(var), gv, 1e-5, "group variances")
+    y = sdfl.ops.group_norm_apply(dxg, mean, var, to_dev(g), to_dev(b), group_size=2 * 256,
+                                  channel_size=256, eps=1e-5, num_channels=64)
+    assert_close(to_np(y), wantg, 1e-5, "group_norm kernel")
+    z = sdfl.ops.silu(y, out=y)                       # silu in place, nn/ResBlock.cpp:136-137
+    assert_close(to_np(z), oracle.group_norm(xg, g, b, 32, 1e-5, True), 1e-5, "then silu")
+
+
+def test_full_size_rows_have_zero_mean_unit_variance(sdfl):
+    rows, D = 2 * 4096, 1280
+    gen = torch.Generator(device="cuda").manual_seed(4004)
+    x = (torch.randn((rows, D), device="cuda", generator=gen) * 2 + 1).half()
+    y = sdfl.ops.layernorm(x, torch.ones(D, device="cuda"), torch.zeros(D, device="cuda"), 1e-5)
+    mean = sdfl.ops.local_reduction_mean(y, rows)
+    var = sdfl.ops.local_reduction_variance(y, mean, rows)
+    assert float(mean.abs().max()) < 2e-3 and float((var - 1).abs().max()) < 5e-3
+    assert torch.equal(y, sdfl.ops.layernorm(x, torch.ones(D, device="cuda"),
+                                             torch.zeros(D, device="cuda"), 1e-5))

@@ -1,0 +1,106 @@
+"""The reference-shaped operator classes (constructor / init / forward), the host-buffer
+pipeline, the launch counter, and sharded execution equivalence on one device."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import TOL, assert_close, rng_for
+from gpu_util import gn_inputs, oracle_group_norm, to_dev, to_np
+
+import oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def test_groupnorm_operator_trio(sdfl):
+    x, gamma, beta = gn_inputs(rng_for(1, 0), (1, 320, 64, 64), "float32")
+    op = sdfl.operators.GroupNorm(32, 320, 1e-5, gamma, beta, fuse_silu=True)
+    with pytest.raises(RuntimeError):
+        op.forward(to_dev(x), to_dev(x))                      # before init()
+    op.init()
+    op.init()                                                  # idempotent, GroupNorm.cpp:52-54
+    buf = to_dev(x)
+    assert op.forward(buf, buf) == 0                           # in place, ResBlock.cpp:222
+    assert_close(to_np(buf), oracle_group_norm(x, gamma, beta, 32, 1e-5, True), 1e-5, "operator")
+    with pytest.raises(RuntimeError, match="input_size % weight->num_vals != 0"):
+        op.forward(torch.zeros((1, 64, 8, 8), device="cuda"), torch.zeros((1, 64, 8, 8), device="cuda"))
+    bad = sdfl.operators.GroupNorm(32, 320, 1e-5, gamma, beta[:100])
+    with pytest.raises(RuntimeError, match=r"weight.shape\[0\] != bias.shape\[0\]"):
+        bad.init()
+    bad = sdfl.operators.GroupNorm(32, 640, 1e-5, gamma, beta)
+    with pytest.raises(RuntimeError, match=r"weight.shape\[0\] != weightSize"):
+        bad.init()
+
+
+def test_layernorm_and_geglu_operator_trio(sdfl):
+    rng = rng_for(4, 7)
+    x = rng.standard_normal((2, 64, 320)).astype(np.float16)
+    gamma = (1 + 0.1 * rng.standard_normal(320)).astype(np.float32)
+    beta = (0.1 * rng.standard_normal(320)).astype(np.float32)
+    ln = sdfl.operators.LayerNorm(320, gamma, beta)
+    ln.init()
+    out = torch.empty((2, 64, 320), dtype=torch.float16, device="cuda")
+    assert ln.forward(to_dev(x), out) == 0
+    assert_close(to_np(out), oracle.layer_norm(x.astype(np.float32), gamma, beta), TOL["float16"], "LN op")
+    with pytest.raises(RuntimeError):
+        sdfl.operators.LayerNorm(320, gamma, beta[:10]).init()
+
+    ge = sdfl.operators.GEGLU(320, 1280)
+    ge.init()
+    assert ge.weightShape == [2560, 320]
+    ab = (rng.standard_normal((2, 64, 2560))).astype(np.float16)
+    out = torch.empty((2, 64, 1280), dtype=torch.float16, device="cuda")
+    assert ge.forward(to_dev(ab), out) == 0
+    assert_close(to_np(out), oracle.gelu_multiply(ab.astype(np.float32)), TOL["float16"], "GEGLU op")
+
+
+def test_launch_counter_counts_one_launch_for_the_fused_path(sdfl):
+    x, gamma, beta = gn_inputs(rng_for(1, 2), (2, 320, 32, 32), "float16")
+    dx, dg, db = to_dev(x), to_dev(gamma), to_dev(beta)
+    n0 = sdfl.ops.launch_count()
+    sdfl.ops.groupnorm(dx, dg, db, 32, 1e-5, True, path=sdfl.ops.GN_RESIDENT)
+    assert sdfl.ops.launch_count() - n0 == 1               # the reference needs 4 launches
+    n0 = sdfl.ops.launch_count()
+    sdfl.ops.groupnorm(dx, dg, db, 32, 1e-5, True, path=sdfl.ops.GN_SPLIT)
+    assert sdfl.ops.launch_count() - n0 == 2
+
+
+@pytest.mark.parametrize("dtype", ["float32", "float16"])
+def test_host_pipeline_matches_device_path_and_oracle(sdfl, dtype):
+    shape = (3, 64, 48, 48)
+    x, gamma, beta = gn_inputs(rng_for(5, 3), shape, dtype)
+    want = oracle_group_norm(x, gamma, beta, 32, 1e-6, True)
+    h_x = torch.from_numpy(x).pin_memory()
+    for slot_bytes, depth in ((1 << 20, 3), (20 << 10, 2), (64 << 20, 1)):
+        pipe = sdfl.ops.HostPipeline(max_slot_bytes=slot_bytes, depth=depth)
+        h_y = pipe.groupnorm(h_x, to_dev(gamma), to_dev(beta), 32, 1e-6, True)
+        pipe.close()
+        assert not h_y.is_cuda
+        assert_close(h_y.numpy(), want, TOL[dtype], f"host pipeline slot {slot_bytes}")
+    dev = sdfl.ops.groupnorm(to_dev(x), to_dev(gamma), to_dev(beta), 32, 1e-6, True)
+    assert_close(h_y.numpy(), to_np(dev), TOL[dtype], "host vs device path")
+    small = sdfl.ops.HostPipeline(max_slot_bytes=1024, depth=2)     # a group does not fit a slot
+    with pytest.raises(sdfl.SdflError) as e:
+        small.groupnorm(h_x, to_dev(gamma), to_dev(beta), 32, 1e-6, True)
+    assert e.value.status == sdfl._capi.ERR_WORKSPACE
+    small.close()
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_sharded_pieces_reproduce_the_whole_tensor(sdfl, world):
+    """What each rank of an N-GPU run computes (its pieces, as sub-tensor calls) put together
+    equals the single-call result bit for bit -- the path has no cross-unit dependence."""
+    B, C, H, G = 2, 64, 16, 32
+    x, gamma, beta = gn_inputs(rng_for(3, world), (B, C, H, H), "float16")
+    dx, dg, db = to_dev(x), to_dev(gamma), to_dev(beta)
+    whole = sdfl.ops.groupnorm(dx, dg, db, G, 1e-5, True)
+    out = torch.zeros_like(whole)
+    cpg = C // G
+    for rank in range(world):
+        pieces = sdfl.sharding.groupnorm_pieces(B, G, world, rank)
+        for first, n_img, g0, ng in sdfl.sharding.merge_whole_images(pieces, G):
+            c0, c1 = g0 * cpg, (g0 + ng) * cpg
+            sub = dx[first:first + n_img, c0:c1].contiguous()
+            y = sdfl.ops.groupnorm(sub, dg[c0:c1].contiguous(), db[c0:c1].contiguous(), ng, 1e-5, True)
+            out[first:first + n_img, c0:c1] = y
+    assert torch.equal(out, whole)
