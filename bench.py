@@ -368,7 +368,8 @@ def run_ours(args) -> None:
             plan = ops.groupnorm_plan(b_local, C, H * H, GROUPS, torch.float16)
             per_shape.append({"shape": [b_local, C, H, H], "us": round(tmed * 1e3, 2),
                               "gbs": round(nbytes / (tmed * 1e-3) / 1e9, 1),
-                              "path": plan["path"], "cluster": plan["cluster"]})
+                              "path": plan["path"], "cluster": plan["cluster"],
+                              "nclusters": plan["nclusters"], "threads": plan["threads"]})
         del flush
 
     # ---- end to end through the host-buffer C-ABI call ------------------------------------------

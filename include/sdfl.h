@@ -91,9 +91,10 @@ size_t sdfl_groupnorm_workspace_bytes_ex(int64_t batch, int64_t channels, int64_
 
 /* Which path sdfl_groupnorm_forward would take for 16-byte aligned buffers:
  * plan[0] = path, [1] = cluster size, [2] = threads per CTA, [3] = chunks per slab (split),
- * [4] = dynamic shared memory bytes per CTA, [5] = workspace bytes. */
+ * [4] = dynamic shared memory bytes per CTA, [5] = workspace bytes, [6] = persistent clusters
+ * launched (resident), [7] = 16-byte vectors per shared-memory ring chunk (resident). */
 int sdfl_groupnorm_plan(int64_t batch, int64_t channels, int64_t hw, int64_t num_groups, int dtype,
-                        int path, int cluster_or_splits, int64_t plan[6]);
+                        int path, int cluster_or_splits, int64_t plan[8]);
 
 /* LayerNorm over the last dimension of [rows, dim].
  * Replaces LayerNorm::forward (NN/LayerNorm.cpp:66-162; K/layer_norm.cl:1-78).  eps is an

@@ -136,9 +136,9 @@ int sdfl_groupnorm_forward_ex(const void *in, void *out, const float *gamma, con
 }
 
 int sdfl_groupnorm_plan(int64_t batch, int64_t channels, int64_t hw, int64_t num_groups, int dtype,
-                        int path, int cluster_or_splits, int64_t plan[6]) {
+                        int path, int cluster_or_splits, int64_t plan[8]) {
     if (!plan) return SDFL_ERR_INVALID_POINTER;
-    for (int i = 0; i < 6; ++i) plan[i] = 0;
+    for (int i = 0; i < 8; ++i) plan[i] = 0;
     if (!dtype_ok(dtype) || batch < 0 || channels <= 0 || hw < 0 || num_groups <= 0 ||
         channels % num_groups != 0 || path < SDFL_GN_AUTO || path > SDFL_GN_SPLIT ||
         cluster_or_splits < 0)
@@ -156,6 +156,7 @@ int sdfl_groupnorm_plan(int64_t batch, int64_t channels, int64_t hw, int64_t num
     if (e != cudaSuccess) return cuda_fail(e);
     plan[0] = p.path; plan[1] = p.cluster; plan[2] = p.threads; plan[3] = p.splits;
     plan[4] = static_cast<int64_t>(p.smem); plan[5] = static_cast<int64_t>(p.workspace);
+    plan[6] = p.nclusters; plan[7] = p.chunk_vecs;
     return SDFL_OK;
 }
 

@@ -8,16 +8,21 @@
 // reference: a batch dimension (slab = one (image, group) pair; weight index wraps per image)
 // and fp16 storage.
 //
-// Resident path: the slab of one (image, group) is contiguous in NCHW (C/G * H*W elements).
-// A thread-block cluster of 1..16 CTAs splits it; each CTA pulls its part into shared memory
-// with cp.async.bulk (bulk-copy engine, mbarrier completion), sums chunks as they land,
-// exchanges partial sums through distributed shared memory, takes the exact two-pass variance
-// from the resident copy, then normalises from shared memory straight to global memory.
-// Because nothing is written before the whole slab is resident, out == in is safe.
+// Resident path (gn_resident_kernel).  The slab of one (image, group) is contiguous in NCHW
+// (C/G * H*W elements).  A persistent thread-block cluster of 1..16 CTAs walks over slabs; each
+// CTA keeps its share of the current slab in shared memory as a ring of chunks:
+//   producer warp : cp.async.bulk (bulk-copy engine) global -> shared, one "full" mbarrier per
+//                   chunk; a chunk is refilled with the NEXT slab's data as soon as the consumer
+//                   warps have released it ("empty" mbarrier), so the next slab streams in
+//                   while the current one is being normalised and stored.
+//   consumer warps: (1) as chunks land, one pass of shifted sums -> per-thread (n, mean, M2),
+//                   merged with Chan's update through warp shuffles, a block merge, and a
+//                   cluster merge over distributed shared memory; (2) normalise + affine
+//                   (+ SiLU) from shared memory straight to global, 16-byte streaming stores.
+// Nothing of a slab is written before the whole slab is resident, so out == in is safe.
 //
-// Split path: any shape.  Kernel 1 writes one (mean, M2) pair per chunk to a scratch buffer
-// (per-thread shifted sums merged pairwise with Chan's update through warp shuffles and a
-// block merge); kernel 2 merges the chunk pairs of its slab in a fixed order and normalises.
+// Split path: any shape.  Kernel 1 writes one (mean, M2) pair per chunk to a scratch buffer;
+// kernel 2 merges the chunk pairs of its slab in a fixed order and normalises.
 #include "common.cuh"
 #include "kernels.h"
 
@@ -34,11 +39,11 @@ namespace {
 
 __device__ unsigned int g_gn_status;   // sticky; bit 0: a bounded mbarrier wait ran out
 
-constexpr int kResidentThreads = 512;
-constexpr int kMaxChunks = 16;
-constexpr uint32_t kHeaderBytes = 512;             // mbarriers + reduction scratch + published sums
-constexpr uint32_t kMaxPartBytes = 200 * 1024;     // per-CTA resident part (227 KB minus headroom)
+constexpr int kMaxChunks = 8;
+constexpr uint32_t kHeaderBytes = 1024;            // mbarriers, merge scratch, published moments
+constexpr uint32_t kMaxPartBytes = 226 * 1024;     // per-CTA resident part (227 KB less the header)
 constexpr long long kWaitCycles = 2000000000LL;    // ~1 s: far beyond any healthy bulk copy
+constexpr long long kWaitCyclesAfterTimeout = 2000000LL;
 
 // ---------------------------------------------------------------------------------------------
 // mbarrier / bulk-copy primitives
@@ -56,6 +61,10 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
                  : "memory");
 }
 
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
@@ -71,7 +80,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 
 // Wait for phase `parity` of `bar`, at most `limit` clock cycles.  Returns false on time-out;
-// the caller records it and carries on (every CTA must still reach the cluster barriers).
+// the caller records it and carries on (every thread must still reach the cluster barriers).
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, long long limit) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
@@ -90,147 +99,16 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_
         : "memory");
 }
 
-struct ResidentArgs {
-    const void *in;
-    void *out;
-    const float *w;
-    const float *b;
-    uint32_t slab_vecs;    // 16-byte vectors per slab
-    uint32_t slab_elems;
-    uint32_t cpg;          // channels per group
-    uint32_t groups;
-    uint32_t chunk_bytes;  // bulk-copy granule, multiple of 16
-    uint32_t vec_uniform;  // hw % lanes-per-vector == 0
-    float eps;
-    FastDiv hw_div;
-};
-
-template <typename T, int ACT>
-__global__ void __launch_bounds__(kResidentThreads)
-gn_resident_kernel(const ResidentArgs a) {
-    constexpr int VEC = VecOf<T>::N;
-    constexpr bool HALF = sizeof(T) == 2;
-    cg::cluster_group cluster = cg::this_cluster();
-    const uint32_t csize = cluster.num_blocks();
-    const uint32_t rank = cluster.block_rank();
-    const uint32_t unit = blockIdx.x / csize;
-    const uint32_t tid = threadIdx.x;
-
-    extern __shared__ __align__(128) unsigned char smem[];
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem);           // [16]
-    float *red = reinterpret_cast<float *>(smem + 128);            // [33]
-    float *pub = reinterpret_cast<float *>(smem + 320);            // [2] read by cluster peers
-    unsigned char *data = smem + kHeaderBytes;
-
-    const uint32_t v0 = static_cast<uint32_t>((static_cast<uint64_t>(a.slab_vecs) * rank) / csize);
-    const uint32_t v1 = static_cast<uint32_t>((static_cast<uint64_t>(a.slab_vecs) * (rank + 1)) / csize);
-    const uint32_t nv = v1 - v0;
-    const uint32_t part_bytes = nv * 16u;
-    const size_t part_off = (static_cast<size_t>(unit) * a.slab_vecs + v0) * 16u;
-    const unsigned char *gsrc = static_cast<const unsigned char *>(a.in) + part_off;
-    unsigned char *gdst = static_cast<unsigned char *>(a.out) + part_off;
-    const uint32_t nchunks = (part_bytes + a.chunk_bytes - 1) / a.chunk_bytes;   // <= kMaxChunks
-
-    if (tid == 0) {
-        for (uint32_t k = 0; k < nchunks; ++k) mbar_init(smem_addr(&bars[k]), 1);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    __syncthreads();
-    if (tid == 0) {
-        for (uint32_t k = 0; k < nchunks; ++k) {
-            const uint32_t off = k * a.chunk_bytes;
-            const uint32_t bytes = min(a.chunk_bytes, part_bytes - off);
-            const uint32_t bar = smem_addr(&bars[k]);
-            mbar_expect_tx(bar, bytes);
-            bulk_load(smem_addr(data + off), gsrc + off, bytes, bar);
-        }
-    }
-
-    // ---- pass 1: sum, chunk by chunk as the copies land --------------------------------------
-    const uint4 *sv = reinterpret_cast<const uint4 *>(data);
-    const uint32_t vpc = a.chunk_bytes / 16u;
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    bool timed_out = false;
-    for (uint32_t k = 0; k < nchunks; ++k) {
-        if (!mbar_wait_bounded(smem_addr(&bars[k]), 0, timed_out ? 2000000LL : kWaitCycles))
-            timed_out = true;
-        const uint32_t hi = min(nv, (k + 1) * vpc);
-        for (uint32_t i = k * vpc + tid; i < hi; i += kResidentThreads) {
-            float f[VEC];
-            unpack<T>(sv[i], f);
-#pragma unroll
-            for (int j = 0; j < VEC; ++j) acc[j & 3] += f[j];
-        }
-    }
-    if (timed_out && tid == 0) atomicOr(&g_gn_status, 1u);
-
-    float part = block_sum((acc[0] + acc[1]) + (acc[2] + acc[3]), red);
-    if (tid == 0) pub[0] = part;
-    cluster.sync();
-    float total = 0.f;
-    for (uint32_t r = 0; r < csize; ++r) total += *cluster.map_shared_rank(&pub[0], r);
-    const float mean = total / static_cast<float>(a.slab_elems);
-
-    // ---- pass 2: exact centred sum of squares from the resident copy -------------------------
-    acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
-    for (uint32_t i = tid; i < nv; i += kResidentThreads) {
-        float f[VEC];
-        unpack<T>(sv[i], f);
-#pragma unroll
-        for (int j = 0; j < VEC; ++j) {
-            const float d = f[j] - mean;
-            acc[j & 3] = fmaf(d, d, acc[j & 3]);
-        }
-    }
-    part = block_sum((acc[0] + acc[1]) + (acc[2] + acc[3]), red);
-    if (tid == 0) pub[1] = part;
-    cluster.sync();
-    total = 0.f;
-    for (uint32_t r = 0; r < csize; ++r) total += *cluster.map_shared_rank(&pub[1], r);
-    cluster.barrier_arrive();     // peers may exit only after everyone has read their sums
-    const float var = total / static_cast<float>(a.slab_elems);   // biased: group_norm.cl:53-55
-    const float rstd = 1.0f / sqrtf(var + a.eps);
-
-    // ---- pass 3: normalise + affine (+ activation) from shared memory to global --------------
-    const uint32_t ch0 = (unit % a.groups) * a.cpg;
-    uint4 *gv = reinterpret_cast<uint4 *>(gdst);
-    for (uint32_t i = tid; i < nv; i += kResidentThreads) {
-        float f[VEC];
-        unpack<T>(sv[i], f);
-        const uint32_t e = (v0 + i) * VEC;
-        if (a.vec_uniform) {
-            const uint32_t c = ch0 + a.hw_div.div(e);
-            const float wv = __ldg(a.w + c), bv = __ldg(a.b + c);
-            if (HALF) {
-                const float sc = wv * rstd;
-                const float sh = fmaf(-mean, sc, bv);
-#pragma unroll
-                for (int j = 0; j < VEC; ++j) f[j] = activate<ACT, HALF>(fmaf(f[j], sc, sh));
-            } else {
-#pragma unroll
-                for (int j = 0; j < VEC; ++j)
-                    f[j] = activate<ACT, HALF>(fmaf((f[j] - mean) * rstd, wv, bv));
-            }
-        } else {
-#pragma unroll
-            for (int j = 0; j < VEC; ++j) {
-                const uint32_t c = ch0 + a.hw_div.div(e + j);
-                f[j] = activate<ACT, HALF>(fmaf((f[j] - mean) * rstd, __ldg(a.w + c), __ldg(a.b + c)));
-            }
-        }
-        st_stream(&gv[i], pack<T>(f));
-    }
-    cluster.barrier_wait();
+// Barrier among the consumer warps only (the producer warp never joins it).
+__device__ __forceinline__ void consumer_sync(uint32_t consumers) {
+    asm volatile("bar.sync 1, %0;" ::"r"(consumers) : "memory");
 }
 
 // ---------------------------------------------------------------------------------------------
-// Split path
+// Moments: (count, mean, sum of squared deviations) with Chan et al.'s pairwise update
 // ---------------------------------------------------------------------------------------------
-constexpr int kSplitThreads = 512;
-
 struct Moments { float n, mean, m2; };
 
-// Chan et al. pairwise update of (count, mean, sum of squared deviations).
 __device__ __forceinline__ Moments merge(const Moments &x, const Moments &y) {
     if (y.n == 0.f) return x;
     if (x.n == 0.f) return y;
@@ -255,22 +133,6 @@ __device__ __forceinline__ Moments warp_merge(Moments m) {
     return m;   // valid in lane 0
 }
 
-struct SplitArgs {
-    const void *in;
-    void *out;
-    const float *w;
-    const float *b;
-    float *partial;        // [units * splits * 2]  (mean, M2) per chunk
-    uint32_t slab_elems;
-    uint32_t chunk_elems;  // multiple of the vector width when `vec` is set
-    uint32_t splits;
-    uint32_t cpg, groups;
-    uint32_t vec;          // 16-byte accesses allowed (alignment and divisibility hold)
-    uint32_t vec_uniform;  // and a vector never straddles a channel
-    float eps;
-    FastDiv hw_div;
-};
-
 // Shifted single-pass moments of a thread's elements: d = x - first, sum d and d*d.
 struct Shifted {
     float k, s, q, n;
@@ -288,6 +150,228 @@ struct Shifted {
         m.m2 = n > 0.f ? fmaxf(q - s * s / n, 0.f) : 0.f;
         return m;
     }
+};
+
+struct ResidentArgs {
+    const void *in;
+    void *out;
+    const float *w;
+    const float *b;
+    uint32_t units;        // slabs = batch * groups
+    uint32_t slab_vecs;    // 16-byte vectors per slab
+    uint32_t slab_elems;
+    uint32_t cpg;          // channels per group
+    uint32_t groups;
+    uint32_t chunk_vecs;   // vectors per ring chunk
+    uint32_t vec_uniform;  // hw % lanes-per-vector == 0
+    float eps;
+    FastDiv hw_div;
+};
+
+// blockDim.x = consumer threads (a multiple of 32) + one producer warp.  BIG: one CTA of up to
+// 1024 threads per SM (parts beyond ~100 KB); otherwise up to 512 threads and at least three
+// CTAs per SM, which caps the kernel at 40 registers per thread.
+template <typename T, int ACT, bool BIG>
+__global__ void __launch_bounds__(BIG ? 1024 : 512, BIG ? 1 : 3)
+gn_resident_kernel(const ResidentArgs a) {
+    constexpr int VEC = VecOf<T>::N;
+    constexpr bool HALF = sizeof(T) == 2;
+    cg::cluster_group cluster = cg::this_cluster();
+    const uint32_t csize = cluster.num_blocks();
+    const uint32_t rank = cluster.block_rank();
+    const uint32_t cluster_id = blockIdx.x / csize;
+    const uint32_t nclusters = gridDim.x / csize;
+    const uint32_t tid = threadIdx.x;
+    const uint32_t lane = tid & 31u, warp = tid >> 5;
+    const uint32_t consumers = blockDim.x - 32u;
+    const uint32_t cwarps = consumers >> 5;
+
+    extern __shared__ __align__(128) unsigned char smem[];
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem);                  // [kMaxChunks]
+    uint64_t *empty = reinterpret_cast<uint64_t *>(smem + 64);            // [kMaxChunks]
+    Moments *warp_m = reinterpret_cast<Moments *>(smem + 128);            // [31]
+    float *bcast = reinterpret_cast<float *>(smem + 512);                 // mean, rstd
+    float *pub = reinterpret_cast<float *>(smem + 576);                   // [2][2] read by peers
+    unsigned char *data = smem + kHeaderBytes;
+
+    // This CTA's share of every slab: vectors [v0, v0 + nv).
+    const uint32_t v0 = static_cast<uint32_t>((static_cast<uint64_t>(a.slab_vecs) * rank) / csize);
+    const uint32_t v1 = static_cast<uint32_t>((static_cast<uint64_t>(a.slab_vecs) * (rank + 1)) / csize);
+    const uint32_t nv = v1 - v0;
+    const uint32_t nchunks = (nv + a.chunk_vecs - 1) / a.chunk_vecs;      // <= kMaxChunks
+
+    if (tid == 0) {
+        for (uint32_t k = 0; k < nchunks; ++k) {
+            mbar_init(smem_addr(&full[k]), 1);
+            mbar_init(smem_addr(&empty[k]), cwarps);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    if (warp == cwarps) {
+        // ---------------- producer warp ----------------------------------------------------------
+        bool timed_out = false;
+        uint32_t it = 0;
+        for (uint32_t unit = cluster_id; unit < a.units; unit += nclusters, ++it) {
+            // The consumers pass one cluster barrier per slab, between reading and releasing
+            // its chunks; join that barrier first, or the empties below could never come.
+            if (it > 0) cluster.sync();
+            if (lane == 0) {
+                const unsigned char *gsrc = static_cast<const unsigned char *>(a.in) +
+                                            (static_cast<size_t>(unit) * a.slab_vecs + v0) * 16u;
+                for (uint32_t k = 0; k < nchunks; ++k) {
+                    if (it > 0) {      // chunk k of the previous slab must have been released
+                        if (!mbar_wait_bounded(smem_addr(&empty[k]), (it - 1) & 1u,
+                                               timed_out ? kWaitCyclesAfterTimeout : kWaitCycles))
+                            timed_out = true;
+                    }
+                    const uint32_t lo = k * a.chunk_vecs;
+                    const uint32_t bytes = (min(nv, lo + a.chunk_vecs) - lo) * 16u;
+                    const uint32_t bar = smem_addr(&full[k]);
+                    mbar_expect_tx(bar, bytes);
+                    bulk_load(smem_addr(data + lo * 16u), gsrc + lo * 16u, bytes, bar);
+                }
+            }
+            __syncwarp();
+        }
+        if (it > 0) cluster.sync();          // the consumers' barrier of the last slab
+        if (timed_out && lane == 0) atomicOr(&g_gn_status, 1u);
+        cluster.sync();                      // nobody leaves while peers may read its moments
+        return;
+    }
+
+    // ---------------- consumer warps -------------------------------------------------------------
+    const uint4 *sv = reinterpret_cast<const uint4 *>(data);
+    const float part_elems = static_cast<float>(nv) * VEC;
+    bool timed_out = false;
+    uint32_t it = 0;
+    for (uint32_t unit = cluster_id; unit < a.units; unit += nclusters, ++it) {
+        const uint32_t par = it & 1u;
+
+        // pass 1: shifted sums, chunk by chunk as the copies land
+        float s0 = 0.f, s1 = 0.f, q0 = 0.f, q1 = 0.f, shift = 0.f, cnt = 0.f;
+        for (uint32_t k = 0; k < nchunks; ++k) {
+            if (!mbar_wait_bounded(smem_addr(&full[k]), par,
+                                   timed_out ? kWaitCyclesAfterTimeout : kWaitCycles))
+                timed_out = true;
+            if (k == 0) shift = to_float<T>(reinterpret_cast<const T *>(data)[0]);
+            const uint32_t hi = min(nv, (k + 1) * a.chunk_vecs);
+            for (uint32_t i = k * a.chunk_vecs + tid; i < hi; i += consumers) {
+                float f[VEC];
+                unpack<T>(sv[i], f);
+#pragma unroll
+                for (int j = 0; j < VEC; j += 2) {
+                    const float d0 = f[j] - shift, d1 = f[j + 1] - shift;
+                    s0 += d0;
+                    s1 += d1;
+                    q0 = fmaf(d0, d0, q0);
+                    q1 = fmaf(d1, d1, q1);
+                }
+                cnt += static_cast<float>(VEC);
+            }
+        }
+        Moments m;
+        {
+            const float s = s0 + s1, q = q0 + q1;
+            m.n = cnt;
+            m.mean = cnt > 0.f ? shift + s / cnt : 0.f;
+            m.m2 = cnt > 0.f ? fmaxf(q - s * s / cnt, 0.f) : 0.f;
+        }
+        m = warp_merge(m);
+        if (lane == 0) warp_m[warp] = m;
+        consumer_sync(consumers);
+        if (warp == 0) {
+            Moments t = lane < cwarps ? warp_m[lane] : Moments{0.f, 0.f, 0.f};
+            t = warp_merge(t);
+            if (lane == 0) {
+                pub[2 * par] = t.mean;
+                pub[2 * par + 1] = t.m2;
+            }
+        }
+        cluster.sync();                       // every CTA's moments of this slab are published
+        if (warp == 0) {
+            Moments t{0.f, 0.f, 0.f};
+            if (lane < csize) {
+                const float *peer = cluster.map_shared_rank(pub, lane);
+                const uint32_t p0 = static_cast<uint32_t>((static_cast<uint64_t>(a.slab_vecs) * lane) / csize);
+                const uint32_t p1 = static_cast<uint32_t>((static_cast<uint64_t>(a.slab_vecs) * (lane + 1)) / csize);
+                t.n = static_cast<float>(p1 - p0) * VEC;
+                t.mean = peer[2 * par];
+                t.m2 = peer[2 * par + 1];
+            }
+            t = warp_merge(t);
+            if (lane == 0) {
+                const float var = t.m2 / static_cast<float>(a.slab_elems);   // biased: group_norm.cl:53-55
+                bcast[0] = t.mean;
+                bcast[1] = 1.0f / sqrtf(var + a.eps);
+            }
+        }
+        consumer_sync(consumers);
+        const float mean = bcast[0], rstd = bcast[1];
+        (void)part_elems;
+
+        // pass 2: normalise + affine (+ activation) from shared memory to global; each chunk is
+        // handed back to the producer as soon as this warp is done with it
+        const uint32_t ch0 = (unit % a.groups) * a.cpg;
+        uint4 *gv = reinterpret_cast<uint4 *>(static_cast<unsigned char *>(a.out) +
+                                              (static_cast<size_t>(unit) * a.slab_vecs + v0) * 16u);
+        for (uint32_t k = 0; k < nchunks; ++k) {
+            const uint32_t hi = min(nv, (k + 1) * a.chunk_vecs);
+            for (uint32_t i = k * a.chunk_vecs + tid; i < hi; i += consumers) {
+                float f[VEC];
+                unpack<T>(sv[i], f);
+                const uint32_t e = (v0 + i) * VEC;
+                if (a.vec_uniform) {
+                    const uint32_t c = ch0 + a.hw_div.div(e);
+                    const float wv = __ldg(a.w + c), bv = __ldg(a.b + c);
+                    if (HALF) {
+                        const float sc = wv * rstd;
+                        const float sh = fmaf(-mean, sc, bv);
+#pragma unroll
+                        for (int j = 0; j < VEC; ++j) f[j] = activate<ACT, HALF>(fmaf(f[j], sc, sh));
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < VEC; ++j)
+                            f[j] = activate<ACT, HALF>(fmaf((f[j] - mean) * rstd, wv, bv));
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < VEC; ++j) {
+                        const uint32_t c = ch0 + a.hw_div.div(e + j);
+                        f[j] = activate<ACT, HALF>(
+                            fmaf((f[j] - mean) * rstd, __ldg(a.w + c), __ldg(a.b + c)));
+                    }
+                }
+                st_stream(&gv[i], pack<T>(f));
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_addr(&empty[k]));
+        }
+    }
+    if (timed_out && lane == 0) atomicOr(&g_gn_status, 1u);
+    cluster.sync();                           // nobody leaves while peers may read its moments
+}
+
+// ---------------------------------------------------------------------------------------------
+// Split path
+// ---------------------------------------------------------------------------------------------
+constexpr int kSplitThreads = 512;
+
+struct SplitArgs {
+    const void *in;
+    void *out;
+    const float *w;
+    const float *b;
+    float *partial;        // [units * splits * 2]  (mean, M2) per chunk
+    uint32_t slab_elems;
+    uint32_t chunk_elems;  // multiple of the vector width when `vec` is set
+    uint32_t splits;
+    uint32_t cpg, groups;
+    uint32_t vec;          // 16-byte accesses allowed (alignment and divisibility hold)
+    uint32_t vec_uniform;  // and a vector never straddles a channel
+    float eps;
+    FastDiv hw_div;
 };
 
 template <typename T>
@@ -452,24 +536,18 @@ __global__ void ln_apply_kernel(const T *__restrict__ in, const float *__restric
 
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-inline int pow2_at_least(double x) {
-    int c = 1;
-    while (c < x) c <<= 1;
-    return c;
-}
-
 // Per-device, per-kernel-instance one-time attribute set-up (maximum dynamic shared memory and
 // the opt-in for 16-CTA clusters), so that launches themselves make no attribute calls.
 constexpr int kMaxDevices = 64;
 
-template <typename T, int ACT>
+template <typename T, int ACT, bool BIG>
 cudaError_t ensure_resident_attrs() {
     static std::atomic<bool> done[kMaxDevices];
     int dev = 0;
     cudaError_t err = cudaGetDevice(&dev);
     if (err != cudaSuccess) return err;
     if (dev >= 0 && dev < kMaxDevices && done[dev].load(std::memory_order_acquire)) return cudaSuccess;
-    auto kernel = gn_resident_kernel<T, ACT>;
+    auto kernel = gn_resident_kernel<T, ACT, BIG>;
     err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                static_cast<int>(kHeaderBytes + kMaxPartBytes));
     if (err != cudaSuccess) return err;
@@ -480,10 +558,10 @@ cudaError_t ensure_resident_attrs() {
 }
 
 inline void cluster_config(cudaLaunchConfig_t *cfg, cudaLaunchAttribute *attr, unsigned grid,
-                           int cluster, size_t smem, cudaStream_t stream) {
+                           int cluster, int threads, size_t smem, cudaStream_t stream) {
     *cfg = cudaLaunchConfig_t{};
     cfg->gridDim = dim3(grid);
-    cfg->blockDim = dim3(kResidentThreads);
+    cfg->blockDim = dim3(static_cast<unsigned>(threads));
     cfg->dynamicSmemBytes = smem;
     cfg->stream = stream;
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -494,50 +572,70 @@ inline void cluster_config(cudaLaunchConfig_t *cfg, cudaLaunchAttribute *attr, u
     cfg->numAttrs = 1;
 }
 
-template <typename T, int ACT>
-cudaError_t launch_resident(const ResidentArgs &a, int64_t units, const GnPlan &plan,
-                            cudaStream_t stream) {
-    cudaError_t err = ensure_resident_attrs<T, ACT>();
+template <typename T, int ACT, bool BIG>
+cudaError_t launch_resident_as(const ResidentArgs &a, const GnPlan &plan, cudaStream_t stream) {
+    cudaError_t err = ensure_resident_attrs<T, ACT, BIG>();
     if (err != cudaSuccess) return err;
     cudaLaunchConfig_t cfg;
     cudaLaunchAttribute attr[1];
-    cluster_config(&cfg, attr, static_cast<unsigned>(units * plan.cluster), plan.cluster, plan.smem,
-                   stream);
-    err = cudaLaunchKernelEx(&cfg, gn_resident_kernel<T, ACT>, a);
+    cluster_config(&cfg, attr, static_cast<unsigned>(plan.nclusters * plan.cluster), plan.cluster,
+                   plan.threads, plan.smem, stream);
+    err = cudaLaunchKernelEx(&cfg, gn_resident_kernel<T, ACT, BIG>, a);
     if (err == cudaSuccess) g_launches.fetch_add(1);
     return err;
 }
 
-// Can at least one cluster of this size and shared-memory footprint be resident (a 16-CTA
-// cluster needs a GPC with 16 free SMs)?  Asked of the driver once per (device, dtype,
-// cluster, shared-memory size in KiB) and remembered.
+template <typename T, int ACT>
+cudaError_t launch_resident(const ResidentArgs &a, const GnPlan &plan, cudaStream_t stream) {
+    return plan.threads > 512 ? launch_resident_as<T, ACT, true>(a, plan, stream)
+                              : launch_resident_as<T, ACT, false>(a, plan, stream);
+}
+
+// How many clusters of this size, block size and shared-memory footprint can be resident at
+// once (a cluster must fit inside one GPC).  Asked of the driver once per (device, dtype,
+// cluster, threads, shared-memory size in KiB) and remembered.
 template <typename T>
-cudaError_t resident_clusters_fit(const GnPlan &plan, int *fits) {
+cudaError_t resident_active_clusters(int cluster, int threads, size_t smem, int *active) {
     static std::mutex mu;
     static std::map<uint64_t, int> cache;
     int dev = 0;
     cudaError_t err = cudaGetDevice(&dev);
     if (err != cudaSuccess) return err;
-    const uint64_t key = (static_cast<uint64_t>(dev) << 40) | (static_cast<uint64_t>(sizeof(T)) << 32) |
-                         (static_cast<uint64_t>(plan.cluster) << 24) | ((plan.smem + 1023) / 1024);
+    const uint64_t kb = (smem + 1023) / 1024;
+    const uint64_t key = (static_cast<uint64_t>(dev) << 48) | (static_cast<uint64_t>(sizeof(T)) << 40) |
+                         (static_cast<uint64_t>(cluster) << 32) |
+                         (static_cast<uint64_t>(threads) << 16) | kb;
     {
         std::lock_guard<std::mutex> lock(mu);
         auto it = cache.find(key);
-        if (it != cache.end()) { *fits = it->second; return cudaSuccess; }
+        if (it != cache.end()) { *active = it->second; return cudaSuccess; }
     }
-    err = ensure_resident_attrs<T, kActSilu>();
+    err = threads > 512 ? ensure_resident_attrs<T, kActSilu, true>()
+                        : ensure_resident_attrs<T, kActSilu, false>();
     if (err != cudaSuccess) return err;
     cudaLaunchConfig_t cfg;
     cudaLaunchAttribute attr[1];
-    cluster_config(&cfg, attr, static_cast<unsigned>(plan.cluster), plan.cluster,
-                   ((plan.smem + 1023) / 1024) * 1024, nullptr);
+    cluster_config(&cfg, attr, static_cast<unsigned>(cluster), cluster, threads, smem, nullptr);
     int n = 0;
-    err = cudaOccupancyMaxActiveClusters(&n, gn_resident_kernel<T, kActSilu>, &cfg);
+    err = threads > 512
+              ? cudaOccupancyMaxActiveClusters(&n, gn_resident_kernel<T, kActSilu, true>, &cfg)
+              : cudaOccupancyMaxActiveClusters(&n, gn_resident_kernel<T, kActSilu, false>, &cfg);
     if (err != cudaSuccess) return err;
-    *fits = n;
+    *active = n;
     std::lock_guard<std::mutex> lock(mu);
     cache[key] = n;
     return cudaSuccess;
+}
+
+constexpr int kSmCount = 148;
+
+// Consumer threads for a resident part of this size: enough warps to keep the SM's issue
+// slots and shared-memory ports busy at the number of CTAs that will share the SM.
+inline int consumers_for(int64_t part_bytes) {
+    if (part_bytes > 100 * 1024) return 992;    // one CTA per SM: 31 + 1 warps
+    if (part_bytes > 40 * 1024) return 480;     // two or three per SM: 15 + 1 warps
+    if (part_bytes > 12 * 1024) return 224;     // 7 + 1 warps
+    return 96;                                  // 3 + 1 warps
 }
 
 }  // namespace
@@ -554,39 +652,58 @@ cudaError_t gn_make_plan(const GnShape &s, const void *in, const void *out, int 
     const int64_t slab_bytes = slab_elems * esz;
     const int64_t units = s.batch * s.groups;
     *plan = GnPlan{};
-    plan->threads = kResidentThreads;
 
     bool resident_ok = aligned16(in) && aligned16(out) && slab_bytes % 16 == 0 && slab_bytes >= 16 &&
                        slab_bytes <= 16 * static_cast<int64_t>(kMaxPartBytes) &&
-                       units * 16 < (1ll << 31);
+                       units < (1ll << 27);
     if (force_path == kGnSplit) resident_ok = false;
 
     if (resident_ok) {
-        const double sb = static_cast<double>(slab_bytes);
-        int c_min = pow2_at_least(sb / kMaxPartBytes);             // must fit
-        int c_occ = pow2_at_least(sb / (72.0 * 1024.0));           // three CTAs per SM
-        int c_fill = pow2_at_least(296.0 / static_cast<double>(units));   // two waves of 148 SMs
-        int c_cap = 1;                                              // parts of at least 8 KB
-        while (c_cap < 16 && sb / (2.0 * c_cap) >= 8192.0) c_cap <<= 1;
-        int c = c_occ > c_fill ? c_occ : c_fill;
-        if (c > c_cap) c = c_cap;
-        if (c > 8 && c_min <= 8) c = 8;      // keep to portable cluster sizes unless forced by size
-        if (c < c_min) c = c_min;
-        if (c > 16) c = 16;
-        if (force_cluster > 0) c = force_cluster;
+        // Try every cluster size; score = how evenly the slabs spread over the SMs (work is
+        // quantised: `waves` slabs per cluster, whole CTAs per SM) times small factors for
+        // having several CTAs per SM (their load and store phases overlap) and for the cost of
+        // the cluster exchange.  The driver says how many such clusters can be co-resident.
         const int64_t slab_vecs = slab_bytes / 16;
-        if (c > slab_vecs) c = 1;
-        const int64_t max_part = ((slab_vecs + c - 1) / c) * 16;
-        if (max_part <= kMaxPartBytes && c >= 1 && c <= 16 && (c & (c - 1)) == 0) {
-            plan->path = kGnResident;
-            plan->cluster = c;
-            plan->smem = kHeaderBytes + static_cast<size_t>(max_part);
-            int fits = 0;
-            cudaError_t err = s.dtype == kF16 ? resident_clusters_fit<__half>(*plan, &fits)
-                                              : resident_clusters_fit<float>(*plan, &fits);
-            if (err != cudaSuccess) { (void)cudaGetLastError(); fits = 0; }
-            if (fits > 0) return cudaSuccess;
+        double best = -1.0;
+        for (int c = 1; c <= 16; ++c) {
+            if (force_cluster > 0 && c != force_cluster) continue;
+            if (c > slab_vecs) break;
+            const int64_t part_bytes = ((slab_vecs + c - 1) / c) * 16;
+            if (part_bytes > kMaxPartBytes) continue;
+            const int consumers = consumers_for(part_bytes);
+            const int threads = consumers + 32;
+            const size_t smem = kHeaderBytes + static_cast<size_t>(part_bytes);
+            int active = 0;
+            cudaError_t err = s.dtype == kF16
+                                  ? resident_active_clusters<__half>(c, threads, smem, &active)
+                                  : resident_active_clusters<float>(c, threads, smem, &active);
+            if (err != cudaSuccess) { (void)cudaGetLastError(); active = 0; }
+            if (active <= 0) continue;
+            const int64_t waves = (units + active - 1) / active;
+            const int64_t nclusters = (units + waves - 1) / waves;
+            const int64_t per_sm = (nclusters * c + kSmCount - 1) / kSmCount;
+            double score = static_cast<double>(units) * c /
+                           (static_cast<double>(kSmCount) * waves * per_sm);
+            if (score > 1.0) score = 1.0;
+            if (static_cast<double>(active) * c / kSmCount < 2.0) score *= 0.92;
+            if (part_bytes < 16 * 1024) score *= 0.9;
+            if (c > 1) score *= 0.99;
+            if (c > 8) score *= 0.98;
+            if (score > best) {
+                best = score;
+                plan->path = kGnResident;
+                plan->cluster = c;
+                plan->threads = threads;
+                plan->smem = smem;
+                plan->nclusters = static_cast<int>(nclusters);
+                // four ring chunks per part (at least 4 KB each)
+                int64_t part_vecs = part_bytes / 16;
+                int64_t chunk = (part_vecs + 3) / 4;
+                if (chunk < 256) chunk = 256;
+                plan->chunk_vecs = static_cast<int>(chunk);
+            }
         }
+        if (best > 0.0) return cudaSuccess;
         if (force_path == kGnResident) return cudaErrorInvalidConfiguration;
     } else if (force_path == kGnResident) {
         return cudaErrorInvalidConfiguration;
@@ -625,22 +742,20 @@ cudaError_t gn_launch(const GnShape &s, const GnPlan &plan, const void *in, void
     if (plan.path == kGnResident) {
         ResidentArgs a;
         a.in = in; a.out = out; a.w = w; a.b = b;
+        a.units = static_cast<uint32_t>(units);
         a.slab_vecs = static_cast<uint32_t>(slab_elems * esz / 16);
         a.slab_elems = static_cast<uint32_t>(slab_elems);
         a.cpg = static_cast<uint32_t>(cpg);
         a.groups = static_cast<uint32_t>(s.groups);
-        const uint32_t max_part = static_cast<uint32_t>(plan.smem - kHeaderBytes);
-        uint32_t chunk = 16 * 1024;
-        while ((max_part + chunk - 1) / chunk > kMaxChunks) chunk *= 2;
-        a.chunk_bytes = chunk;
+        a.chunk_vecs = static_cast<uint32_t>(plan.chunk_vecs);
         a.vec_uniform = s.hw % vec == 0;
         a.eps = s.eps;
         a.hw_div = FastDiv::make(static_cast<uint32_t>(s.hw));
         if (s.dtype == kF16)
-            return s.act == kActSilu ? launch_resident<__half, kActSilu>(a, units, plan, stream)
-                                     : launch_resident<__half, kActNone>(a, units, plan, stream);
-        return s.act == kActSilu ? launch_resident<float, kActSilu>(a, units, plan, stream)
-                                 : launch_resident<float, kActNone>(a, units, plan, stream);
+            return s.act == kActSilu ? launch_resident<__half, kActSilu>(a, plan, stream)
+                                     : launch_resident<__half, kActNone>(a, plan, stream);
+        return s.act == kActSilu ? launch_resident<float, kActSilu>(a, plan, stream)
+                                 : launch_resident<float, kActNone>(a, plan, stream);
     }
 
     if (workspace == nullptr) return cudaErrorInvalidValue;

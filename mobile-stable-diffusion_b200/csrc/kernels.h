@@ -23,8 +23,10 @@ enum GnPath : int { kGnAuto = 0, kGnResident = 1, kGnSplit = 2 };
 
 struct GnPlan {
     int path;          // kGnResident or kGnSplit
-    int cluster;       // CTAs per slab (resident) -- 1,2,4,8,16
-    int threads;       // threads per CTA
+    int cluster;       // CTAs per slab (resident): 1..16
+    int threads;       // threads per CTA (resident: consumer warps + one producer warp)
+    int nclusters;     // persistent clusters launched (resident)
+    int chunk_vecs;    // 16-byte vectors per shared-memory ring chunk (resident)
     int splits;        // chunks per slab (split path)
     size_t smem;       // dynamic shared memory per CTA (resident)
     size_t workspace;  // scratch bytes the split path needs

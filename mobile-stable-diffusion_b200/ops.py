@@ -73,11 +73,11 @@ def device_status(clear: bool = True, stream=None) -> int:
 
 def groupnorm_plan(batch: int, channels: int, hw: int, num_groups: int, dtype: torch.dtype,
                    path: int = GN_AUTO, cluster_or_splits: int = 0) -> dict:
-    arr = (C.c_int64 * 6)()
+    arr = (C.c_int64 * 8)()
     code = F16 if dtype == torch.float16 else F32
     check(lib.sdfl_groupnorm_plan(batch, channels, hw, num_groups, code, path, cluster_or_splits,
                                   arr), "sdfl_groupnorm_plan")
-    keys = ("path", "cluster", "threads", "splits", "smem", "workspace")
+    keys = ("path", "cluster", "threads", "splits", "smem", "workspace", "nclusters", "chunk_vecs")
     return dict(zip(keys, (int(v) for v in arr)))
 
 
@@ -87,6 +87,7 @@ def groupnorm(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor, num_grou
     """GroupNorm(+SiLU) on an NCHW tensor [B, C, ...]; out may be x itself."""
     if x.dim() < 2:
         raise ValueError("x must be [batch, channels, ...]")
+    _dev(x, "x")
     out = torch.empty_like(x) if out is None else out
     if out.shape != x.shape or out.dtype != x.dtype:
         raise ValueError("out must match x in shape and dtype")

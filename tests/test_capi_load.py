@@ -71,7 +71,7 @@ def test_workspace_query_and_plan_without_device():
     n = lib.sdfl_groupnorm_workspace_bytes(8, 128, 512 * 512, 32, 1)
     assert n > 0 and n % 8 == 0
     assert lib.sdfl_groupnorm_workspace_bytes(8, 130, 64, 32, 1) == 0     # invalid shape
-    plan = (C.c_int64 * 6)()
+    plan = (C.c_int64 * 8)()
     assert lib.sdfl_groupnorm_plan(2, 30, 64, 32, 0, 0, 0, plan) == cap.ERR_INVALID_VALUE
 
 

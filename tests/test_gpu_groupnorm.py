@@ -34,13 +34,13 @@ def test_config1_fp32_every_path_and_cluster_size(sdfl):
     plan = sdfl.ops.groupnorm_plan(1, 320, 4096, 32, torch.float32)
     assert plan["path"] == sdfl.ops.GN_RESIDENT and plan["workspace"] == 0
     assert_close(run_gn(sdfl, x, gamma, beta, 32, 1e-5, True), want, 1e-5, "auto")
-    for cluster in (1, 2, 4, 8, 16):
+    for cluster in (1, 2, 3, 4, 5, 7, 8, 12, 16):
         try:
             got = run_gn(sdfl, x, gamma, beta, 32, 1e-5, True, path=sdfl.ops.GN_RESIDENT,
                          cluster_or_splits=cluster)
         except sdfl.SdflError as e:
             # a 16-CTA cluster is an opt-in size: the device may not be able to host one
-            assert cluster == 16 and e.status == sdfl._capi.ERR_UNSUPPORTED
+            assert cluster > 8 and e.status == sdfl._capi.ERR_UNSUPPORTED
             continue
         assert_close(got, want, 1e-5, f"resident cluster {cluster}")
     for splits in (0, 1, 3, 8):
