@@ -39,7 +39,7 @@ namespace {
 
 __device__ unsigned int g_gn_status;   // sticky; bit 0: a bounded mbarrier wait ran out
 
-constexpr int kMaxChunks = 8;
+constexpr int kMaxSlots = 16;
 constexpr uint32_t kHeaderBytes = 1024;            // mbarriers, merge scratch, published moments
 constexpr uint32_t kMaxPartBytes = 226 * 1024;     // per-CTA resident part (227 KB less the header)
 constexpr long long kWaitCycles = 2000000000LL;    // ~1 s: far beyond any healthy bulk copy
@@ -99,6 +99,29 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_
         : "memory");
 }
 
+// Same with an L2 eviction-priority hint: evict_last for data that will be read again soon
+// (the first read of the re-read mode), evict_first for data that is dead after this read.
+__device__ __forceinline__ void bulk_load_hint(uint32_t dst, const void *src, uint32_t bytes,
+                                               uint32_t bar, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint "
+        "[%0], [%1], %2, [%3], %4;"
+        ::"r"(dst), "l"(src), "r"(bytes), "r"(bar), "l"(policy)
+        : "memory");
+}
+
+__device__ __forceinline__ uint64_t policy_evict_last() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+
+__device__ __forceinline__ uint64_t policy_evict_first() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+
 // Barrier among the consumer warps only (the producer warp never joins it).
 __device__ __forceinline__ void consumer_sync(uint32_t consumers) {
     asm volatile("bar.sync 1, %0;" ::"r"(consumers) : "memory");
@@ -152,6 +175,96 @@ struct Shifted {
     }
 };
 
+// ---------------------------------------------------------------------------------------------
+// Per-vector work of the resident kernel
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ float tanh_approx(float x) {
+    float y;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// s += x - shift, q += (x - shift)^2 over the lanes of one 16-byte vector.
+template <typename T>
+__device__ __forceinline__ void stats_vec(const uint4 &v, float shift, float (&s)[2], float (&q)[2]);
+
+template <>
+__device__ __forceinline__ void stats_vec<float>(const uint4 &v, float shift, float (&s)[2], float (&q)[2]) {
+    const float d0 = __uint_as_float(v.x) - shift, d1 = __uint_as_float(v.y) - shift;
+    const float d2 = __uint_as_float(v.z) - shift, d3 = __uint_as_float(v.w) - shift;
+    s[0] += d0; s[1] += d1; s[0] += d2; s[1] += d3;
+    q[0] = fmaf(d0, d0, q[0]); q[1] = fmaf(d1, d1, q[1]);
+    q[0] = fmaf(d2, d2, q[0]); q[1] = fmaf(d3, d3, q[1]);
+}
+
+// fp16 lanes: the mixed-precision subtract (f16 operand, f32 result) widens and shifts in one
+// instruction, so a lane costs three instructions instead of four.
+__device__ __forceinline__ void stats_half2(uint32_t packed, float shift, float (&s)[2], float (&q)[2]) {
+    asm("{\n"
+        " .reg .b16 lo, hi;\n"
+        " .reg .f32 d0, d1;\n"
+        " mov.b32 {lo, hi}, %4;\n"
+        " sub.rn.f32.f16 d0, lo, %5;\n"
+        " sub.rn.f32.f16 d1, hi, %5;\n"
+        " add.rn.f32 %0, %0, d0;\n"
+        " add.rn.f32 %1, %1, d1;\n"
+        " fma.rn.f32 %2, d0, d0, %2;\n"
+        " fma.rn.f32 %3, d1, d1, %3;\n"
+        "}\n"
+        : "+f"(s[0]), "+f"(s[1]), "+f"(q[0]), "+f"(q[1])
+        : "r"(packed), "f"(shift));
+}
+
+template <>
+__device__ __forceinline__ void stats_vec<__half>(const uint4 &v, float shift, float (&s)[2], float (&q)[2]) {
+    stats_half2(v.x, shift, s, q);
+    stats_half2(v.y, shift, s, q);
+    stats_half2(v.z, shift, s, q);
+    stats_half2(v.w, shift, s, q);
+}
+
+// Per-channel constants of the normalise pass.
+//   fp32 storage: the reference's operation order, y = fma((x - mean) * rstd, w, b).
+//   fp16 storage: folded, y = fma(x, sc, sh) with sc = w * rstd, sh = b - mean * sc; with SiLU
+//   the fold goes one step further to h = y / 2, because silu(y) = h + h * tanh(h) needs one
+//   SFU operation where y / (1 + exp(-y)) needs two.  tanh.approx on h keeps the fp16 result
+//   within a quarter of the 2e-3 tolerance over the whole range (the error is dominated by
+//   the final fp16 rounding).
+template <typename T> struct Affine { float p0, p1, p2, p3; };
+
+template <typename T, int ACT>
+__device__ __forceinline__ Affine<T> make_affine(float mean, float rstd, float w, float b) {
+    Affine<T> a;
+    if (sizeof(T) == 2) {
+        const float sc = w * rstd;
+        const float sh = fmaf(-mean, sc, b);
+        const float half = ACT == kActSilu ? 0.5f : 1.0f;
+        a.p0 = sc * half; a.p1 = sh * half; a.p2 = 0.f; a.p3 = 0.f;
+    } else {
+        a.p0 = mean; a.p1 = rstd; a.p2 = w; a.p3 = b;
+    }
+    return a;
+}
+
+template <typename T, int ACT>
+__device__ __forceinline__ uint4 norm_vec(const uint4 &v, const Affine<T> &a) {
+    constexpr int VEC = VecOf<T>::N;
+    float f[VEC];
+    unpack<T>(v, f);
+    if (sizeof(T) == 2) {
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) {
+            const float h = fmaf(f[j], a.p0, a.p1);
+            f[j] = ACT == kActSilu ? fmaf(h, tanh_approx(h), h) : h;
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < VEC; ++j)
+            f[j] = activate<ACT, false>(fmaf((f[j] - a.p0) * a.p1, a.p2, a.p3));
+    }
+    return pack<T>(f);
+}
+
 struct ResidentArgs {
     const void *in;
     void *out;
@@ -163,14 +276,27 @@ struct ResidentArgs {
     uint32_t cpg;          // channels per group
     uint32_t groups;
     uint32_t chunk_vecs;   // vectors per ring chunk
+    uint32_t nslots;       // chunk slots in the shared-memory ring
     uint32_t vec_uniform;  // hw % lanes-per-vector == 0
+    uint32_t hw_vecs;      // hw / lanes-per-vector (when vec_uniform)
     float eps;
-    FastDiv hw_div;
+    FastDiv hw_div;        // element offset -> channel
+    FastDiv hwv_div;       // vector offset -> channel (when vec_uniform)
 };
 
 // blockDim.x = consumer threads (a multiple of 32) + one producer warp.  BIG: one CTA of up to
-// 1024 threads per SM (parts beyond ~100 KB); otherwise up to 512 threads and at least three
-// CTAs per SM, which caps the kernel at 40 registers per thread.
+// 1024 threads per SM; otherwise up to 512 threads and at least three CTAs per SM, which caps
+// the kernel at 40 registers per thread.
+//
+// Shared memory is a ring of `nslots` chunk slots.  The producer numbers its chunk loads
+// n = 0, 1, 2, ... across slabs; load n goes to slot n % nslots and completes phase
+// (n / nslots) & 1 of that slot's "full" barrier; it may start once the consumers have released
+// the slot's previous occupant (phase ((n / nslots) - 1) & 1 of the "empty" barrier).
+//   resident  (a part has at most nslots chunks): a slab's chunks are loaded once, read for the
+//             moments, read again for the normalise pass, then released; free slots are filled
+//             with the next slab's chunks meanwhile.
+//   otherwise the chunks are released after the moments pass and loaded a second time for the
+//             normalise pass (this second read is served by L2 when the clusters' slabs fit it).
 template <typename T, int ACT, bool BIG>
 __global__ void __launch_bounds__(BIG ? 1024 : 512, BIG ? 1 : 3)
 gn_resident_kernel(const ResidentArgs a) {
@@ -187,21 +313,25 @@ gn_resident_kernel(const ResidentArgs a) {
     const uint32_t cwarps = consumers >> 5;
 
     extern __shared__ __align__(128) unsigned char smem[];
-    uint64_t *full = reinterpret_cast<uint64_t *>(smem);                  // [kMaxChunks]
-    uint64_t *empty = reinterpret_cast<uint64_t *>(smem + 64);            // [kMaxChunks]
-    Moments *warp_m = reinterpret_cast<Moments *>(smem + 128);            // [31]
-    float *bcast = reinterpret_cast<float *>(smem + 512);                 // mean, rstd
-    float *pub = reinterpret_cast<float *>(smem + 576);                   // [2][2] read by peers
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem);                  // [kMaxSlots]
+    uint64_t *empty = reinterpret_cast<uint64_t *>(smem + 128);           // [kMaxSlots]
+    Moments *warp_m = reinterpret_cast<Moments *>(smem + 256);            // [31]
+    float *bcast = reinterpret_cast<float *>(smem + 640);                 // mean, rstd
+    float *pub = reinterpret_cast<float *>(smem + 704);                   // [2][2] read by peers
     unsigned char *data = smem + kHeaderBytes;
 
-    // This CTA's share of every slab: vectors [v0, v0 + nv).
+    // This CTA's share of every slab: vectors [v0, v0 + nv), cut into `nchunks` chunks.
     const uint32_t v0 = static_cast<uint32_t>((static_cast<uint64_t>(a.slab_vecs) * rank) / csize);
     const uint32_t v1 = static_cast<uint32_t>((static_cast<uint64_t>(a.slab_vecs) * (rank + 1)) / csize);
     const uint32_t nv = v1 - v0;
-    const uint32_t nchunks = (nv + a.chunk_vecs - 1) / a.chunk_vecs;      // <= kMaxChunks
+    const uint32_t cv = a.chunk_vecs;
+    const uint32_t nchunks = (nv + cv - 1) / cv;
+    const uint32_t nslots = a.nslots;
+    const bool resident = nchunks <= nslots;
+    const uint32_t chunk_bytes = cv * 16u;
 
     if (tid == 0) {
-        for (uint32_t k = 0; k < nchunks; ++k) {
+        for (uint32_t k = 0; k < nslots; ++k) {
             mbar_init(smem_addr(&full[k]), 1);
             mbar_init(smem_addr(&empty[k]), cwarps);
         }
@@ -212,71 +342,78 @@ gn_resident_kernel(const ResidentArgs a) {
     if (warp == cwarps) {
         // ---------------- producer warp ----------------------------------------------------------
         bool timed_out = false;
-        uint32_t it = 0;
+        uint32_t n = 0, slot = 0, round = 0, it = 0;
+        const uint64_t keep = policy_evict_last(), drop = policy_evict_first();
         for (uint32_t unit = cluster_id; unit < a.units; unit += nclusters, ++it) {
-            // The consumers pass one cluster barrier per slab, between reading and releasing
-            // its chunks; join that barrier first, or the empties below could never come.
-            if (it > 0) cluster.sync();
+            // Take part in the consumers' one cluster barrier per slab without ever blocking
+            // ahead of them: arrive for slab `it` now, wait for it before the next arrive.
+            if (it > 0) cluster.barrier_wait();
+            cluster.barrier_arrive();
             if (lane == 0) {
                 const unsigned char *gsrc = static_cast<const unsigned char *>(a.in) +
                                             (static_cast<size_t>(unit) * a.slab_vecs + v0) * 16u;
-                for (uint32_t k = 0; k < nchunks; ++k) {
-                    if (it > 0) {      // chunk k of the previous slab must have been released
-                        if (!mbar_wait_bounded(smem_addr(&empty[k]), (it - 1) & 1u,
+                const uint32_t loads = resident ? nchunks : 2u * nchunks;
+                for (uint32_t l = 0; l < loads; ++l, ++n) {
+                    const uint32_t j = l < nchunks ? l : l - nchunks;
+                    if (round > 0) {
+                        if (!mbar_wait_bounded(smem_addr(&empty[slot]), (round - 1) & 1u,
                                                timed_out ? kWaitCyclesAfterTimeout : kWaitCycles))
                             timed_out = true;
                     }
-                    const uint32_t lo = k * a.chunk_vecs;
-                    const uint32_t bytes = (min(nv, lo + a.chunk_vecs) - lo) * 16u;
-                    const uint32_t bar = smem_addr(&full[k]);
+                    const uint32_t lo = j * cv;
+                    const uint32_t bytes = (min(nv, lo + cv) - lo) * 16u;
+                    const uint32_t bar = smem_addr(&full[slot]);
                     mbar_expect_tx(bar, bytes);
-                    bulk_load(smem_addr(data + lo * 16u), gsrc + lo * 16u, bytes, bar);
+                    // the first of two reads should stay in L2; a last read need not
+                    bulk_load_hint(smem_addr(data + slot * chunk_bytes), gsrc + lo * 16u, bytes, bar,
+                                   (!resident && l < nchunks) ? keep : drop);
+                    if (++slot == nslots) { slot = 0; ++round; }
                 }
             }
             __syncwarp();
         }
-        if (it > 0) cluster.sync();          // the consumers' barrier of the last slab
+        if (it > 0) cluster.barrier_wait();
         if (timed_out && lane == 0) atomicOr(&g_gn_status, 1u);
         cluster.sync();                      // nobody leaves while peers may read its moments
         return;
     }
 
     // ---------------- consumer warps -------------------------------------------------------------
-    const uint4 *sv = reinterpret_cast<const uint4 *>(data);
-    const float part_elems = static_cast<float>(nv) * VEC;
+    const uint32_t hwv = a.hw_vecs;          // vectors per channel (valid when vec_uniform)
     bool timed_out = false;
-    uint32_t it = 0;
+    uint32_t slot = 0, round = 0, it = 0;    // position of the next chunk to consume
     for (uint32_t unit = cluster_id; unit < a.units; unit += nclusters, ++it) {
         const uint32_t par = it & 1u;
+        const uint32_t slot0 = slot, round0 = round;
 
         // pass 1: shifted sums, chunk by chunk as the copies land
-        float s0 = 0.f, s1 = 0.f, q0 = 0.f, q1 = 0.f, shift = 0.f, cnt = 0.f;
-        for (uint32_t k = 0; k < nchunks; ++k) {
-            if (!mbar_wait_bounded(smem_addr(&full[k]), par,
+        float s[2] = {0.f, 0.f}, q[2] = {0.f, 0.f};
+        float shift = 0.f;
+        uint32_t nvec_mine = 0;
+        for (uint32_t j = 0; j < nchunks; ++j) {
+            if (!mbar_wait_bounded(smem_addr(&full[slot]), round & 1u,
                                    timed_out ? kWaitCyclesAfterTimeout : kWaitCycles))
                 timed_out = true;
-            if (k == 0) shift = to_float<T>(reinterpret_cast<const T *>(data)[0]);
-            const uint32_t hi = min(nv, (k + 1) * a.chunk_vecs);
-            for (uint32_t i = k * a.chunk_vecs + tid; i < hi; i += consumers) {
-                float f[VEC];
-                unpack<T>(sv[i], f);
-#pragma unroll
-                for (int j = 0; j < VEC; j += 2) {
-                    const float d0 = f[j] - shift, d1 = f[j + 1] - shift;
-                    s0 += d0;
-                    s1 += d1;
-                    q0 = fmaf(d0, d0, q0);
-                    q1 = fmaf(d1, d1, q1);
-                }
-                cnt += static_cast<float>(VEC);
+            const uint4 *sv = reinterpret_cast<const uint4 *>(data + slot * chunk_bytes);
+            if (j == 0) shift = to_float<T>(reinterpret_cast<const T *>(sv)[0]);
+            const uint32_t cnt = min(cv, nv - j * cv);
+            for (uint32_t i = tid; i < cnt; i += consumers) {
+                stats_vec<T>(sv[i], shift, s, q);
+                ++nvec_mine;
             }
+            if (!resident) {
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_addr(&empty[slot]));
+            }
+            if (++slot == nslots) { slot = 0; ++round; }
         }
         Moments m;
         {
-            const float s = s0 + s1, q = q0 + q1;
+            const float cnt = static_cast<float>(nvec_mine * VEC);
+            const float ss = s[0] + s[1], qq = q[0] + q[1];
             m.n = cnt;
-            m.mean = cnt > 0.f ? shift + s / cnt : 0.f;
-            m.m2 = cnt > 0.f ? fmaxf(q - s * s / cnt, 0.f) : 0.f;
+            m.mean = nvec_mine ? shift + ss / cnt : 0.f;
+            m.m2 = nvec_mine ? fmaxf(qq - ss * ss / cnt, 0.f) : 0.f;
         }
         m = warp_merge(m);
         if (lane == 0) warp_m[warp] = m;
@@ -309,48 +446,201 @@ gn_resident_kernel(const ResidentArgs a) {
         }
         consumer_sync(consumers);
         const float mean = bcast[0], rstd = bcast[1];
-        (void)part_elems;
 
-        // pass 2: normalise + affine (+ activation) from shared memory to global; each chunk is
+        // pass 2: normalise + affine (+ activation) from shared memory to global; each slot is
         // handed back to the producer as soon as this warp is done with it
+        if (resident) { slot = slot0; round = round0; }
         const uint32_t ch0 = (unit % a.groups) * a.cpg;
         uint4 *gv = reinterpret_cast<uint4 *>(static_cast<unsigned char *>(a.out) +
                                               (static_cast<size_t>(unit) * a.slab_vecs + v0) * 16u);
-        for (uint32_t k = 0; k < nchunks; ++k) {
-            const uint32_t hi = min(nv, (k + 1) * a.chunk_vecs);
-            for (uint32_t i = k * a.chunk_vecs + tid; i < hi; i += consumers) {
-                float f[VEC];
-                unpack<T>(sv[i], f);
-                const uint32_t e = (v0 + i) * VEC;
-                if (a.vec_uniform) {
-                    const uint32_t c = ch0 + a.hw_div.div(e);
-                    const float wv = __ldg(a.w + c), bv = __ldg(a.b + c);
-                    if (HALF) {
-                        const float sc = wv * rstd;
-                        const float sh = fmaf(-mean, sc, bv);
-#pragma unroll
-                        for (int j = 0; j < VEC; ++j) f[j] = activate<ACT, HALF>(fmaf(f[j], sc, sh));
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < VEC; ++j)
-                            f[j] = activate<ACT, HALF>(fmaf((f[j] - mean) * rstd, wv, bv));
-                    }
-                } else {
-#pragma unroll
-                    for (int j = 0; j < VEC; ++j) {
-                        const uint32_t c = ch0 + a.hw_div.div(e + j);
-                        f[j] = activate<ACT, HALF>(
-                            fmaf((f[j] - mean) * rstd, __ldg(a.w + c), __ldg(a.b + c)));
-                    }
+        for (uint32_t j = 0; j < nchunks; ++j) {
+            if (!resident) {
+                if (!mbar_wait_bounded(smem_addr(&full[slot]), round & 1u,
+                                       timed_out ? kWaitCyclesAfterTimeout : kWaitCycles))
+                    timed_out = true;
+            }
+            const uint4 *sv = reinterpret_cast<const uint4 *>(data + slot * chunk_bytes);
+            const uint32_t lo = j * cv;                 // part-relative vector index of the chunk
+            const uint32_t hi = min(nv, lo + cv);
+            if (a.vec_uniform && hwv >= consumers) {
+                // long channels: walk channel by channel, weights hoisted out of the vector loop
+                uint32_t i0 = lo;
+                while (i0 < hi) {
+                    const uint32_t c = a.hwv_div.div(v0 + i0);
+                    const uint32_t seg_end = min(hi, (c + 1) * hwv - v0);
+                    const Affine<T> af = make_affine<T, ACT>(mean, rstd, __ldg(a.w + ch0 + c),
+                                                            __ldg(a.b + ch0 + c));
+                    for (uint32_t i = i0 + tid; i < seg_end; i += consumers)
+                        st_stream(&gv[i], norm_vec<T, ACT>(sv[i - lo], af));
+                    i0 = seg_end;
                 }
-                st_stream(&gv[i], pack<T>(f));
+            } else if (a.vec_uniform) {
+                for (uint32_t i = lo + tid; i < hi; i += consumers) {
+                    const uint32_t c = ch0 + a.hwv_div.div(v0 + i);
+                    const Affine<T> af = make_affine<T, ACT>(mean, rstd, __ldg(a.w + c), __ldg(a.b + c));
+                    st_stream(&gv[i], norm_vec<T, ACT>(sv[i - lo], af));
+                }
+            } else {
+                for (uint32_t i = lo + tid; i < hi; i += consumers) {
+                    float f[VEC];
+                    unpack<T>(sv[i - lo], f);
+                    const uint32_t e = (v0 + i) * VEC;
+#pragma unroll
+                    for (int l = 0; l < VEC; ++l) {
+                        const uint32_t c = ch0 + a.hw_div.div(e + l);
+                        f[l] = activate<ACT, HALF>(
+                            fmaf((f[l] - mean) * rstd, __ldg(a.w + c), __ldg(a.b + c)));
+                    }
+                    st_stream(&gv[i], pack<T>(f));
+                }
             }
             __syncwarp();
-            if (lane == 0) mbar_arrive(smem_addr(&empty[k]));
+            if (lane == 0) mbar_arrive(smem_addr(&empty[slot]));
+            if (++slot == nslots) { slot = 0; ++round; }
         }
     }
     if (timed_out && lane == 0) atomicOr(&g_gn_status, 1u);
     cluster.sync();                           // nobody leaves while peers may read its moments
+}
+
+// ---------------------------------------------------------------------------------------------
+// Streaming path: the slab is read twice, the second time from L2
+// ---------------------------------------------------------------------------------------------
+// For slabs whose share per CTA does not leave room for a second CTA on the SM, shared-memory
+// residency serialises load, statistics and store.  Here a persistent cluster streams its slab
+// from HBM once for the moments (normal caching, so the lines stay in L2), merges over the
+// cluster, and reads it again for the normalise pass while the lines are still in L2 (a
+// cluster's slab is a few MB; all resident clusters together hold far less than the L2).
+// No shared-memory capacity limit: several CTAs per SM at any slab size.  Every vector is
+// read and then written by the same thread, so out == in is safe.
+constexpr int kStreamThreads = 512;
+
+template <typename T, int ACT>
+__global__ void __launch_bounds__(kStreamThreads, 3)
+gn_stream_kernel(const ResidentArgs a) {
+    constexpr int VEC = VecOf<T>::N;
+    constexpr bool HALF = sizeof(T) == 2;
+    cg::cluster_group cluster = cg::this_cluster();
+    const uint32_t csize = cluster.num_blocks();
+    const uint32_t rank = cluster.block_rank();
+    const uint32_t cluster_id = blockIdx.x / csize;
+    const uint32_t nclusters = gridDim.x / csize;
+    const uint32_t tid = threadIdx.x;
+    const uint32_t lane = tid & 31u, warp = tid >> 5;
+    constexpr uint32_t kWarps = kStreamThreads / 32;
+
+    __shared__ Moments warp_m[kWarps];
+    __shared__ float bcast[2];
+    __shared__ float pub[4];
+
+    const uint32_t v0 = static_cast<uint32_t>((static_cast<uint64_t>(a.slab_vecs) * rank) / csize);
+    const uint32_t v1 = static_cast<uint32_t>((static_cast<uint64_t>(a.slab_vecs) * (rank + 1)) / csize);
+    const uint32_t nv = v1 - v0;
+    const uint32_t hwv = a.hw_vecs;
+
+    uint32_t it = 0;
+    for (uint32_t unit = cluster_id; unit < a.units; unit += nclusters, ++it) {
+        const uint32_t par = it & 1u;
+        const size_t off = (static_cast<size_t>(unit) * a.slab_vecs + v0) * 16u;
+        const uint4 *gx = reinterpret_cast<const uint4 *>(static_cast<const unsigned char *>(a.in) + off);
+        uint4 *gy = reinterpret_cast<uint4 *>(static_cast<unsigned char *>(a.out) + off);
+
+        // pass 1 (HBM): shifted sums
+        const float shift = to_float<T>(*reinterpret_cast<const T *>(gx));
+        float s[2] = {0.f, 0.f}, q[2] = {0.f, 0.f};
+        uint32_t mine = 0;
+        uint32_t i = tid;
+        for (; i + 3 * kStreamThreads < nv; i += 4 * kStreamThreads) {
+            const uint4 x0 = gx[i], x1 = gx[i + kStreamThreads];
+            const uint4 x2 = gx[i + 2 * kStreamThreads], x3 = gx[i + 3 * kStreamThreads];
+            stats_vec<T>(x0, shift, s, q);
+            stats_vec<T>(x1, shift, s, q);
+            stats_vec<T>(x2, shift, s, q);
+            stats_vec<T>(x3, shift, s, q);
+            mine += 4;
+        }
+        for (; i < nv; i += kStreamThreads) {
+            stats_vec<T>(gx[i], shift, s, q);
+            ++mine;
+        }
+        Moments m;
+        {
+            const float cnt = static_cast<float>(mine * VEC);
+            const float ss = s[0] + s[1], qq = q[0] + q[1];
+            m.n = cnt;
+            m.mean = mine ? shift + ss / cnt : 0.f;
+            m.m2 = mine ? fmaxf(qq - ss * ss / cnt, 0.f) : 0.f;
+        }
+        m = warp_merge(m);
+        if (lane == 0) warp_m[warp] = m;
+        __syncthreads();
+        if (warp == 0) {
+            Moments t = lane < kWarps ? warp_m[lane] : Moments{0.f, 0.f, 0.f};
+            t = warp_merge(t);
+            if (lane == 0) {
+                pub[2 * par] = t.mean;
+                pub[2 * par + 1] = t.m2;
+            }
+        }
+        cluster.sync();
+        if (warp == 0) {
+            Moments t{0.f, 0.f, 0.f};
+            if (lane < csize) {
+                const float *peer = cluster.map_shared_rank(pub, lane);
+                const uint32_t p0 = static_cast<uint32_t>((static_cast<uint64_t>(a.slab_vecs) * lane) / csize);
+                const uint32_t p1 = static_cast<uint32_t>((static_cast<uint64_t>(a.slab_vecs) * (lane + 1)) / csize);
+                t.n = static_cast<float>(p1 - p0) * VEC;
+                t.mean = peer[2 * par];
+                t.m2 = peer[2 * par + 1];
+            }
+            t = warp_merge(t);
+            if (lane == 0) {
+                bcast[0] = t.mean;
+                bcast[1] = 1.0f / sqrtf(t.m2 / static_cast<float>(a.slab_elems) + a.eps);
+            }
+        }
+        __syncthreads();
+        const float mean = bcast[0], rstd = bcast[1];
+
+        // pass 2 (L2): normalise + affine (+ activation)
+        const uint32_t ch0 = (unit % a.groups) * a.cpg;
+        if (a.vec_uniform && hwv >= kStreamThreads) {
+            uint32_t i0 = 0;
+            while (i0 < nv) {
+                const uint32_t c = a.hwv_div.div(v0 + i0);
+                const uint32_t seg_end = min(nv, (c + 1) * hwv - v0);
+                const Affine<T> af = make_affine<T, ACT>(mean, rstd, __ldg(a.w + ch0 + c),
+                                                        __ldg(a.b + ch0 + c));
+                uint32_t j = i0 + tid;
+                for (; j + kStreamThreads < seg_end; j += 2 * kStreamThreads) {
+                    const uint4 x0 = gx[j], x1 = gx[j + kStreamThreads];
+                    st_stream(&gy[j], norm_vec<T, ACT>(x0, af));
+                    st_stream(&gy[j + kStreamThreads], norm_vec<T, ACT>(x1, af));
+                }
+                for (; j < seg_end; j += kStreamThreads) st_stream(&gy[j], norm_vec<T, ACT>(gx[j], af));
+                i0 = seg_end;
+            }
+        } else if (a.vec_uniform) {
+            for (uint32_t j = tid; j < nv; j += kStreamThreads) {
+                const uint32_t c = ch0 + a.hwv_div.div(v0 + j);
+                const Affine<T> af = make_affine<T, ACT>(mean, rstd, __ldg(a.w + c), __ldg(a.b + c));
+                st_stream(&gy[j], norm_vec<T, ACT>(gx[j], af));
+            }
+        } else {
+            for (uint32_t j = tid; j < nv; j += kStreamThreads) {
+                float f[VEC];
+                unpack<T>(gx[j], f);
+                const uint32_t e = (v0 + j) * VEC;
+#pragma unroll
+                for (int l = 0; l < VEC; ++l) {
+                    const uint32_t c = ch0 + a.hw_div.div(e + l);
+                    f[l] = activate<ACT, HALF>(fmaf((f[l] - mean) * rstd, __ldg(a.w + c), __ldg(a.b + c)));
+                }
+                st_stream(&gy[j], pack<T>(f));
+            }
+        }
+    }
+    cluster.sync();     // nobody leaves while peers may read its moments
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -627,16 +917,60 @@ cudaError_t resident_active_clusters(int cluster, int threads, size_t smem, int 
     return cudaSuccess;
 }
 
-constexpr int kSmCount = 148;
-
-// Consumer threads for a resident part of this size: enough warps to keep the SM's issue
-// slots and shared-memory ports busy at the number of CTAs that will share the SM.
-inline int consumers_for(int64_t part_bytes) {
-    if (part_bytes > 100 * 1024) return 992;    // one CTA per SM: 31 + 1 warps
-    if (part_bytes > 40 * 1024) return 480;     // two or three per SM: 15 + 1 warps
-    if (part_bytes > 12 * 1024) return 224;     // 7 + 1 warps
-    return 96;                                  // 3 + 1 warps
+template <typename T, int ACT>
+cudaError_t ensure_stream_attrs() {
+    static std::atomic<bool> done[kMaxDevices];
+    int dev = 0;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess) return err;
+    if (dev >= 0 && dev < kMaxDevices && done[dev].load(std::memory_order_acquire)) return cudaSuccess;
+    err = cudaFuncSetAttribute(gn_stream_kernel<T, ACT>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    if (err != cudaSuccess) return err;
+    if (dev >= 0 && dev < kMaxDevices) done[dev].store(true, std::memory_order_release);
+    return cudaSuccess;
 }
+
+template <typename T>
+cudaError_t stream_active_clusters(int cluster, int *active) {
+    static std::mutex mu;
+    static std::map<uint64_t, int> cache;
+    int dev = 0;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess) return err;
+    const uint64_t key = (static_cast<uint64_t>(dev) << 16) | static_cast<uint64_t>(cluster);
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        auto it = cache.find(key);
+        if (it != cache.end()) { *active = it->second; return cudaSuccess; }
+    }
+    err = ensure_stream_attrs<T, kActSilu>();
+    if (err != cudaSuccess) return err;
+    cudaLaunchConfig_t cfg;
+    cudaLaunchAttribute attr[1];
+    cluster_config(&cfg, attr, static_cast<unsigned>(cluster), cluster, kStreamThreads, 0, nullptr);
+    int n = 0;
+    err = cudaOccupancyMaxActiveClusters(&n, gn_stream_kernel<T, kActSilu>, &cfg);
+    if (err != cudaSuccess) return err;
+    *active = n;
+    std::lock_guard<std::mutex> lock(mu);
+    cache[key] = n;
+    return cudaSuccess;
+}
+
+template <typename T, int ACT>
+cudaError_t launch_stream(const ResidentArgs &a, const GnPlan &plan, cudaStream_t stream) {
+    cudaError_t err = ensure_stream_attrs<T, ACT>();
+    if (err != cudaSuccess) return err;
+    cudaLaunchConfig_t cfg;
+    cudaLaunchAttribute attr[1];
+    cluster_config(&cfg, attr, static_cast<unsigned>(plan.nclusters * plan.cluster), plan.cluster,
+                   kStreamThreads, 0, stream);
+    err = cudaLaunchKernelEx(&cfg, gn_stream_kernel<T, ACT>, a);
+    if (err == cudaSuccess) g_launches.fetch_add(1);
+    return err;
+}
+
+constexpr int kSmCount = 148;
 
 }  // namespace
 
@@ -653,26 +987,62 @@ cudaError_t gn_make_plan(const GnShape &s, const void *in, const void *out, int 
     const int64_t units = s.batch * s.groups;
     *plan = GnPlan{};
 
+    if (force_path == kGnStream) {
+        const bool ok = aligned16(in) && aligned16(out) && slab_bytes % 16 == 0 && slab_bytes >= 16 &&
+                        units < (1ll << 27);
+        if (!ok) return cudaErrorInvalidConfiguration;
+        int c = (force_cluster & 0xff) > 0 ? (force_cluster & 0xff) : 8;
+        if (c > 16 || c > slab_bytes / 16) return cudaErrorInvalidConfiguration;
+        int active = 0;
+        cudaError_t err = s.dtype == kF16 ? stream_active_clusters<__half>(c, &active)
+                                          : stream_active_clusters<float>(c, &active);
+        if (err != cudaSuccess) return err;
+        if (active <= 0) return cudaErrorInvalidConfiguration;
+        const int64_t waves = (units + active - 1) / active;
+        plan->path = kGnStream;
+        plan->cluster = c;
+        plan->threads = kStreamThreads;
+        plan->nclusters = static_cast<int>((units + waves - 1) / waves);
+        return cudaSuccess;
+    }
+
     bool resident_ok = aligned16(in) && aligned16(out) && slab_bytes % 16 == 0 && slab_bytes >= 16 &&
-                       slab_bytes <= 16 * static_cast<int64_t>(kMaxPartBytes) &&
                        units < (1ll << 27);
     if (force_path == kGnSplit) resident_ok = false;
 
     if (resident_ok) {
         // Try every cluster size; score = how evenly the slabs spread over the SMs (work is
         // quantised: `waves` slabs per cluster, whole CTAs per SM) times small factors for
-        // having several CTAs per SM (their load and store phases overlap) and for the cost of
-        // the cluster exchange.  The driver says how many such clusters can be co-resident.
+        // having several CTAs per SM and for the cost of the cluster exchange.  The driver says
+        // how many such clusters can be co-resident.
         const int64_t slab_vecs = slab_bytes / 16;
+        const int k_cluster = force_cluster & 0xff, k_slots = (force_cluster >> 8) & 0xff;
+        const int k_chunk_kb = (force_cluster >> 16) & 0xff, k_cwarps = (force_cluster >> 24) & 0x3f;
         double best = -1.0;
         for (int c = 1; c <= 16; ++c) {
-            if (force_cluster > 0 && c != force_cluster) continue;
+            if (k_cluster > 0 && c != k_cluster) continue;
             if (c > slab_vecs) break;
-            const int64_t part_bytes = ((slab_vecs + c - 1) / c) * 16;
-            if (part_bytes > kMaxPartBytes) continue;
-            const int consumers = consumers_for(part_bytes);
+            const int64_t part_vecs = (slab_vecs + c - 1) / c;
+            const int64_t part_bytes = part_vecs * 16;
+            // ring geometry
+            int64_t chunk_vecs = k_chunk_kb > 0 ? k_chunk_kb * 64 : 1024;          // 16 KB
+            if (chunk_vecs > part_vecs) chunk_vecs = part_vecs;
+            const int64_t chunks = (part_vecs + chunk_vecs - 1) / chunk_vecs;
+            const int64_t chunk_bytes = chunk_vecs * 16;
+            int64_t nslots;
+            if (k_slots > 0) nslots = k_slots;
+            else if (2 * chunks <= kMaxSlots && 2 * chunks * chunk_bytes <= 200 * 1024) nslots = 2 * chunks;
+            else if (chunks <= kMaxSlots && chunks * chunk_bytes <= kMaxPartBytes)
+                nslots = (chunks + 1 <= kMaxSlots && (chunks + 1) * chunk_bytes <= kMaxPartBytes) ? chunks + 1 : chunks;
+            else nslots = 4;
+            if (nslots > kMaxSlots || nslots * chunk_bytes > kMaxPartBytes || nslots < 1) continue;
+            if (nslots < chunks && nslots < 2) continue;      // the re-read mode needs a real ring
+            const size_t smem = kHeaderBytes + static_cast<size_t>(nslots * chunk_bytes);
+            int consumers = k_cwarps > 0 ? k_cwarps * 32
+                                         : (smem > 100 * 1024 ? 992 : smem > 40 * 1024 ? 480
+                                                                : smem > 12 * 1024 ? 224 : 96);
+            if (consumers > 992) consumers = 992;
             const int threads = consumers + 32;
-            const size_t smem = kHeaderBytes + static_cast<size_t>(part_bytes);
             int active = 0;
             cudaError_t err = s.dtype == kF16
                                   ? resident_active_clusters<__half>(c, threads, smem, &active)
@@ -685,7 +1055,8 @@ cudaError_t gn_make_plan(const GnShape &s, const void *in, const void *out, int 
             double score = static_cast<double>(units) * c /
                            (static_cast<double>(kSmCount) * waves * per_sm);
             if (score > 1.0) score = 1.0;
-            if (static_cast<double>(active) * c / kSmCount < 2.0) score *= 0.92;
+            if (static_cast<double>(active) * c / kSmCount < 2.0 && nslots < 2 * chunks) score *= 0.92;
+            if (nslots < chunks) score *= 0.9;                 // second read (L2)
             if (part_bytes < 16 * 1024) score *= 0.9;
             if (c > 1) score *= 0.99;
             if (c > 8) score *= 0.98;
@@ -696,11 +1067,8 @@ cudaError_t gn_make_plan(const GnShape &s, const void *in, const void *out, int 
                 plan->threads = threads;
                 plan->smem = smem;
                 plan->nclusters = static_cast<int>(nclusters);
-                // four ring chunks per part (at least 4 KB each)
-                int64_t part_vecs = part_bytes / 16;
-                int64_t chunk = (part_vecs + 3) / 4;
-                if (chunk < 256) chunk = 256;
-                plan->chunk_vecs = static_cast<int>(chunk);
+                plan->chunk_vecs = static_cast<int>(chunk_vecs);
+                plan->nslots = static_cast<int>(nslots);
             }
         }
         if (best > 0.0) return cudaSuccess;
@@ -721,7 +1089,7 @@ cudaError_t gn_make_plan(const GnShape &s, const void *in, const void *out, int 
     if (splits > max_splits) splits = max_splits;
     if (splits < 1) splits = 1;
     if (splits > 1024) splits = 1024;
-    if (force_cluster > 0) splits = force_cluster;
+    if (force_cluster > 0) splits = force_cluster & 0xffff;
     int64_t chunk = (slab_elems + splits - 1) / splits;
     chunk = ((chunk + vec - 1) / vec) * vec;
     splits = (slab_elems + chunk - 1) / chunk;
@@ -739,7 +1107,7 @@ cudaError_t gn_launch(const GnShape &s, const GnPlan &plan, const void *in, void
     const int64_t units = s.batch * s.groups;
     if (units == 0 || slab_elems == 0) return cudaSuccess;
 
-    if (plan.path == kGnResident) {
+    if (plan.path == kGnResident || plan.path == kGnStream) {
         ResidentArgs a;
         a.in = in; a.out = out; a.w = w; a.b = b;
         a.units = static_cast<uint32_t>(units);
@@ -748,9 +1116,19 @@ cudaError_t gn_launch(const GnShape &s, const GnPlan &plan, const void *in, void
         a.cpg = static_cast<uint32_t>(cpg);
         a.groups = static_cast<uint32_t>(s.groups);
         a.chunk_vecs = static_cast<uint32_t>(plan.chunk_vecs);
+        a.nslots = static_cast<uint32_t>(plan.nslots);
         a.vec_uniform = s.hw % vec == 0;
+        a.hw_vecs = a.vec_uniform ? static_cast<uint32_t>(s.hw / vec) : 1u;
         a.eps = s.eps;
         a.hw_div = FastDiv::make(static_cast<uint32_t>(s.hw));
+        a.hwv_div = FastDiv::make(a.hw_vecs);
+        if (plan.path == kGnStream) {
+            if (s.dtype == kF16)
+                return s.act == kActSilu ? launch_stream<__half, kActSilu>(a, plan, stream)
+                                         : launch_stream<__half, kActNone>(a, plan, stream);
+            return s.act == kActSilu ? launch_stream<float, kActSilu>(a, plan, stream)
+                                     : launch_stream<float, kActNone>(a, plan, stream);
+        }
         if (s.dtype == kF16)
             return s.act == kActSilu ? launch_resident<__half, kActSilu>(a, plan, stream)
                                      : launch_resident<__half, kActNone>(a, plan, stream);

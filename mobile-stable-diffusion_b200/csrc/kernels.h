@@ -19,7 +19,7 @@ extern std::atomic<long long> g_launches;
 //                and activation cost one HBM read and one HBM write.
 //   kGnSplit     two kernels with a caller-provided scratch of per-chunk (mean, M2) partials;
 //                any size, any alignment; one extra read of the tensor (mostly L2 for mid sizes).
-enum GnPath : int { kGnAuto = 0, kGnResident = 1, kGnSplit = 2 };
+enum GnPath : int { kGnAuto = 0, kGnResident = 1, kGnSplit = 2, kGnStream = 3 };
 
 struct GnPlan {
     int path;          // kGnResident or kGnSplit
@@ -27,6 +27,7 @@ struct GnPlan {
     int threads;       // threads per CTA (resident: consumer warps + one producer warp)
     int nclusters;     // persistent clusters launched (resident)
     int chunk_vecs;    // 16-byte vectors per shared-memory ring chunk (resident)
+    int nslots;        // chunk slots in the ring (resident); fewer than a part's chunks = re-read mode
     int splits;        // chunks per slab (split path)
     size_t smem;       // dynamic shared memory per CTA (resident)
     size_t workspace;  // scratch bytes the split path needs

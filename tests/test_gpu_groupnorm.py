@@ -22,7 +22,7 @@ def test_golden_vectors_from_the_reference_kernels(sdfl):
     for name in sorted({k.split(".")[0] for k in g.files if k.startswith("gn_")}):
         G, silu = (int(v) for v in g[f"{name}.meta"])
         eps = float(g[f"{name}.eps"][0])
-        for path in (sdfl.ops.GN_AUTO, sdfl.ops.GN_SPLIT):
+        for path in (sdfl.ops.GN_AUTO, sdfl.ops.GN_SPLIT, sdfl.ops.GN_STREAM):
             got = run_gn(sdfl, g[f"{name}.x"], g[f"{name}.gamma"], g[f"{name}.beta"], G, eps,
                          bool(silu), path=path)
             assert_close(got, g[f"{name}.y"], 1e-5, f"{name} path {path}")
@@ -85,13 +85,14 @@ def test_config5_vae_shapes_fp16(sdfl, shape):
     assert sdfl.ops.device_status() == 0
 
 
-def test_vae_fp32_slab_beyond_cluster_capacity_takes_split_path(sdfl):
-    shape = (1, 128, 512, 512)                 # 4 MiB per group in fp32
-    plan = sdfl.ops.groupnorm_plan(1, 128, 512 * 512, 32, torch.float32)
-    assert plan["path"] == sdfl.ops.GN_SPLIT and plan["workspace"] > 0
+def test_vae_fp32_slab_larger_than_any_cluster_can_hold(sdfl):
+    shape = (1, 128, 512, 512)                 # 4 MiB per group in fp32: cannot be shared-memory resident
     x, gamma, beta = gn_inputs(rng_for(5, 99), shape, "float32")
     want = oracle_group_norm(x, gamma, beta, 32, 1e-6, True)
-    assert_close(run_gn(sdfl, x, gamma, beta, 32, 1e-6, True), want, 1e-5, "fp32 4 MiB slabs")
+    assert_close(run_gn(sdfl, x, gamma, beta, 32, 1e-6, True), want, 1e-5, "fp32 4 MiB slabs, auto")
+    got = run_gn(sdfl, x, gamma, beta, 32, 1e-6, True, path=sdfl.ops.GN_SPLIT)
+    assert_close(got, want, 1e-5, "fp32 4 MiB slabs, split path")
+    assert sdfl.ops.groupnorm_plan(1, 128, 512 * 512, 32, torch.float32, sdfl.ops.GN_SPLIT)["workspace"] > 0
 
 
 RAGGED = [((3, 6, 5, 7), 3), ((2, 12, 1, 1), 4), ((1, 4, 3, 3), 4), ((2, 10, 9, 11), 5),
@@ -153,9 +154,15 @@ def test_batch_is_independent_runs_and_results_are_deterministic(sdfl):
     full = sdfl.ops.groupnorm(dx, dg, db, 32, 1e-6, True)
     again = sdfl.ops.groupnorm(dx, dg, db, 32, 1e-6, True)
     assert torch.equal(full, again)
+    # with the same cluster size the per-slab arithmetic does not depend on the batch at all
+    kw = dict(path=sdfl.ops.GN_RESIDENT, cluster_or_splits=4)
+    full4 = sdfl.ops.groupnorm(dx, dg, db, 32, 1e-6, True, **kw)
     for n in range(4):
-        one = sdfl.ops.groupnorm(dx[n:n + 1].contiguous(), dg, db, 32, 1e-6, True)
-        assert torch.equal(one[0], full[n])
+        one = sdfl.ops.groupnorm(dx[n:n + 1].contiguous(), dg, db, 32, 1e-6, True, **kw)
+        assert torch.equal(one[0], full4[n])
+        # and whatever plan a single image gets, the values agree within tolerance
+        auto = sdfl.ops.groupnorm(dx[n:n + 1].contiguous(), dg, db, 32, 1e-6, True)
+        assert_close(to_np(auto[0]), to_np(full[n]).astype(np.float32), TOL["float16"], f"image {n}")
 
 
 def test_empty_batch_and_errors(sdfl):
@@ -186,8 +193,9 @@ def test_full_size_vae_tensor_properties(sdfl):
     assert float(mean.abs().max()) < 2e-3
     assert float((var - 1).abs().max()) < 5e-3
     one = sdfl.ops.groupnorm(x[3:4].contiguous(), ones, zeros, 32, 1e-6, False)
-    assert torch.equal(one[0], y[3])
-    del one
+    d = (one[0].float() - y[3].float()).abs()          # other cluster size, same values
+    assert float((d - 2e-3 * y[3].float().abs()).max()) <= 2e-3
+    del one, d
     ys = sdfl.ops.groupnorm(x, ones, zeros, 32, 1e-6, True)
     ref = sdfl.ops.silu(y)
     diff = (ys.float() - ref.float()).abs()
