@@ -28,6 +28,7 @@
 
 #include <cooperative_groups.h>
 
+#include <cstdlib>
 #include <map>
 #include <mutex>
 
@@ -79,15 +80,34 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
-// Wait for phase `parity` of `bar`, at most `limit` clock cycles.  Returns false on time-out;
-// the caller records it and carries on (every thread must still reach the cluster barriers).
+__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        " .reg .pred p;\n"
+        " mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+        " selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(ns)
+        : "memory");
+    return ok != 0;
+}
+
+// Wait for phase `parity` of `bar`, at most about `limit` clock cycles.  The hardware parks the
+// warp inside try_wait (suspend-time hint), so a waiting warp takes almost no issue slots from
+// the warps that have work; the clock is only looked at every few wake-ups.  Returns false on
+// time-out; the caller records it and carries on (every thread must still reach the cluster
+// barriers).
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, long long limit) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
-    while (!mbar_try_wait(bar, parity)) {
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 8; ++i)
+            if (mbar_try_wait_hint(bar, parity, 4000u)) return true;
         if (clock64() - t0 > limit) return false;
     }
-    return true;
 }
 
 // 1-D bulk copy global -> this CTA's shared memory; completion counted in bytes on `bar`.
@@ -223,6 +243,49 @@ __device__ __forceinline__ void stats_vec<__half>(const uint4 &v, float shift, f
     stats_half2(v.w, shift, s, q);
 }
 
+// Moments of fp16 data on the tensor pipe (legacy warp-level MMA): the data vector of each lane
+// is one A fragment of a 16x16 tile.  With B = ones the accumulator holds row sums; with B
+// built from the same registers (rows 0-7, then rows 8-15, of A transposed) the accumulator's
+// diagonal holds the rows' sums of squares.  Three MMAs replace 24 scalar instructions per
+// lane; products of fp16 values are exact in the fp32 accumulator.
+__device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                          uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+struct MmaMoments {
+    float sum[4], sq_lo[4], sq_hi[4];
+    __device__ __forceinline__ void clear() {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) sum[i] = sq_lo[i] = sq_hi[i] = 0.f;
+    }
+    // v: 8 fp16 lanes; shift2: the shift replicated in both halves.  Every lane of the warp
+    // must call this together (lanes without data pass v = shift pattern -> zeros).
+    __device__ __forceinline__ void add(const uint4 &v, uint32_t shift2) {
+        const __half2 k = *reinterpret_cast<const __half2 *>(&shift2);
+        const __half2 d0 = __hsub2(*reinterpret_cast<const __half2 *>(&v.x), k);
+        const __half2 d1 = __hsub2(*reinterpret_cast<const __half2 *>(&v.y), k);
+        const __half2 d2 = __hsub2(*reinterpret_cast<const __half2 *>(&v.z), k);
+        const __half2 d3 = __hsub2(*reinterpret_cast<const __half2 *>(&v.w), k);
+        const uint32_t a0 = *reinterpret_cast<const uint32_t *>(&d0), a1 = *reinterpret_cast<const uint32_t *>(&d1);
+        const uint32_t a2 = *reinterpret_cast<const uint32_t *>(&d2), a3 = *reinterpret_cast<const uint32_t *>(&d3);
+        mma_16816(sum, a0, a1, a2, a3, 0x3C003C00u, 0x3C003C00u);   // B = ones
+        mma_16816(sq_lo, a0, a1, a2, a3, a0, a2);                   // B[k][n] = A[n][k]
+        mma_16816(sq_hi, a0, a1, a2, a3, a1, a3);                   // B[k][n] = A[8 + n][k]
+    }
+    // This lane's share of sum(d) and sum(d*d): row sums sit in the lanes with t == 0, the
+    // diagonal entries in the lane with t == g / 2 (g = lane / 4, t = lane % 4).
+    __device__ __forceinline__ void extract(uint32_t lane, float &s, float &q) const {
+        const uint32_t g = lane >> 2, t = lane & 3u;
+        s = t == 0 ? sum[0] + sum[2] : 0.f;
+        q = t == (g >> 1) ? ((g & 1u) ? sq_lo[1] + sq_hi[3] : sq_lo[0] + sq_hi[2]) : 0.f;
+    }
+};
+
 // Per-channel constants of the normalise pass.
 //   fp32 storage: the reference's operation order, y = fma((x - mean) * rstd, w, b).
 //   fp16 storage: folded, y = fma(x, sc, sh) with sc = w * rstd, sh = b - mean * sc; with SiLU
@@ -277,6 +340,7 @@ struct ResidentArgs {
     uint32_t groups;
     uint32_t chunk_vecs;   // vectors per ring chunk
     uint32_t nslots;       // chunk slots in the shared-memory ring
+    uint32_t dbg;          // experiment switches (0 in production)
     uint32_t vec_uniform;  // hw % lanes-per-vector == 0
     uint32_t hw_vecs;      // hw / lanes-per-vector (when vec_uniform)
     float eps;
@@ -297,7 +361,7 @@ struct ResidentArgs {
 //             with the next slab's chunks meanwhile.
 //   otherwise the chunks are released after the moments pass and loaded a second time for the
 //             normalise pass (this second read is served by L2 when the clusters' slabs fit it).
-template <typename T, int ACT, bool BIG>
+template <typename T, int ACT, bool BIG, bool MMA>
 __global__ void __launch_bounds__(BIG ? 1024 : 512, BIG ? 1 : 3)
 gn_resident_kernel(const ResidentArgs a) {
     constexpr int VEC = VecOf<T>::N;
@@ -389,17 +453,37 @@ gn_resident_kernel(const ResidentArgs a) {
         // pass 1: shifted sums, chunk by chunk as the copies land
         float s[2] = {0.f, 0.f}, q[2] = {0.f, 0.f};
         float shift = 0.f;
+        uint32_t shift2 = 0;
         uint32_t nvec_mine = 0;
+        MmaMoments mm;
+        if (MMA) mm.clear();
         for (uint32_t j = 0; j < nchunks; ++j) {
             if (!mbar_wait_bounded(smem_addr(&full[slot]), round & 1u,
                                    timed_out ? kWaitCyclesAfterTimeout : kWaitCycles))
                 timed_out = true;
             const uint4 *sv = reinterpret_cast<const uint4 *>(data + slot * chunk_bytes);
-            if (j == 0) shift = to_float<T>(reinterpret_cast<const T *>(sv)[0]);
+            if (j == 0) {
+                shift = to_float<T>(reinterpret_cast<const T *>(sv)[0]);
+                if (MMA) {
+                    const uint32_t h = *reinterpret_cast<const unsigned short *>(sv);
+                    shift2 = h | (h << 16);
+                }
+            }
             const uint32_t cnt = min(cv, nv - j * cv);
-            for (uint32_t i = tid; i < cnt; i += consumers) {
-                stats_vec<T>(sv[i], shift, s, q);
-                ++nvec_mine;
+            if (MMA) {
+                // warp-uniform trip count: every lane takes part in every MMA
+                for (uint32_t base = warp * 32u; base < cnt; base += consumers) {
+                    const uint32_t i = base + lane;
+                    const bool valid = i < cnt;
+                    const uint4 v = valid ? sv[i] : make_uint4(shift2, shift2, shift2, shift2);
+                    mm.add(v, shift2);
+                    nvec_mine += valid ? 1u : 0u;
+                }
+            } else if (!(a.dbg & 4u)) {
+                for (uint32_t i = tid; i < cnt; i += consumers) {
+                    stats_vec<T>(sv[i], shift, s, q);
+                    ++nvec_mine;
+                }
             }
             if (!resident) {
                 __syncwarp();
@@ -408,7 +492,17 @@ gn_resident_kernel(const ResidentArgs a) {
             if (++slot == nslots) { slot = 0; ++round; }
         }
         Moments m;
-        {
+        if (MMA) {
+            // sums belong to tile rows, not to lanes: fold the warp's plain sums first
+            float ss, qq;
+            mm.extract(lane, ss, qq);
+            ss = warp_sum(ss);
+            qq = warp_sum(qq);
+            const float cnt = warp_sum(static_cast<float>(nvec_mine * VEC));
+            m.n = lane == 0 ? cnt : 0.f;
+            m.mean = cnt > 0.f ? shift + ss / cnt : 0.f;
+            m.m2 = cnt > 0.f ? fmaxf(qq - ss * ss / cnt, 0.f) : 0.f;
+        } else {
             const float cnt = static_cast<float>(nvec_mine * VEC);
             const float ss = s[0] + s[1], qq = q[0] + q[1];
             m.n = cnt;
@@ -462,7 +556,9 @@ gn_resident_kernel(const ResidentArgs a) {
             const uint4 *sv = reinterpret_cast<const uint4 *>(data + slot * chunk_bytes);
             const uint32_t lo = j * cv;                 // part-relative vector index of the chunk
             const uint32_t hi = min(nv, lo + cv);
-            if (a.vec_uniform && hwv >= consumers) {
+            if (a.dbg & 8u) {
+                for (uint32_t i = lo + tid; i < hi; i += consumers) st_stream(&gv[i], sv[i - lo]);
+            } else if (a.vec_uniform && hwv >= consumers) {
                 // long channels: walk channel by channel, weights hoisted out of the vector loop
                 uint32_t i0 = lo;
                 while (i0 < hi) {
@@ -830,14 +926,14 @@ inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 
 // the opt-in for 16-CTA clusters), so that launches themselves make no attribute calls.
 constexpr int kMaxDevices = 64;
 
-template <typename T, int ACT, bool BIG>
+template <typename T, int ACT, bool BIG, bool MMA>
 cudaError_t ensure_resident_attrs() {
     static std::atomic<bool> done[kMaxDevices];
     int dev = 0;
     cudaError_t err = cudaGetDevice(&dev);
     if (err != cudaSuccess) return err;
     if (dev >= 0 && dev < kMaxDevices && done[dev].load(std::memory_order_acquire)) return cudaSuccess;
-    auto kernel = gn_resident_kernel<T, ACT, BIG>;
+    auto kernel = gn_resident_kernel<T, ACT, BIG, MMA>;
     err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                static_cast<int>(kHeaderBytes + kMaxPartBytes));
     if (err != cudaSuccess) return err;
@@ -862,23 +958,29 @@ inline void cluster_config(cudaLaunchConfig_t *cfg, cudaLaunchAttribute *attr, u
     cfg->numAttrs = 1;
 }
 
-template <typename T, int ACT, bool BIG>
+template <typename T, int ACT, bool BIG, bool MMA>
 cudaError_t launch_resident_as(const ResidentArgs &a, const GnPlan &plan, cudaStream_t stream) {
-    cudaError_t err = ensure_resident_attrs<T, ACT, BIG>();
+    cudaError_t err = ensure_resident_attrs<T, ACT, BIG, MMA>();
     if (err != cudaSuccess) return err;
     cudaLaunchConfig_t cfg;
     cudaLaunchAttribute attr[1];
     cluster_config(&cfg, attr, static_cast<unsigned>(plan.nclusters * plan.cluster), plan.cluster,
                    plan.threads, plan.smem, stream);
-    err = cudaLaunchKernelEx(&cfg, gn_resident_kernel<T, ACT, BIG>, a);
+    err = cudaLaunchKernelEx(&cfg, gn_resident_kernel<T, ACT, BIG, MMA>, a);
     if (err == cudaSuccess) g_launches.fetch_add(1);
     return err;
 }
 
 template <typename T, int ACT>
 cudaError_t launch_resident(const ResidentArgs &a, const GnPlan &plan, cudaStream_t stream) {
-    return plan.threads > 512 ? launch_resident_as<T, ACT, true>(a, plan, stream)
-                              : launch_resident_as<T, ACT, false>(a, plan, stream);
+    // fp16 moments on the tensor pipe unless SDFL_GN_FLAGS has bit 1 clear (experiment switch)
+    static const int flags = [] { const char *e = getenv("SDFL_GN_FLAGS"); return e ? atoi(e) : 0; }();
+    if (sizeof(T) == 2 && (flags & 2)) {
+        return plan.threads > 512 ? launch_resident_as<T, ACT, true, sizeof(T) == 2>(a, plan, stream)
+                                  : launch_resident_as<T, ACT, false, sizeof(T) == 2>(a, plan, stream);
+    }
+    return plan.threads > 512 ? launch_resident_as<T, ACT, true, false>(a, plan, stream)
+                              : launch_resident_as<T, ACT, false, false>(a, plan, stream);
 }
 
 // How many clusters of this size, block size and shared-memory footprint can be resident at
@@ -900,16 +1002,16 @@ cudaError_t resident_active_clusters(int cluster, int threads, size_t smem, int 
         auto it = cache.find(key);
         if (it != cache.end()) { *active = it->second; return cudaSuccess; }
     }
-    err = threads > 512 ? ensure_resident_attrs<T, kActSilu, true>()
-                        : ensure_resident_attrs<T, kActSilu, false>();
+    err = threads > 512 ? ensure_resident_attrs<T, kActSilu, true, false>()
+                        : ensure_resident_attrs<T, kActSilu, false, false>();
     if (err != cudaSuccess) return err;
     cudaLaunchConfig_t cfg;
     cudaLaunchAttribute attr[1];
     cluster_config(&cfg, attr, static_cast<unsigned>(cluster), cluster, threads, smem, nullptr);
     int n = 0;
     err = threads > 512
-              ? cudaOccupancyMaxActiveClusters(&n, gn_resident_kernel<T, kActSilu, true>, &cfg)
-              : cudaOccupancyMaxActiveClusters(&n, gn_resident_kernel<T, kActSilu, false>, &cfg);
+              ? cudaOccupancyMaxActiveClusters(&n, gn_resident_kernel<T, kActSilu, true, false>, &cfg)
+              : cudaOccupancyMaxActiveClusters(&n, gn_resident_kernel<T, kActSilu, false, false>, &cfg);
     if (err != cudaSuccess) return err;
     *active = n;
     std::lock_guard<std::mutex> lock(mu);
@@ -1011,36 +1113,38 @@ cudaError_t gn_make_plan(const GnShape &s, const void *in, const void *out, int 
     if (force_path == kGnSplit) resident_ok = false;
 
     if (resident_ok) {
-        // Try every cluster size; score = how evenly the slabs spread over the SMs (work is
-        // quantised: `waves` slabs per cluster, whole CTAs per SM) times small factors for
-        // having several CTAs per SM and for the cost of the cluster exchange.  The driver says
-        // how many such clusters can be co-resident.
+        // Ring geometry and cluster size, from sweeps on B200 (fp16 and fp32 behave alike per
+        // byte).  A small ring (3 slots of 16-32 KB, 7 consumer warps) with the second read
+        // served by L2 beats full shared-memory residency at every size tried: it keeps 2-4 CTAs
+        // on each SM, so one CTA's cluster exchange hides behind the others' traffic.  The
+        // cluster grows with the slab so that the slabs in flight (clusters x slab bytes) stay
+        // well inside L2, and with few slabs so that every SM still gets a CTA.
         const int64_t slab_vecs = slab_bytes / 16;
         const int k_cluster = force_cluster & 0xff, k_slots = (force_cluster >> 8) & 0xff;
         const int k_chunk_kb = (force_cluster >> 16) & 0xff, k_cwarps = (force_cluster >> 24) & 0x3f;
-        double best = -1.0;
-        for (int c = 1; c <= 16; ++c) {
-            if (k_cluster > 0 && c != k_cluster) continue;
-            if (c > slab_vecs) break;
+        int c = slab_bytes <= 192 * 1024 ? 2 : slab_bytes <= 768 * 1024 ? 4 : 8;
+        const int64_t want_ctas = 2 * kSmCount;
+        while (c < 16 && units * c < want_ctas && slab_bytes / (2 * c) >= 8 * 1024) c *= 2;
+        while (c > 1 && slab_bytes / c < 8 * 1024) c /= 2;
+        if (k_cluster > 0) c = k_cluster;
+        if (c > 16) c = 16;
+        if (c > slab_vecs) c = 1;
+        for (; c >= 1; c = (k_cluster > 0 ? 0 : c / 2)) {
             const int64_t part_vecs = (slab_vecs + c - 1) / c;
             const int64_t part_bytes = part_vecs * 16;
-            // ring geometry
-            int64_t chunk_vecs = k_chunk_kb > 0 ? k_chunk_kb * 64 : 1024;          // 16 KB
+            int64_t chunk_vecs = k_chunk_kb > 0 ? k_chunk_kb * 64 : (part_bytes >= 256 * 1024 ? 2048 : 1024);
             if (chunk_vecs > part_vecs) chunk_vecs = part_vecs;
             const int64_t chunks = (part_vecs + chunk_vecs - 1) / chunk_vecs;
             const int64_t chunk_bytes = chunk_vecs * 16;
-            int64_t nslots;
-            if (k_slots > 0) nslots = k_slots;
-            else if (2 * chunks <= kMaxSlots && 2 * chunks * chunk_bytes <= 200 * 1024) nslots = 2 * chunks;
-            else if (chunks <= kMaxSlots && chunks * chunk_bytes <= kMaxPartBytes)
-                nslots = (chunks + 1 <= kMaxSlots && (chunks + 1) * chunk_bytes <= kMaxPartBytes) ? chunks + 1 : chunks;
-            else nslots = 4;
-            if (nslots > kMaxSlots || nslots * chunk_bytes > kMaxPartBytes || nslots < 1) continue;
-            if (nslots < chunks && nslots < 2) continue;      // the re-read mode needs a real ring
+            int64_t nslots = k_slots > 0 ? k_slots : 3;
+            if (k_slots == 0 && chunks < nslots) nslots = chunks;      // tiny parts: fully resident
+            if (nslots > kMaxSlots || nslots * chunk_bytes > kMaxPartBytes || nslots < 1) {
+                if (k_cluster > 0) break;
+                continue;
+            }
+            if (nslots < chunks && nslots < 2) { if (k_cluster > 0) break; continue; }
             const size_t smem = kHeaderBytes + static_cast<size_t>(nslots * chunk_bytes);
-            int consumers = k_cwarps > 0 ? k_cwarps * 32
-                                         : (smem > 100 * 1024 ? 992 : smem > 40 * 1024 ? 480
-                                                                : smem > 12 * 1024 ? 224 : 96);
+            int consumers = k_cwarps > 0 ? k_cwarps * 32 : (part_bytes >= 8 * 1024 ? 224 : 96);
             if (consumers > 992) consumers = 992;
             const int threads = consumers + 32;
             int active = 0;
@@ -1048,30 +1152,17 @@ cudaError_t gn_make_plan(const GnShape &s, const void *in, const void *out, int 
                                   ? resident_active_clusters<__half>(c, threads, smem, &active)
                                   : resident_active_clusters<float>(c, threads, smem, &active);
             if (err != cudaSuccess) { (void)cudaGetLastError(); active = 0; }
-            if (active <= 0) continue;
+            if (active <= 0) { if (k_cluster > 0) break; continue; }
             const int64_t waves = (units + active - 1) / active;
-            const int64_t nclusters = (units + waves - 1) / waves;
-            const int64_t per_sm = (nclusters * c + kSmCount - 1) / kSmCount;
-            double score = static_cast<double>(units) * c /
-                           (static_cast<double>(kSmCount) * waves * per_sm);
-            if (score > 1.0) score = 1.0;
-            if (static_cast<double>(active) * c / kSmCount < 2.0 && nslots < 2 * chunks) score *= 0.92;
-            if (nslots < chunks) score *= 0.9;                 // second read (L2)
-            if (part_bytes < 16 * 1024) score *= 0.9;
-            if (c > 1) score *= 0.99;
-            if (c > 8) score *= 0.98;
-            if (score > best) {
-                best = score;
-                plan->path = kGnResident;
-                plan->cluster = c;
-                plan->threads = threads;
-                plan->smem = smem;
-                plan->nclusters = static_cast<int>(nclusters);
-                plan->chunk_vecs = static_cast<int>(chunk_vecs);
-                plan->nslots = static_cast<int>(nslots);
-            }
+            plan->path = kGnResident;
+            plan->cluster = c;
+            plan->threads = threads;
+            plan->smem = smem;
+            plan->nclusters = static_cast<int>((units + waves - 1) / waves);
+            plan->chunk_vecs = static_cast<int>(chunk_vecs);
+            plan->nslots = static_cast<int>(nslots);
+            return cudaSuccess;
         }
-        if (best > 0.0) return cudaSuccess;
         if (force_path == kGnResident) return cudaErrorInvalidConfiguration;
     } else if (force_path == kGnResident) {
         return cudaErrorInvalidConfiguration;
@@ -1117,6 +1208,10 @@ cudaError_t gn_launch(const GnShape &s, const GnPlan &plan, const void *in, void
         a.groups = static_cast<uint32_t>(s.groups);
         a.chunk_vecs = static_cast<uint32_t>(plan.chunk_vecs);
         a.nslots = static_cast<uint32_t>(plan.nslots);
+        {
+            static const unsigned dbg = [] { const char *e = getenv("SDFL_GN_FLAGS"); return e ? static_cast<unsigned>(atoi(e)) : 0u; }();
+            a.dbg = dbg;
+        }
         a.vec_uniform = s.hw % vec == 0;
         a.hw_vecs = a.vec_uniform ? static_cast<uint32_t>(s.hw / vec) : 1u;
         a.eps = s.eps;
