@@ -96,6 +96,29 @@ size_t sdfl_groupnorm_workspace_bytes_ex(int64_t batch, int64_t channels, int64_
 int sdfl_groupnorm_plan(int64_t batch, int64_t channels, int64_t hw, int64_t num_groups, int dtype,
                         int path, int cluster_or_splits, int64_t plan[8]);
 
+/* GroupNorm(+SiLU) for callers that may not allocate device memory and therefore cannot supply
+ * the workspace sdfl_groupnorm_forward may ask for.  (No counterpart in the reference: it
+ * creates and releases its mean/variance buffers inside every forward call,
+ * NN/GroupNorm.cpp:95-103,164-165.)
+ * Who needs it: a host application that hands all device memory to its own pools at start-up
+ * and forbids later cudaMalloc calls, plugins running inside such a host, and latency-critical
+ * threads that cannot take the device-wide synchronisation an allocator call may imply.
+ * It always runs the two-kernel split path; the per-chunk (mean, M2) scratch lives in a fixed
+ * 64 KiB array inside the library image (resident on every device that loads the library, for
+ * the life of the process).  This call and everything under it makes no cudaMalloc / cudaFree /
+ * allocating-library call.
+ * Limit: batch * num_groups * chunks-per-slab * 8 bytes <= 65536 (e.g. batch 8 x 32 groups with
+ * up to 32 chunks per slab); larger problems return SDFL_ERR_WORKSPACE and touch nothing.
+ * The first call on a device looks up the array's device address (once per device, with that
+ * device current); make that first call before starting any stream capture on the device.
+ * All calls on a device share the one array and it keeps the previous call's values: nothing
+ * in it needs clearing (each call overwrites every entry it later reads), but two calls whose
+ * kernels can overlap on the GPU (different streams, no dependency) race on it -- order them.
+ * Results equal sdfl_groupnorm_forward_ex(..., SDFL_GN_SPLIT, 0, ...) bit for bit. */
+int sdfl_groupnorm_forward_noalloc(const void *in, void *out, const float *gamma, const float *beta,
+                                   int64_t batch, int64_t channels, int64_t hw, int64_t num_groups,
+                                   float eps, int fuse_silu, int dtype, void *stream);
+
 /* LayerNorm over the last dimension of [rows, dim].
  * Replaces LayerNorm::forward (NN/LayerNorm.cpp:66-162; K/layer_norm.cl:1-78).  eps is an
  * argument; the reference fixes it at 1e-5 (K/layer_norm.cl:58).  The reference demands

@@ -48,6 +48,7 @@ SIGNATURES = {
     "sdfl_groupnorm_forward_ex": (_i, [_p, _p, _p, _p, _i64, _i64, _i64, _i64, _f, _i, _i, _p, _sz,
                                        _i, _i, _p]),
     "sdfl_groupnorm_workspace_bytes_ex": (_sz, [_i64, _i64, _i64, _i64, _i, _i, _i]),
+    "sdfl_groupnorm_forward_noalloc": (_i, [_p, _p, _p, _p, _i64, _i64, _i64, _i64, _f, _i, _i, _p]),
     "sdfl_groupnorm_plan": (_i, [_i64, _i64, _i64, _i64, _i, _i, _i, C.POINTER(_i64)]),
     "sdfl_layernorm_forward": (_i, [_p, _p, _p, _p, _i64, _i64, _f, _i, _p]),
     "sdfl_token_embedding": (_i, [_p, _p, _p, _p, _i64, _i64, _i64, _i64, _i, _p, _p]),

@@ -135,6 +135,25 @@ int sdfl_groupnorm_forward_ex(const void *in, void *out, const float *gamma, con
                       workspace, workspace_bytes, path, cluster_or_splits, as_stream(stream));
 }
 
+// GroupNorm(+SiLU) through the split path with the scratch in the library's own fixed device
+// array: for callers that are not allowed to allocate (see sdfl.h).  No allocation is made
+// here or below; shapes whose scratch would exceed the array are refused before any launch.
+int sdfl_groupnorm_forward_noalloc(const void *in, void *out, const float *gamma, const float *beta,
+                                   int64_t batch, int64_t channels, int64_t hw, int64_t num_groups,
+                                   float eps, int fuse_silu, int dtype, void *stream) {
+    int rc = gn_validate(in, out, gamma, beta, batch, channels, hw, num_groups, eps, dtype);
+    if (rc != SDFL_OK) return rc;
+    if (batch == 0 || hw == 0) return SDFL_OK;
+    sdfl::GnShape s{batch, channels, hw, num_groups, dtype, eps,
+                    fuse_silu ? sdfl::kActSilu : sdfl::kActNone};
+    sdfl::GnPlan plan;
+    cudaError_t e = sdfl::gn_make_plan(s, in, out, sdfl::kGnSplit, 0, &plan);
+    if (e == cudaErrorInvalidConfiguration || e == cudaErrorInvalidValue) return SDFL_ERR_UNSUPPORTED;
+    if (e != cudaSuccess) return cuda_fail(e);
+    if (plan.workspace > sdfl::kGnStaticScratchBytes) return SDFL_ERR_WORKSPACE;   // beyond the fixed array
+    return wrap(sdfl::gn_launch_static_scratch(s, plan, in, out, gamma, beta, as_stream(stream)));
+}
+
 int sdfl_groupnorm_plan(int64_t batch, int64_t channels, int64_t hw, int64_t num_groups, int dtype,
                         int path, int cluster_or_splits, int64_t plan[8]) {
     if (!plan) return SDFL_ERR_INVALID_POINTER;

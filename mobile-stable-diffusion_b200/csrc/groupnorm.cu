@@ -1261,6 +1261,45 @@ cudaError_t gn_launch(const GnShape &s, const GnPlan &plan, const void *in, void
     return err;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Split path with its scratch inside the library image (no allocation anywhere)
+// ---------------------------------------------------------------------------------------------
+// Some callers cannot give the split path a workspace because they are not allowed to call an
+// allocator at all: a host that pre-commits every byte of device memory to its own pools at
+// start-up and treats any later cudaMalloc as a bug, a plugin loaded into such a host, or code
+// on a latency-critical thread where an allocator's implicit device synchronisation is not
+// acceptable.  For them the (mean, M2) pairs of the split path live in this fixed array, which
+// every device that loads the library carries until the process exits.
+//
+// g_static_scratch names device memory only inside device code.  On the host the symbol is a
+// stand-in; its device address has to be asked for (cudaGetSymbolAddress) with the right device
+// current, once per device, and that address is what the kernels get.
+static __device__ __align__(256) unsigned char g_static_scratch[kGnStaticScratchBytes];
+
+cudaError_t gn_launch_static_scratch(const GnShape &s, const GnPlan &plan, const void *in, void *out,
+                                     const float *w, const float *b, cudaStream_t stream) {
+    static std::mutex mu;
+    static void *address[kMaxDevices] = {};       // device address of g_static_scratch, per device
+    if (plan.path != kGnSplit || plan.workspace > kGnStaticScratchBytes) return cudaErrorInvalidValue;
+    int dev = 0;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess) return err;
+    if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+    void *ptr = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (address[dev] == nullptr) {
+            // first call on this device: resolve the symbol while this device is current
+            err = cudaGetSymbolAddress(&address[dev], g_static_scratch);
+            if (err != cudaSuccess) { address[dev] = nullptr; return err; }
+        }
+        ptr = address[dev];
+    }
+    // Nothing in the scratch has to start at zero: the statistics kernel overwrites every
+    // (mean, M2) pair the apply kernel reads, and the two run in stream order.
+    return gn_launch(s, plan, in, out, w, b, ptr, stream);
+}
+
 cudaError_t gn_read_status(unsigned int *value, bool clear, cudaStream_t stream) {
     cudaError_t err = cudaMemcpyFromSymbolAsync(value, g_gn_status, sizeof(unsigned int), 0,
                                                 cudaMemcpyDeviceToHost, stream);

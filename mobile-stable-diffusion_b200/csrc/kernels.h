@@ -48,6 +48,13 @@ cudaError_t gn_make_plan(const GnShape &s, const void *in, const void *out, int 
 cudaError_t gn_launch(const GnShape &s, const GnPlan &plan, const void *in, void *out,
                       const float *w, const float *b, void *workspace, cudaStream_t stream);
 
+// The split path with its scratch in a fixed array inside the library (64 KiB per device: up to
+// 8192 (mean, M2) pairs, i.e. batch * groups * chunks-per-slab <= 8192).  Allocates nothing; the
+// first call on a device resolves the array's device address.
+constexpr size_t kGnStaticScratchBytes = 64 * 1024;
+cudaError_t gn_launch_static_scratch(const GnShape &s, const GnPlan &plan, const void *in, void *out,
+                                     const float *w, const float *b, cudaStream_t stream);
+
 // Sticky device-side status word of the GroupNorm kernels (bit 0: a bounded wait on a bulk
 // copy ran out).  Reads it, optionally clears it.
 cudaError_t gn_read_status(unsigned int *value, bool clear, cudaStream_t stream);

@@ -14,7 +14,7 @@ from . import _capi
 from ._capi import F16, F32, GN_AUTO, GN_RESIDENT, GN_SPLIT, GN_STREAM, SdflError, check, lib
 
 __all__ = [
-    "groupnorm", "groupnorm_plan", "layernorm", "gelu_multiply", "silu", "gelu", "quick_gelu",
+    "groupnorm", "groupnorm_noalloc", "groupnorm_plan", "layernorm", "gelu_multiply", "silu", "gelu", "quick_gelu",
     "elemwise_add", "token_embedding", "timestep_embedding", "local_reduction_mean",
     "local_reduction_variance", "group_norm_apply", "layer_norm_apply", "device_status",
     "launch_count", "HostPipeline", "GN_AUTO", "GN_RESIDENT", "GN_SPLIT", "GN_STREAM",
@@ -102,6 +102,28 @@ def groupnorm(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor, num_grou
             _dev(x, "x"), _dev(out, "out"), _f32(gamma, "gamma"), _f32(beta, "beta"), B, Cc, hw,
             num_groups, eps, int(silu), code, ws.data_ptr(), ws.numel(), path, cluster_or_splits,
             _stream(stream)), "sdfl_groupnorm_forward")
+    return out
+
+
+def groupnorm_noalloc(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor, num_groups: int,
+                      eps: float = 1e-5, silu: bool = False, out: torch.Tensor | None = None,
+                      stream=None) -> torch.Tensor:
+    """GroupNorm(+SiLU) through sdfl_groupnorm_forward_noalloc: the library call allocates no
+    device memory (its scratch is a fixed array inside the library), for hosts that forbid
+    allocation after start-up.  `out` should be supplied by such callers; problems whose scratch
+    would not fit the fixed array raise SdflError(ERR_WORKSPACE).  Calls that may overlap on
+    the GPU must be ordered: they share the one scratch array."""
+    if x.dim() < 2:
+        raise ValueError("x must be [batch, channels, ...]")
+    _dev(x, "x")
+    out = torch.empty_like(x) if out is None else out
+    B, Cc = x.shape[0], x.shape[1]
+    hw = x.numel() // (B * Cc) if B * Cc else 0
+    with torch.cuda.device(x.device):
+        check(lib.sdfl_groupnorm_forward_noalloc(
+            _dev(x, "x"), _dev(out, "out"), _f32(gamma, "gamma"), _f32(beta, "beta"), B, Cc, hw,
+            num_groups, eps, int(silu), _dtype_code(x), _stream(stream)),
+            "sdfl_groupnorm_forward_noalloc")
     return out
 
 
