@@ -446,6 +446,128 @@ def run_ours(args) -> None:
         dist.destroy_process_group()
 
 
+
+# ---------------------------------------------------------------------------------------------
+# per-kernel table (--ops) and single cases for profiling (--case NAME)
+# ---------------------------------------------------------------------------------------------
+def op_cases(torch, ops, dev):
+    """Every kernel of the path at the workload's named shapes (BASELINE configs 1-5).
+    Each case: name, algorithmic bytes, a closure that enqueues one launch."""
+    gen = torch.Generator(device=dev).manual_seed(1234)
+
+    def rnd(shape, dtype, scale=1.0):
+        return (torch.randn(shape, device=dev, generator=gen) * scale).to(dtype)
+
+    f16, f32 = torch.float16, torch.float32
+    cases = []
+
+    def gn(name, B, C, H, dtype, eps):
+        x = rnd((B, C, H, H), dtype)
+        y = torch.empty_like(x)
+        g, b = 1 + 0.1 * rnd((C,), f32), 0.1 * rnd((C,), f32)
+        nbytes = 2 * x.numel() * x.element_size() + 2 * C * 4
+        cases.append((name, nbytes, lambda: ops.groupnorm(x, g, b, 32, eps, True, out=y)))
+
+    gn("cfg1 GN+SiLU f32 [1,320,64,64]", 1, 320, 64, f32, 1e-5)
+    for C, H in [(320, 64), (640, 32), (1280, 16), (1280, 8), (640, 64), (960, 64), (960, 32),
+                 (1280, 32), (1920, 32), (1920, 16), (2560, 16), (2560, 8)]:
+        gn(f"cfg3 GN+SiLU f16 [2,{C},{H},{H}]", 2, C, H, f16, 1e-5)
+    for C, H in SHAPES:
+        gn(f"cfg5 GN+SiLU f16 [8,{C},{H},{H}]", 8, C, H, f16, 1e-6)
+    gn("cfg5 GN+SiLU f16 [1,128,512,512] (8-GPU shard)", 1, 128, 512, f16, 1e-6)
+    gn("GN+SiLU f32 [8,256,256,256]", 8, 256, 256, f32, 1e-6)
+
+    def ln(name, rows, D, dtype):
+        x = rnd((rows, D), dtype)
+        y = torch.empty_like(x)
+        g, b = 1 + 0.1 * rnd((D,), f32), 0.1 * rnd((D,), f32)
+        nbytes = 2 * x.numel() * x.element_size() + 2 * D * 4
+        cases.append((name, nbytes, lambda: ops.layernorm(x, g, b, 1e-5, out=y)))
+
+    ln("cfg2 LN f32 [2,77,768]", 154, 768, f32)
+    ln("cfg2 LN f32 [1,77,1024] (reference width)", 77, 1024, f32)
+    ln("cfg4 LN f16 [2,4096,320]", 8192, 320, f16)
+    ln("LN f16 [16,4096,1280] (large)", 65536, 1280, f16)
+    ln("LN f32 [16,4096,320] (large)", 65536, 320, f32)
+
+    def geglu(name, rows, D, dtype):
+        ab = rnd((rows, 2 * D), dtype)
+        y = torch.empty((rows, D), device=dev, dtype=dtype)
+        nbytes = 3 * rows * D * ab.element_size()
+        cases.append((name, nbytes, lambda: ops.gelu_multiply(ab, out=y)))
+
+    geglu("cfg4 GEGLU f16 [2,4096,2560]->[2,4096,1280]", 8192, 1280, f16)
+    geglu("GEGLU f16 [16,4096,2560] (large)", 65536, 1280, f16)
+    geglu("GEGLU f32 [8,4096,2560] (large)", 32768, 1280, f32)
+
+    def act(name, fn, n, dtype):
+        x = rnd((n,), dtype)
+        y = torch.empty_like(x)
+        cases.append((name, 2 * n * x.element_size(), lambda: fn(x, out=y)))
+
+    act("cfg2 quick_gelu f32 [2,77,3072]", ops.quick_gelu, 2 * 77 * 3072, f32)
+    act("cfg2 gelu(erf) f32 [2,77,3072]", ops.gelu, 2 * 77 * 3072, f32)
+    act("cfg4 SiLU f16 [2,1280]", ops.silu, 2 * 1280, f16)
+    act("SiLU f16 256M elements (large)", ops.silu, 1 << 28, f16)
+    act("gelu(erf) f32 128M elements (large)", ops.gelu, 1 << 27, f32)
+    act("quick_gelu f16 256M elements (large)", ops.quick_gelu, 1 << 28, f16)
+
+    for D in (768, 1024):
+        table = rnd((49408, D), f32, 0.02)
+        pos = rnd((77, D), f32, 0.02)
+        ids = torch.randint(0, 49408, (2, 77), device=dev, generator=gen, dtype=torch.int64)
+        out = torch.empty((2, 77, D), device=dev, dtype=f32)
+        nbytes = 2 * 77 * 8 + 2 * (2 * 77 * D * 4) + 77 * D * 4
+        cases.append((f"cfg2 token+pos embedding f32 [2,77]->[2,77,{D}]", nbytes,
+                      lambda ids=ids, table=table, pos=pos, out=out: ops.token_embedding(ids, table, pos, out=out)))
+    t = torch.randint(0, 1000, (2,), device=dev, generator=gen, dtype=torch.int64)
+    emb = torch.empty((2, 320), device=dev, dtype=f16)
+    cases.append(("cfg4 timestep embedding f16 [2]->[2,320]", 2 * 8 + 2 * 320 * 2,
+                  lambda: ops.timestep_embedding(t, 320, out=emb)))
+    a_, b_ = rnd((1 << 27,), f32), rnd((1 << 27,), f32)
+    c_ = torch.empty_like(a_)
+    cases.append(("elemwise_add f32 128M elements (large)", 3 * (1 << 27) * 4,
+                  lambda: ops.elemwise_add(a_, b_, out=c_)))
+    return cases
+
+
+def run_ops(args) -> None:
+    """--ops: one JSON line per kernel/shape (device time per launch with L2 flushed, GB/s of
+    algorithmic bytes, fraction of the measured HBM peak).  --case SUBSTRING: run only the
+    matching cases, `--steps` launches each (the form used under ncu)."""
+    import torch
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the kernels have no CPU fallback")
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    pkg = importlib.import_module("mobile-stable-diffusion_b200")
+    ops = pkg.ops
+    peak, peak_kind = measured_peak()
+    flush = torch.empty(2 * L2_BYTES, dtype=torch.uint8, device=dev)
+    reps = max(args.steps, 1) if args.case else 9
+    for name, nbytes, fn in op_cases(torch, ops, dev):
+        if args.case and args.case not in name:
+            continue
+        for _ in range(max(args.warmup, 1)):
+            fn()
+        times = []
+        for _ in range(reps):
+            flush.fill_(1)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize(dev)
+            times.append(a.elapsed_time(b))
+        t = statistics.median(times)
+        gbs = nbytes / (t * 1e-3) / 1e9
+        print(json.dumps({"case": name, "bytes": nbytes, "us": round(t * 1e3, 2), "gbs": round(gbs, 1),
+                          "frac_of_peak": round(gbs / peak, 4), "peak": peak, "peak_source": f"of {peak_kind}",
+                          "timing": "CUDA events around one launch, L2 flushed before it, median"}),
+              flush=True)
+    assert ops.device_status() == 0
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -453,9 +575,13 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--ops", action="store_true", help="per-kernel table over all named shapes")
+    ap.add_argument("--case", default="", help="with --ops: only cases whose name contains this")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.ops or args.case:
+        run_ops(args)
     else:
         run_ours(args)
 

@@ -362,7 +362,7 @@ struct ResidentArgs {
 //   otherwise the chunks are released after the moments pass and loaded a second time for the
 //             normalise pass (this second read is served by L2 when the clusters' slabs fit it).
 template <typename T, int ACT, bool BIG, bool MMA>
-__global__ void __launch_bounds__(BIG ? 1024 : 512, BIG ? 1 : 3)
+__global__ void __launch_bounds__(BIG ? 1024 : 512, BIG ? 1 : 2)
 gn_resident_kernel(const ResidentArgs a) {
     constexpr int VEC = VecOf<T>::N;
     constexpr bool HALF = sizeof(T) == 2;
@@ -411,12 +411,14 @@ gn_resident_kernel(const ResidentArgs a) {
         for (uint32_t unit = cluster_id; unit < a.units; unit += nclusters, ++it) {
             // Take part in the consumers' one cluster barrier per slab without ever blocking
             // ahead of them: arrive for slab `it` now, wait for it before the next arrive.
-            if (it > 0) cluster.barrier_wait();
-            cluster.barrier_arrive();
+            if (!(a.dbg & 32u)) {
+                if (it > 0) cluster.barrier_wait();
+                cluster.barrier_arrive();
+            }
             if (lane == 0) {
                 const unsigned char *gsrc = static_cast<const unsigned char *>(a.in) +
                                             (static_cast<size_t>(unit) * a.slab_vecs + v0) * 16u;
-                const uint32_t loads = resident ? nchunks : 2u * nchunks;
+                const uint32_t loads = (resident || (a.dbg & 16u)) ? nchunks : 2u * nchunks;
                 for (uint32_t l = 0; l < loads; ++l, ++n) {
                     const uint32_t j = l < nchunks ? l : l - nchunks;
                     if (round > 0) {
@@ -436,7 +438,7 @@ gn_resident_kernel(const ResidentArgs a) {
             }
             __syncwarp();
         }
-        if (it > 0) cluster.barrier_wait();
+        if (it > 0 && !(a.dbg & 32u)) cluster.barrier_wait();
         if (timed_out && lane == 0) atomicOr(&g_gn_status, 1u);
         cluster.sync();                      // nobody leaves while peers may read its moments
         return;
@@ -457,7 +459,7 @@ gn_resident_kernel(const ResidentArgs a) {
         uint32_t nvec_mine = 0;
         MmaMoments mm;
         if (MMA) mm.clear();
-        for (uint32_t j = 0; j < nchunks; ++j) {
+        for (uint32_t j = 0; j < ((a.dbg & 16u) ? 0u : nchunks); ++j) {
             if (!mbar_wait_bounded(smem_addr(&full[slot]), round & 1u,
                                    timed_out ? kWaitCyclesAfterTimeout : kWaitCycles))
                 timed_out = true;
@@ -480,6 +482,7 @@ gn_resident_kernel(const ResidentArgs a) {
                     nvec_mine += valid ? 1u : 0u;
                 }
             } else if (!(a.dbg & 4u)) {
+#pragma unroll 2
                 for (uint32_t i = tid; i < cnt; i += consumers) {
                     stats_vec<T>(sv[i], shift, s, q);
                     ++nvec_mine;
@@ -520,7 +523,7 @@ gn_resident_kernel(const ResidentArgs a) {
                 pub[2 * par + 1] = t.m2;
             }
         }
-        cluster.sync();                       // every CTA's moments of this slab are published
+        if (!(a.dbg & 32u)) cluster.sync();   // every CTA's moments of this slab are published
         if (warp == 0) {
             Moments t{0.f, 0.f, 0.f};
             if (lane < csize) {
@@ -566,6 +569,7 @@ gn_resident_kernel(const ResidentArgs a) {
                     const uint32_t seg_end = min(hi, (c + 1) * hwv - v0);
                     const Affine<T> af = make_affine<T, ACT>(mean, rstd, __ldg(a.w + ch0 + c),
                                                             __ldg(a.b + ch0 + c));
+#pragma unroll 2
                     for (uint32_t i = i0 + tid; i < seg_end; i += consumers)
                         st_stream(&gv[i], norm_vec<T, ACT>(sv[i - lo], af));
                     i0 = seg_end;
@@ -1114,7 +1118,7 @@ cudaError_t gn_make_plan(const GnShape &s, const void *in, const void *out, int 
 
     if (resident_ok) {
         // Ring geometry and cluster size, from sweeps on B200 (fp16 and fp32 behave alike per
-        // byte).  A small ring (3 slots of 16-32 KB, 7 consumer warps) with the second read
+        // byte).  A small ring (3 slots of 16-32 KB, 7-11 consumer warps) with the second read
         // served by L2 beats full shared-memory residency at every size tried: it keeps 2-4 CTAs
         // on each SM, so one CTA's cluster exchange hides behind the others' traffic.  The
         // cluster grows with the slab so that the slabs in flight (clusters x slab bytes) stay
@@ -1144,7 +1148,8 @@ cudaError_t gn_make_plan(const GnShape &s, const void *in, const void *out, int 
             }
             if (nslots < chunks && nslots < 2) { if (k_cluster > 0) break; continue; }
             const size_t smem = kHeaderBytes + static_cast<size_t>(nslots * chunk_bytes);
-            int consumers = k_cwarps > 0 ? k_cwarps * 32 : (part_bytes >= 8 * 1024 ? 224 : 96);
+            int consumers = k_cwarps > 0 ? k_cwarps * 32
+                                         : (part_bytes >= 256 * 1024 ? 352 : part_bytes >= 8 * 1024 ? 224 : 96);
             if (consumers > 992) consumers = 992;
             const int threads = consumers + 32;
             int active = 0;
