@@ -475,6 +475,7 @@ def op_cases(torch, ops, dev):
     for C, H in SHAPES:
         gn(f"cfg5 GN+SiLU f16 [8,{C},{H},{H}]", 8, C, H, f16, 1e-6)
     gn("cfg5 GN+SiLU f16 [1,128,512,512] (8-GPU shard)", 1, 128, 512, f16, 1e-6)
+    gn("profiling size GN+SiLU f16 [4,128,512,512]", 4, 128, 512, f16, 1e-6)
     gn("GN+SiLU f32 [8,256,256,256]", 8, 256, 256, f32, 1e-6)
 
     def ln(name, rows, D, dtype):

@@ -1128,7 +1128,8 @@ cudaError_t gn_make_plan(const GnShape &s, const void *in, const void *out, int 
         const int k_chunk_kb = (force_cluster >> 16) & 0xff, k_cwarps = (force_cluster >> 24) & 0x3f;
         int c = slab_bytes <= 192 * 1024 ? 2 : slab_bytes <= 768 * 1024 ? 4 : 8;
         const int64_t want_ctas = 2 * kSmCount;
-        while (c < 16 && units * c < want_ctas && slab_bytes / (2 * c) >= 8 * 1024) c *= 2;
+        // (not beyond 8: only about half as many 16-CTA clusters can be co-resident)
+        while (c < 8 && units * c < want_ctas && slab_bytes / (2 * c) >= 8 * 1024) c *= 2;
         while (c > 1 && slab_bytes / c < 8 * 1024) c /= 2;
         if (k_cluster > 0) c = k_cluster;
         if (c > 16) c = 16;

@@ -18,8 +18,14 @@ namespace {
 constexpr int kLnThreads = 256;
 constexpr int kLnWarps = kLnThreads / 32;
 
-template <typename T, int MAXV>
-__global__ void __launch_bounds__(kLnThreads)
+// PREFETCH: the next row of the warp is already on its way into a second register set while
+// the current one is reduced and written, so two rows per warp are in flight (the kernel is
+// bound by load latency otherwise).  Only for short rows, where the registers allow it.
+// Register budget: the more row vectors a lane holds, the fewer CTAs share an SM.
+constexpr int ln_min_blocks(int maxv) { return maxv <= 3 ? 6 : maxv <= 6 ? 4 : maxv <= 8 ? 3 : 2; }
+
+template <typename T, int MAXV, bool PREFETCH>
+__global__ void __launch_bounds__(kLnThreads, ln_min_blocks(MAXV))
 ln_warp_kernel(const T *__restrict__ in, T *__restrict__ out, const float *__restrict__ w,
                const float *__restrict__ b, long long rows, int nvec, int dim, float eps) {
     constexpr int VEC = VecOf<T>::N;
@@ -27,15 +33,32 @@ ln_warp_kernel(const T *__restrict__ in, T *__restrict__ out, const float *__res
     const long long warp0 = static_cast<long long>(blockIdx.x) * kLnWarps + (threadIdx.x >> 5);
     const long long nwarps = static_cast<long long>(gridDim.x) * kLnWarps;
     const float inv_d = 1.0f / static_cast<float>(dim);
-    for (long long row = warp0; row < rows; row += nwarps) {
+    uint4 v[MAXV], nxt[PREFETCH ? MAXV : 1];
+
+    auto load_row = [&](uint4 (&dst)[MAXV], long long row) {
         const uint4 *xr = reinterpret_cast<const uint4 *>(in + row * dim);
-        uint4 *yr = reinterpret_cast<uint4 *>(out + row * dim);
-        uint4 v[MAXV];
 #pragma unroll
         for (int i = 0; i < MAXV; ++i) {
             const int idx = lane + 32 * i;
-            if (idx < nvec) v[i] = ld_stream(xr + idx);
+            if (idx < nvec) dst[i] = ld_stream(xr + idx);
         }
+    };
+
+    if (warp0 < rows) load_row(v, warp0);
+    for (long long row = warp0; row < rows; row += nwarps) {
+        if (PREFETCH) {
+            if (row + nwarps < rows) {
+                const uint4 *xr = reinterpret_cast<const uint4 *>(in + (row + nwarps) * dim);
+#pragma unroll
+                for (int i = 0; i < MAXV; ++i) {
+                    const int idx = lane + 32 * i;
+                    if (idx < nvec) nxt[i] = ld_stream(xr + idx);
+                }
+            }
+        } else if (row != warp0) {
+            load_row(v, row);
+        }
+        uint4 *yr = reinterpret_cast<uint4 *>(out + row * dim);
         float s = 0.f;
 #pragma unroll
         for (int i = 0; i < MAXV; ++i) {
@@ -81,6 +104,10 @@ ln_warp_kernel(const T *__restrict__ in, T *__restrict__ out, const float *__res
                 st_stream(yr + idx, pack<T>(f));
             }
         }
+        if (PREFETCH) {
+#pragma unroll
+            for (int i = 0; i < MAXV; ++i) v[i] = nxt[i];
+        }
     }
 }
 
@@ -115,7 +142,7 @@ void launch_warp(const void *in, void *out, const float *w, const float *b, int6
     int64_t blocks = (rows + kLnWarps - 1) / kLnWarps;
     const int64_t cap = 148 * 8 * 4;
     if (blocks > cap) blocks = cap;
-    ln_warp_kernel<T, MAXV><<<static_cast<unsigned>(blocks), kLnThreads, 0, stream>>>(
+    ln_warp_kernel<T, MAXV, false><<<static_cast<unsigned>(blocks), kLnThreads, 0, stream>>>(
         static_cast<const T *>(in), static_cast<T *>(out), w, b, rows, nvec, dim, eps);
 }
 
@@ -133,8 +160,12 @@ cudaError_t ln_dispatch(const void *in, void *out, const float *w, const float *
         const int nv = static_cast<int>(nvec), d = static_cast<int>(dim);
         if (need <= 1) launch_warp<T, 1>(in, out, w, b, rows, nv, d, eps, stream);
         else if (need <= 2) launch_warp<T, 2>(in, out, w, b, rows, nv, d, eps, stream);
+        else if (need <= 3) launch_warp<T, 3>(in, out, w, b, rows, nv, d, eps, stream);
         else if (need <= 4) launch_warp<T, 4>(in, out, w, b, rows, nv, d, eps, stream);
+        else if (need <= 5) launch_warp<T, 5>(in, out, w, b, rows, nv, d, eps, stream);
+        else if (need <= 6) launch_warp<T, 6>(in, out, w, b, rows, nv, d, eps, stream);
         else if (need <= 8) launch_warp<T, 8>(in, out, w, b, rows, nv, d, eps, stream);
+        else if (need <= 10) launch_warp<T, 10>(in, out, w, b, rows, nv, d, eps, stream);
         else if (need <= 12) launch_warp<T, 12>(in, out, w, b, rows, nv, d, eps, stream);
         else launch_warp<T, 16>(in, out, w, b, rows, nv, d, eps, stream);
     } else {
