@@ -43,8 +43,12 @@ EPS = 1e-6
 L2_BYTES = 126 * 1024 * 1024
 PEAK_FALLBACK_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel divided by
-# its algorithmic bytes, from the ncu capture summarised under profiles/ (None until captured).
-NCU_TRAFFIC_RATIO = None
+# its algorithmic bytes, from the ncu capture of [4,128,512,512] fp16 summarised in
+# profiles/gn_resident_kernel_half_silu_4x128x512x512.md: 291.7 MB read + 210.4 MB written for
+# 536.9 MB algorithmic (reads 1.09x the input; part of the output is still dirty in L2 when
+# the kernel ends).  Traffic grows in proportion to the slabs processed, so the per-launch
+# figure reported is this ratio times the launch's algorithmic bytes.
+NCU_TRAFFIC_RATIO = 0.935
 
 
 def algorithmic_bytes(batch: int, C: int, H: int, esz: int = 2) -> int:

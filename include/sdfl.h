@@ -44,7 +44,7 @@ enum {
 };
 
 /* GroupNorm path selection for sdfl_groupnorm_forward_ex (tests and sweeps). */
-enum { SDFL_GN_AUTO = 0, SDFL_GN_RESIDENT = 1, SDFL_GN_SPLIT = 2, SDFL_GN_STREAM = 3 };
+enum { SDFL_GN_AUTO = 0, SDFL_GN_RESIDENT = 1, SDFL_GN_SPLIT = 2 };
 
 const char *sdfl_version(void);
 const char *sdfl_status_string(int status);

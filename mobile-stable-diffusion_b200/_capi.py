@@ -12,7 +12,7 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(PKG, "lib", "libsdfl.so")
 
 F32, F16 = 0, 1
-GN_AUTO, GN_RESIDENT, GN_SPLIT, GN_STREAM = 0, 1, 2, 3
+GN_AUTO, GN_RESIDENT, GN_SPLIT = 0, 1, 2
 
 OK = 0
 ERR_INVALID_VALUE = -1

@@ -62,7 +62,7 @@ int gn_forward(const void *in, void *out, const float *gamma, const float *beta,
     int rc = gn_validate(in, out, gamma, beta, batch, channels, hw, groups, eps, dtype);
     if (rc != SDFL_OK) return rc;
     if (batch == 0 || hw == 0) return SDFL_OK;
-    if (path < SDFL_GN_AUTO || path > SDFL_GN_STREAM || cluster < 0) return SDFL_ERR_INVALID_VALUE;
+    if (path < SDFL_GN_AUTO || path > SDFL_GN_SPLIT || cluster < 0) return SDFL_ERR_INVALID_VALUE;
     sdfl::GnShape s{batch, channels, hw, groups, dtype, eps,
                     fuse_silu ? sdfl::kActSilu : sdfl::kActNone};
     sdfl::GnPlan plan;
@@ -159,7 +159,7 @@ int sdfl_groupnorm_plan(int64_t batch, int64_t channels, int64_t hw, int64_t num
     if (!plan) return SDFL_ERR_INVALID_POINTER;
     for (int i = 0; i < 8; ++i) plan[i] = 0;
     if (!dtype_ok(dtype) || batch < 0 || channels <= 0 || hw < 0 || num_groups <= 0 ||
-        channels % num_groups != 0 || path < SDFL_GN_AUTO || path > SDFL_GN_STREAM ||
+        channels % num_groups != 0 || path < SDFL_GN_AUTO || path > SDFL_GN_SPLIT ||
         cluster_or_splits < 0)
         return SDFL_ERR_INVALID_VALUE;
     if (hw >= (1ll << 31) || (channels / num_groups) * hw >= (1ll << 31) ||

@@ -8,18 +8,24 @@
 // reference: a batch dimension (slab = one (image, group) pair; weight index wraps per image)
 // and fp16 storage.
 //
-// Resident path (gn_resident_kernel).  The slab of one (image, group) is contiguous in NCHW
+// Cluster path (gn_resident_kernel).  The slab of one (image, group) is contiguous in NCHW
 // (C/G * H*W elements).  A persistent thread-block cluster of 1..16 CTAs walks over slabs; each
-// CTA keeps its share of the current slab in shared memory as a ring of chunks:
+// CTA owns a fixed share of every slab and moves it through a small shared-memory ring of
+// chunk slots:
 //   producer warp : cp.async.bulk (bulk-copy engine) global -> shared, one "full" mbarrier per
-//                   chunk; a chunk is refilled with the NEXT slab's data as soon as the consumer
-//                   warps have released it ("empty" mbarrier), so the next slab streams in
-//                   while the current one is being normalised and stored.
+//                   slot; a slot is refilled as soon as the consumer warps have released it
+//                   ("empty" mbarrier), also across slab boundaries, so loads never drain.
 //   consumer warps: (1) as chunks land, one pass of shifted sums -> per-thread (n, mean, M2),
 //                   merged with Chan's update through warp shuffles, a block merge, and a
 //                   cluster merge over distributed shared memory; (2) normalise + affine
 //                   (+ SiLU) from shared memory straight to global, 16-byte streaming stores.
-// Nothing of a slab is written before the whole slab is resident, so out == in is safe.
+// If a CTA's share fits the ring it stays resident between (1) and (2).  Otherwise -- the
+// normal case for large slabs, and the faster one on B200 because several CTAs then share an
+// SM -- the chunks are loaded a second time for (2): the first load carries an L2 evict_last
+// hint, the clusters in flight hold a few tens of MB, and the second load is served by L2
+// (measured: DRAM reads = 1.00-1.07x the tensor).  HBM therefore sees one read and one write.
+// Every output chunk is written only after the whole slab has been read for (1) and the chunk
+// itself has been read again for (2), so out == in is safe.
 //
 // Split path: any shape.  Kernel 1 writes one (mean, M2) pair per chunk to a scratch buffer;
 // kernel 2 merges the chunk pairs of its slab in a fixed order and normalises.
@@ -28,7 +34,6 @@
 
 #include <cooperative_groups.h>
 
-#include <cstdlib>
 #include <map>
 #include <mutex>
 
@@ -243,49 +248,6 @@ __device__ __forceinline__ void stats_vec<__half>(const uint4 &v, float shift, f
     stats_half2(v.w, shift, s, q);
 }
 
-// Moments of fp16 data on the tensor pipe (legacy warp-level MMA): the data vector of each lane
-// is one A fragment of a 16x16 tile.  With B = ones the accumulator holds row sums; with B
-// built from the same registers (rows 0-7, then rows 8-15, of A transposed) the accumulator's
-// diagonal holds the rows' sums of squares.  Three MMAs replace 24 scalar instructions per
-// lane; products of fp16 values are exact in the fp32 accumulator.
-__device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
-                                          uint32_t a3, uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
-        "{%0,%1,%2,%3};"
-        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-struct MmaMoments {
-    float sum[4], sq_lo[4], sq_hi[4];
-    __device__ __forceinline__ void clear() {
-#pragma unroll
-        for (int i = 0; i < 4; ++i) sum[i] = sq_lo[i] = sq_hi[i] = 0.f;
-    }
-    // v: 8 fp16 lanes; shift2: the shift replicated in both halves.  Every lane of the warp
-    // must call this together (lanes without data pass v = shift pattern -> zeros).
-    __device__ __forceinline__ void add(const uint4 &v, uint32_t shift2) {
-        const __half2 k = *reinterpret_cast<const __half2 *>(&shift2);
-        const __half2 d0 = __hsub2(*reinterpret_cast<const __half2 *>(&v.x), k);
-        const __half2 d1 = __hsub2(*reinterpret_cast<const __half2 *>(&v.y), k);
-        const __half2 d2 = __hsub2(*reinterpret_cast<const __half2 *>(&v.z), k);
-        const __half2 d3 = __hsub2(*reinterpret_cast<const __half2 *>(&v.w), k);
-        const uint32_t a0 = *reinterpret_cast<const uint32_t *>(&d0), a1 = *reinterpret_cast<const uint32_t *>(&d1);
-        const uint32_t a2 = *reinterpret_cast<const uint32_t *>(&d2), a3 = *reinterpret_cast<const uint32_t *>(&d3);
-        mma_16816(sum, a0, a1, a2, a3, 0x3C003C00u, 0x3C003C00u);   // B = ones
-        mma_16816(sq_lo, a0, a1, a2, a3, a0, a2);                   // B[k][n] = A[n][k]
-        mma_16816(sq_hi, a0, a1, a2, a3, a1, a3);                   // B[k][n] = A[8 + n][k]
-    }
-    // This lane's share of sum(d) and sum(d*d): row sums sit in the lanes with t == 0, the
-    // diagonal entries in the lane with t == g / 2 (g = lane / 4, t = lane % 4).
-    __device__ __forceinline__ void extract(uint32_t lane, float &s, float &q) const {
-        const uint32_t g = lane >> 2, t = lane & 3u;
-        s = t == 0 ? sum[0] + sum[2] : 0.f;
-        q = t == (g >> 1) ? ((g & 1u) ? sq_lo[1] + sq_hi[3] : sq_lo[0] + sq_hi[2]) : 0.f;
-    }
-};
-
 // Per-channel constants of the normalise pass.
 //   fp32 storage: the reference's operation order, y = fma((x - mean) * rstd, w, b).
 //   fp16 storage: folded, y = fma(x, sc, sh) with sc = w * rstd, sh = b - mean * sc; with SiLU
@@ -340,7 +302,6 @@ struct ResidentArgs {
     uint32_t groups;
     uint32_t chunk_vecs;   // vectors per ring chunk
     uint32_t nslots;       // chunk slots in the shared-memory ring
-    uint32_t dbg;          // experiment switches (0 in production)
     uint32_t vec_uniform;  // hw % lanes-per-vector == 0
     uint32_t hw_vecs;      // hw / lanes-per-vector (when vec_uniform)
     float eps;
@@ -361,7 +322,7 @@ struct ResidentArgs {
 //             with the next slab's chunks meanwhile.
 //   otherwise the chunks are released after the moments pass and loaded a second time for the
 //             normalise pass (this second read is served by L2 when the clusters' slabs fit it).
-template <typename T, int ACT, bool BIG, bool MMA>
+template <typename T, int ACT, bool BIG>
 __global__ void __launch_bounds__(BIG ? 1024 : 512, BIG ? 1 : 2)
 gn_resident_kernel(const ResidentArgs a) {
     constexpr int VEC = VecOf<T>::N;
@@ -411,14 +372,12 @@ gn_resident_kernel(const ResidentArgs a) {
         for (uint32_t unit = cluster_id; unit < a.units; unit += nclusters, ++it) {
             // Take part in the consumers' one cluster barrier per slab without ever blocking
             // ahead of them: arrive for slab `it` now, wait for it before the next arrive.
-            if (!(a.dbg & 32u)) {
-                if (it > 0) cluster.barrier_wait();
-                cluster.barrier_arrive();
-            }
+            if (it > 0) cluster.barrier_wait();
+            cluster.barrier_arrive();
             if (lane == 0) {
                 const unsigned char *gsrc = static_cast<const unsigned char *>(a.in) +
                                             (static_cast<size_t>(unit) * a.slab_vecs + v0) * 16u;
-                const uint32_t loads = (resident || (a.dbg & 16u)) ? nchunks : 2u * nchunks;
+                const uint32_t loads = resident ? nchunks : 2u * nchunks;
                 for (uint32_t l = 0; l < loads; ++l, ++n) {
                     const uint32_t j = l < nchunks ? l : l - nchunks;
                     if (round > 0) {
@@ -438,7 +397,7 @@ gn_resident_kernel(const ResidentArgs a) {
             }
             __syncwarp();
         }
-        if (it > 0 && !(a.dbg & 32u)) cluster.barrier_wait();
+        if (it > 0) cluster.barrier_wait();
         if (timed_out && lane == 0) atomicOr(&g_gn_status, 1u);
         cluster.sync();                      // nobody leaves while peers may read its moments
         return;
@@ -455,38 +414,18 @@ gn_resident_kernel(const ResidentArgs a) {
         // pass 1: shifted sums, chunk by chunk as the copies land
         float s[2] = {0.f, 0.f}, q[2] = {0.f, 0.f};
         float shift = 0.f;
-        uint32_t shift2 = 0;
         uint32_t nvec_mine = 0;
-        MmaMoments mm;
-        if (MMA) mm.clear();
-        for (uint32_t j = 0; j < ((a.dbg & 16u) ? 0u : nchunks); ++j) {
+        for (uint32_t j = 0; j < nchunks; ++j) {
             if (!mbar_wait_bounded(smem_addr(&full[slot]), round & 1u,
                                    timed_out ? kWaitCyclesAfterTimeout : kWaitCycles))
                 timed_out = true;
             const uint4 *sv = reinterpret_cast<const uint4 *>(data + slot * chunk_bytes);
-            if (j == 0) {
-                shift = to_float<T>(reinterpret_cast<const T *>(sv)[0]);
-                if (MMA) {
-                    const uint32_t h = *reinterpret_cast<const unsigned short *>(sv);
-                    shift2 = h | (h << 16);
-                }
-            }
+            if (j == 0) shift = to_float<T>(reinterpret_cast<const T *>(sv)[0]);
             const uint32_t cnt = min(cv, nv - j * cv);
-            if (MMA) {
-                // warp-uniform trip count: every lane takes part in every MMA
-                for (uint32_t base = warp * 32u; base < cnt; base += consumers) {
-                    const uint32_t i = base + lane;
-                    const bool valid = i < cnt;
-                    const uint4 v = valid ? sv[i] : make_uint4(shift2, shift2, shift2, shift2);
-                    mm.add(v, shift2);
-                    nvec_mine += valid ? 1u : 0u;
-                }
-            } else if (!(a.dbg & 4u)) {
 #pragma unroll 2
-                for (uint32_t i = tid; i < cnt; i += consumers) {
-                    stats_vec<T>(sv[i], shift, s, q);
-                    ++nvec_mine;
-                }
+            for (uint32_t i = tid; i < cnt; i += consumers) {
+                stats_vec<T>(sv[i], shift, s, q);
+                ++nvec_mine;
             }
             if (!resident) {
                 __syncwarp();
@@ -495,17 +434,7 @@ gn_resident_kernel(const ResidentArgs a) {
             if (++slot == nslots) { slot = 0; ++round; }
         }
         Moments m;
-        if (MMA) {
-            // sums belong to tile rows, not to lanes: fold the warp's plain sums first
-            float ss, qq;
-            mm.extract(lane, ss, qq);
-            ss = warp_sum(ss);
-            qq = warp_sum(qq);
-            const float cnt = warp_sum(static_cast<float>(nvec_mine * VEC));
-            m.n = lane == 0 ? cnt : 0.f;
-            m.mean = cnt > 0.f ? shift + ss / cnt : 0.f;
-            m.m2 = cnt > 0.f ? fmaxf(qq - ss * ss / cnt, 0.f) : 0.f;
-        } else {
+        {
             const float cnt = static_cast<float>(nvec_mine * VEC);
             const float ss = s[0] + s[1], qq = q[0] + q[1];
             m.n = cnt;
@@ -523,7 +452,7 @@ gn_resident_kernel(const ResidentArgs a) {
                 pub[2 * par + 1] = t.m2;
             }
         }
-        if (!(a.dbg & 32u)) cluster.sync();   // every CTA's moments of this slab are published
+        cluster.sync();                       // every CTA's moments of this slab are published
         if (warp == 0) {
             Moments t{0.f, 0.f, 0.f};
             if (lane < csize) {
@@ -559,9 +488,7 @@ gn_resident_kernel(const ResidentArgs a) {
             const uint4 *sv = reinterpret_cast<const uint4 *>(data + slot * chunk_bytes);
             const uint32_t lo = j * cv;                 // part-relative vector index of the chunk
             const uint32_t hi = min(nv, lo + cv);
-            if (a.dbg & 8u) {
-                for (uint32_t i = lo + tid; i < hi; i += consumers) st_stream(&gv[i], sv[i - lo]);
-            } else if (a.vec_uniform && hwv >= consumers) {
+            if (a.vec_uniform && hwv >= consumers) {
                 // long channels: walk channel by channel, weights hoisted out of the vector loop
                 uint32_t i0 = lo;
                 while (i0 < hi) {
@@ -601,146 +528,6 @@ gn_resident_kernel(const ResidentArgs a) {
     }
     if (timed_out && lane == 0) atomicOr(&g_gn_status, 1u);
     cluster.sync();                           // nobody leaves while peers may read its moments
-}
-
-// ---------------------------------------------------------------------------------------------
-// Streaming path: the slab is read twice, the second time from L2
-// ---------------------------------------------------------------------------------------------
-// For slabs whose share per CTA does not leave room for a second CTA on the SM, shared-memory
-// residency serialises load, statistics and store.  Here a persistent cluster streams its slab
-// from HBM once for the moments (normal caching, so the lines stay in L2), merges over the
-// cluster, and reads it again for the normalise pass while the lines are still in L2 (a
-// cluster's slab is a few MB; all resident clusters together hold far less than the L2).
-// No shared-memory capacity limit: several CTAs per SM at any slab size.  Every vector is
-// read and then written by the same thread, so out == in is safe.
-constexpr int kStreamThreads = 512;
-
-template <typename T, int ACT>
-__global__ void __launch_bounds__(kStreamThreads, 3)
-gn_stream_kernel(const ResidentArgs a) {
-    constexpr int VEC = VecOf<T>::N;
-    constexpr bool HALF = sizeof(T) == 2;
-    cg::cluster_group cluster = cg::this_cluster();
-    const uint32_t csize = cluster.num_blocks();
-    const uint32_t rank = cluster.block_rank();
-    const uint32_t cluster_id = blockIdx.x / csize;
-    const uint32_t nclusters = gridDim.x / csize;
-    const uint32_t tid = threadIdx.x;
-    const uint32_t lane = tid & 31u, warp = tid >> 5;
-    constexpr uint32_t kWarps = kStreamThreads / 32;
-
-    __shared__ Moments warp_m[kWarps];
-    __shared__ float bcast[2];
-    __shared__ float pub[4];
-
-    const uint32_t v0 = static_cast<uint32_t>((static_cast<uint64_t>(a.slab_vecs) * rank) / csize);
-    const uint32_t v1 = static_cast<uint32_t>((static_cast<uint64_t>(a.slab_vecs) * (rank + 1)) / csize);
-    const uint32_t nv = v1 - v0;
-    const uint32_t hwv = a.hw_vecs;
-
-    uint32_t it = 0;
-    for (uint32_t unit = cluster_id; unit < a.units; unit += nclusters, ++it) {
-        const uint32_t par = it & 1u;
-        const size_t off = (static_cast<size_t>(unit) * a.slab_vecs + v0) * 16u;
-        const uint4 *gx = reinterpret_cast<const uint4 *>(static_cast<const unsigned char *>(a.in) + off);
-        uint4 *gy = reinterpret_cast<uint4 *>(static_cast<unsigned char *>(a.out) + off);
-
-        // pass 1 (HBM): shifted sums
-        const float shift = to_float<T>(*reinterpret_cast<const T *>(gx));
-        float s[2] = {0.f, 0.f}, q[2] = {0.f, 0.f};
-        uint32_t mine = 0;
-        uint32_t i = tid;
-        for (; i + 3 * kStreamThreads < nv; i += 4 * kStreamThreads) {
-            const uint4 x0 = gx[i], x1 = gx[i + kStreamThreads];
-            const uint4 x2 = gx[i + 2 * kStreamThreads], x3 = gx[i + 3 * kStreamThreads];
-            stats_vec<T>(x0, shift, s, q);
-            stats_vec<T>(x1, shift, s, q);
-            stats_vec<T>(x2, shift, s, q);
-            stats_vec<T>(x3, shift, s, q);
-            mine += 4;
-        }
-        for (; i < nv; i += kStreamThreads) {
-            stats_vec<T>(gx[i], shift, s, q);
-            ++mine;
-        }
-        Moments m;
-        {
-            const float cnt = static_cast<float>(mine * VEC);
-            const float ss = s[0] + s[1], qq = q[0] + q[1];
-            m.n = cnt;
-            m.mean = mine ? shift + ss / cnt : 0.f;
-            m.m2 = mine ? fmaxf(qq - ss * ss / cnt, 0.f) : 0.f;
-        }
-        m = warp_merge(m);
-        if (lane == 0) warp_m[warp] = m;
-        __syncthreads();
-        if (warp == 0) {
-            Moments t = lane < kWarps ? warp_m[lane] : Moments{0.f, 0.f, 0.f};
-            t = warp_merge(t);
-            if (lane == 0) {
-                pub[2 * par] = t.mean;
-                pub[2 * par + 1] = t.m2;
-            }
-        }
-        cluster.sync();
-        if (warp == 0) {
-            Moments t{0.f, 0.f, 0.f};
-            if (lane < csize) {
-                const float *peer = cluster.map_shared_rank(pub, lane);
-                const uint32_t p0 = static_cast<uint32_t>((static_cast<uint64_t>(a.slab_vecs) * lane) / csize);
-                const uint32_t p1 = static_cast<uint32_t>((static_cast<uint64_t>(a.slab_vecs) * (lane + 1)) / csize);
-                t.n = static_cast<float>(p1 - p0) * VEC;
-                t.mean = peer[2 * par];
-                t.m2 = peer[2 * par + 1];
-            }
-            t = warp_merge(t);
-            if (lane == 0) {
-                bcast[0] = t.mean;
-                bcast[1] = 1.0f / sqrtf(t.m2 / static_cast<float>(a.slab_elems) + a.eps);
-            }
-        }
-        __syncthreads();
-        const float mean = bcast[0], rstd = bcast[1];
-
-        // pass 2 (L2): normalise + affine (+ activation)
-        const uint32_t ch0 = (unit % a.groups) * a.cpg;
-        if (a.vec_uniform && hwv >= kStreamThreads) {
-            uint32_t i0 = 0;
-            while (i0 < nv) {
-                const uint32_t c = a.hwv_div.div(v0 + i0);
-                const uint32_t seg_end = min(nv, (c + 1) * hwv - v0);
-                const Affine<T> af = make_affine<T, ACT>(mean, rstd, __ldg(a.w + ch0 + c),
-                                                        __ldg(a.b + ch0 + c));
-                uint32_t j = i0 + tid;
-                for (; j + kStreamThreads < seg_end; j += 2 * kStreamThreads) {
-                    const uint4 x0 = gx[j], x1 = gx[j + kStreamThreads];
-                    st_stream(&gy[j], norm_vec<T, ACT>(x0, af));
-                    st_stream(&gy[j + kStreamThreads], norm_vec<T, ACT>(x1, af));
-                }
-                for (; j < seg_end; j += kStreamThreads) st_stream(&gy[j], norm_vec<T, ACT>(gx[j], af));
-                i0 = seg_end;
-            }
-        } else if (a.vec_uniform) {
-            for (uint32_t j = tid; j < nv; j += kStreamThreads) {
-                const uint32_t c = ch0 + a.hwv_div.div(v0 + j);
-                const Affine<T> af = make_affine<T, ACT>(mean, rstd, __ldg(a.w + c), __ldg(a.b + c));
-                st_stream(&gy[j], norm_vec<T, ACT>(gx[j], af));
-            }
-        } else {
-            for (uint32_t j = tid; j < nv; j += kStreamThreads) {
-                float f[VEC];
-                unpack<T>(gx[j], f);
-                const uint32_t e = (v0 + j) * VEC;
-#pragma unroll
-                for (int l = 0; l < VEC; ++l) {
-                    const uint32_t c = ch0 + a.hw_div.div(e + l);
-                    f[l] = activate<ACT, HALF>(fmaf((f[l] - mean) * rstd, __ldg(a.w + c), __ldg(a.b + c)));
-                }
-                st_stream(&gy[j], pack<T>(f));
-            }
-        }
-    }
-    cluster.sync();     // nobody leaves while peers may read its moments
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -930,14 +717,14 @@ inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 
 // the opt-in for 16-CTA clusters), so that launches themselves make no attribute calls.
 constexpr int kMaxDevices = 64;
 
-template <typename T, int ACT, bool BIG, bool MMA>
+template <typename T, int ACT, bool BIG>
 cudaError_t ensure_resident_attrs() {
     static std::atomic<bool> done[kMaxDevices];
     int dev = 0;
     cudaError_t err = cudaGetDevice(&dev);
     if (err != cudaSuccess) return err;
     if (dev >= 0 && dev < kMaxDevices && done[dev].load(std::memory_order_acquire)) return cudaSuccess;
-    auto kernel = gn_resident_kernel<T, ACT, BIG, MMA>;
+    auto kernel = gn_resident_kernel<T, ACT, BIG>;
     err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                static_cast<int>(kHeaderBytes + kMaxPartBytes));
     if (err != cudaSuccess) return err;
@@ -962,29 +749,23 @@ inline void cluster_config(cudaLaunchConfig_t *cfg, cudaLaunchAttribute *attr, u
     cfg->numAttrs = 1;
 }
 
-template <typename T, int ACT, bool BIG, bool MMA>
+template <typename T, int ACT, bool BIG>
 cudaError_t launch_resident_as(const ResidentArgs &a, const GnPlan &plan, cudaStream_t stream) {
-    cudaError_t err = ensure_resident_attrs<T, ACT, BIG, MMA>();
+    cudaError_t err = ensure_resident_attrs<T, ACT, BIG>();
     if (err != cudaSuccess) return err;
     cudaLaunchConfig_t cfg;
     cudaLaunchAttribute attr[1];
     cluster_config(&cfg, attr, static_cast<unsigned>(plan.nclusters * plan.cluster), plan.cluster,
                    plan.threads, plan.smem, stream);
-    err = cudaLaunchKernelEx(&cfg, gn_resident_kernel<T, ACT, BIG, MMA>, a);
+    err = cudaLaunchKernelEx(&cfg, gn_resident_kernel<T, ACT, BIG>, a);
     if (err == cudaSuccess) g_launches.fetch_add(1);
     return err;
 }
 
 template <typename T, int ACT>
 cudaError_t launch_resident(const ResidentArgs &a, const GnPlan &plan, cudaStream_t stream) {
-    // fp16 moments on the tensor pipe unless SDFL_GN_FLAGS has bit 1 clear (experiment switch)
-    static const int flags = [] { const char *e = getenv("SDFL_GN_FLAGS"); return e ? atoi(e) : 0; }();
-    if (sizeof(T) == 2 && (flags & 2)) {
-        return plan.threads > 512 ? launch_resident_as<T, ACT, true, sizeof(T) == 2>(a, plan, stream)
-                                  : launch_resident_as<T, ACT, false, sizeof(T) == 2>(a, plan, stream);
-    }
-    return plan.threads > 512 ? launch_resident_as<T, ACT, true, false>(a, plan, stream)
-                              : launch_resident_as<T, ACT, false, false>(a, plan, stream);
+    return plan.threads > 512 ? launch_resident_as<T, ACT, true>(a, plan, stream)
+                              : launch_resident_as<T, ACT, false>(a, plan, stream);
 }
 
 // How many clusters of this size, block size and shared-memory footprint can be resident at
@@ -1006,74 +787,21 @@ cudaError_t resident_active_clusters(int cluster, int threads, size_t smem, int 
         auto it = cache.find(key);
         if (it != cache.end()) { *active = it->second; return cudaSuccess; }
     }
-    err = threads > 512 ? ensure_resident_attrs<T, kActSilu, true, false>()
-                        : ensure_resident_attrs<T, kActSilu, false, false>();
+    err = threads > 512 ? ensure_resident_attrs<T, kActSilu, true>()
+                        : ensure_resident_attrs<T, kActSilu, false>();
     if (err != cudaSuccess) return err;
     cudaLaunchConfig_t cfg;
     cudaLaunchAttribute attr[1];
     cluster_config(&cfg, attr, static_cast<unsigned>(cluster), cluster, threads, smem, nullptr);
     int n = 0;
     err = threads > 512
-              ? cudaOccupancyMaxActiveClusters(&n, gn_resident_kernel<T, kActSilu, true, false>, &cfg)
-              : cudaOccupancyMaxActiveClusters(&n, gn_resident_kernel<T, kActSilu, false, false>, &cfg);
+              ? cudaOccupancyMaxActiveClusters(&n, gn_resident_kernel<T, kActSilu, true>, &cfg)
+              : cudaOccupancyMaxActiveClusters(&n, gn_resident_kernel<T, kActSilu, false>, &cfg);
     if (err != cudaSuccess) return err;
     *active = n;
     std::lock_guard<std::mutex> lock(mu);
     cache[key] = n;
     return cudaSuccess;
-}
-
-template <typename T, int ACT>
-cudaError_t ensure_stream_attrs() {
-    static std::atomic<bool> done[kMaxDevices];
-    int dev = 0;
-    cudaError_t err = cudaGetDevice(&dev);
-    if (err != cudaSuccess) return err;
-    if (dev >= 0 && dev < kMaxDevices && done[dev].load(std::memory_order_acquire)) return cudaSuccess;
-    err = cudaFuncSetAttribute(gn_stream_kernel<T, ACT>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
-    if (err != cudaSuccess) return err;
-    if (dev >= 0 && dev < kMaxDevices) done[dev].store(true, std::memory_order_release);
-    return cudaSuccess;
-}
-
-template <typename T>
-cudaError_t stream_active_clusters(int cluster, int *active) {
-    static std::mutex mu;
-    static std::map<uint64_t, int> cache;
-    int dev = 0;
-    cudaError_t err = cudaGetDevice(&dev);
-    if (err != cudaSuccess) return err;
-    const uint64_t key = (static_cast<uint64_t>(dev) << 16) | static_cast<uint64_t>(cluster);
-    {
-        std::lock_guard<std::mutex> lock(mu);
-        auto it = cache.find(key);
-        if (it != cache.end()) { *active = it->second; return cudaSuccess; }
-    }
-    err = ensure_stream_attrs<T, kActSilu>();
-    if (err != cudaSuccess) return err;
-    cudaLaunchConfig_t cfg;
-    cudaLaunchAttribute attr[1];
-    cluster_config(&cfg, attr, static_cast<unsigned>(cluster), cluster, kStreamThreads, 0, nullptr);
-    int n = 0;
-    err = cudaOccupancyMaxActiveClusters(&n, gn_stream_kernel<T, kActSilu>, &cfg);
-    if (err != cudaSuccess) return err;
-    *active = n;
-    std::lock_guard<std::mutex> lock(mu);
-    cache[key] = n;
-    return cudaSuccess;
-}
-
-template <typename T, int ACT>
-cudaError_t launch_stream(const ResidentArgs &a, const GnPlan &plan, cudaStream_t stream) {
-    cudaError_t err = ensure_stream_attrs<T, ACT>();
-    if (err != cudaSuccess) return err;
-    cudaLaunchConfig_t cfg;
-    cudaLaunchAttribute attr[1];
-    cluster_config(&cfg, attr, static_cast<unsigned>(plan.nclusters * plan.cluster), plan.cluster,
-                   kStreamThreads, 0, stream);
-    err = cudaLaunchKernelEx(&cfg, gn_stream_kernel<T, ACT>, a);
-    if (err == cudaSuccess) g_launches.fetch_add(1);
-    return err;
 }
 
 constexpr int kSmCount = 148;
@@ -1092,25 +820,6 @@ cudaError_t gn_make_plan(const GnShape &s, const void *in, const void *out, int 
     const int64_t slab_bytes = slab_elems * esz;
     const int64_t units = s.batch * s.groups;
     *plan = GnPlan{};
-
-    if (force_path == kGnStream) {
-        const bool ok = aligned16(in) && aligned16(out) && slab_bytes % 16 == 0 && slab_bytes >= 16 &&
-                        units < (1ll << 27);
-        if (!ok) return cudaErrorInvalidConfiguration;
-        int c = (force_cluster & 0xff) > 0 ? (force_cluster & 0xff) : 8;
-        if (c > 16 || c > slab_bytes / 16) return cudaErrorInvalidConfiguration;
-        int active = 0;
-        cudaError_t err = s.dtype == kF16 ? stream_active_clusters<__half>(c, &active)
-                                          : stream_active_clusters<float>(c, &active);
-        if (err != cudaSuccess) return err;
-        if (active <= 0) return cudaErrorInvalidConfiguration;
-        const int64_t waves = (units + active - 1) / active;
-        plan->path = kGnStream;
-        plan->cluster = c;
-        plan->threads = kStreamThreads;
-        plan->nclusters = static_cast<int>((units + waves - 1) / waves);
-        return cudaSuccess;
-    }
 
     bool resident_ok = aligned16(in) && aligned16(out) && slab_bytes % 16 == 0 && slab_bytes >= 16 &&
                        units < (1ll << 27);
@@ -1204,7 +913,7 @@ cudaError_t gn_launch(const GnShape &s, const GnPlan &plan, const void *in, void
     const int64_t units = s.batch * s.groups;
     if (units == 0 || slab_elems == 0) return cudaSuccess;
 
-    if (plan.path == kGnResident || plan.path == kGnStream) {
+    if (plan.path == kGnResident) {
         ResidentArgs a;
         a.in = in; a.out = out; a.w = w; a.b = b;
         a.units = static_cast<uint32_t>(units);
@@ -1214,22 +923,11 @@ cudaError_t gn_launch(const GnShape &s, const GnPlan &plan, const void *in, void
         a.groups = static_cast<uint32_t>(s.groups);
         a.chunk_vecs = static_cast<uint32_t>(plan.chunk_vecs);
         a.nslots = static_cast<uint32_t>(plan.nslots);
-        {
-            static const unsigned dbg = [] { const char *e = getenv("SDFL_GN_FLAGS"); return e ? static_cast<unsigned>(atoi(e)) : 0u; }();
-            a.dbg = dbg;
-        }
         a.vec_uniform = s.hw % vec == 0;
         a.hw_vecs = a.vec_uniform ? static_cast<uint32_t>(s.hw / vec) : 1u;
         a.eps = s.eps;
         a.hw_div = FastDiv::make(static_cast<uint32_t>(s.hw));
         a.hwv_div = FastDiv::make(a.hw_vecs);
-        if (plan.path == kGnStream) {
-            if (s.dtype == kF16)
-                return s.act == kActSilu ? launch_stream<__half, kActSilu>(a, plan, stream)
-                                         : launch_stream<__half, kActNone>(a, plan, stream);
-            return s.act == kActSilu ? launch_stream<float, kActSilu>(a, plan, stream)
-                                     : launch_stream<float, kActNone>(a, plan, stream);
-        }
         if (s.dtype == kF16)
             return s.act == kActSilu ? launch_resident<__half, kActSilu>(a, plan, stream)
                                      : launch_resident<__half, kActNone>(a, plan, stream);

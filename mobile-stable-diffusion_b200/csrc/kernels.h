@@ -19,7 +19,7 @@ extern std::atomic<long long> g_launches;
 //                and activation cost one HBM read and one HBM write.
 //   kGnSplit     two kernels with a caller-provided scratch of per-chunk (mean, M2) partials;
 //                any size, any alignment; one extra read of the tensor (mostly L2 for mid sizes).
-enum GnPath : int { kGnAuto = 0, kGnResident = 1, kGnSplit = 2, kGnStream = 3 };
+enum GnPath : int { kGnAuto = 0, kGnResident = 1, kGnSplit = 2 };
 
 struct GnPlan {
     int path;          // kGnResident or kGnSplit

@@ -11,13 +11,13 @@ import ctypes as C
 import torch
 
 from . import _capi
-from ._capi import F16, F32, GN_AUTO, GN_RESIDENT, GN_SPLIT, GN_STREAM, SdflError, check, lib
+from ._capi import F16, F32, GN_AUTO, GN_RESIDENT, GN_SPLIT, SdflError, check, lib
 
 __all__ = [
     "groupnorm", "groupnorm_noalloc", "groupnorm_plan", "layernorm", "gelu_multiply", "silu", "gelu", "quick_gelu",
     "elemwise_add", "token_embedding", "timestep_embedding", "local_reduction_mean",
     "local_reduction_variance", "group_norm_apply", "layer_norm_apply", "device_status",
-    "launch_count", "HostPipeline", "GN_AUTO", "GN_RESIDENT", "GN_SPLIT", "GN_STREAM",
+    "launch_count", "HostPipeline", "GN_AUTO", "GN_RESIDENT", "GN_SPLIT",
 ]
 
 
