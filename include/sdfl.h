@@ -198,6 +198,14 @@ int sdfl_elemwise_add(const void *A, const void *B, void *C, int64_t n, int dtyp
  * not valid.  Synchronises `stream`. */
 int sdfl_device_status(unsigned int *value, int clear, void *stream);
 
+/* Failure-detection self-test.  Every wait inside the kernels (on a bulk copy, or on the
+ * cluster peers' moments) is bounded; when one runs out the kernel raises the status word and
+ * finishes instead of hanging.  This enqueues a one-warp kernel whose wait can never be
+ * satisfied, with `limit_cycles` (clamped to [1e3, 2e9]) as its bound, so that a caller can
+ * check the whole chain -- the wait ends, sdfl_device_status() reports bit 0, later launches
+ * still work -- without faulting or hanging the device. */
+int sdfl_selftest_bounded_wait(long long limit_cycles, void *stream);
+
 /* Host-buffer GroupNorm(+SiLU): what a caller holding host tensors uses (the reference's
  * models take and return std::vector<float>, JNI boundary).  A pipeline object owns `depth`
  * device staging slots and streams, created once; forward_host copies image slabs in,

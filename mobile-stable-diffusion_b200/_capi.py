@@ -63,6 +63,7 @@ SIGNATURES = {
     "sdfl_quick_gelu": (_i, [_p, _p, _i64, _i, _p]),
     "sdfl_elemwise_add": (_i, [_p, _p, _p, _i64, _i, _p]),
     "sdfl_device_status": (_i, [C.POINTER(C.c_uint), _i, _p]),
+    "sdfl_selftest_bounded_wait": (_i, [C.c_longlong, _p]),
     "sdfl_host_pipeline_create": (_i, [C.POINTER(_p), _sz, _i]),
     "sdfl_host_pipeline_destroy": (_i, [_p]),
     "sdfl_groupnorm_forward_host": (_i, [_p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _f, _i, _i]),

@@ -307,6 +307,10 @@ int sdfl_device_status(unsigned int *value, int clear, void *stream) {
     return wrap(sdfl::gn_read_status(value, clear != 0, as_stream(stream)));
 }
 
+int sdfl_selftest_bounded_wait(long long limit_cycles, void *stream) {
+    return wrap(sdfl::gn_wait_selftest(limit_cycles, as_stream(stream)));
+}
+
 // ---- host-buffer pipeline ---------------------------------------------------------------------
 
 int sdfl_host_pipeline_create(sdfl_host_pipeline **pipe, size_t max_slot_bytes, int depth) {

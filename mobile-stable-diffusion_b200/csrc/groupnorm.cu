@@ -147,6 +147,48 @@ __device__ __forceinline__ uint64_t policy_evict_first() {
     return p;
 }
 
+// ---- cluster exchange primitives: write into a peer CTA's shared memory and signal its mbarrier
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t local_smem_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_smem_addr), "r"(rank));
+    return r;
+}
+
+__device__ __forceinline__ void st_peer_f32x2(uint32_t peer_addr, float a, float b) {
+    asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};" ::"r"(peer_addr), "f"(a), "f"(b) : "memory");
+}
+
+// Release at cluster scope: the stores above are visible to whoever acquires this arrival.
+__device__ __forceinline__ void mbar_arrive_peer(uint32_t peer_bar) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(peer_bar) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        " .reg .pred p;\n"
+        " mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n"
+        " selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(ns)
+        : "memory");
+    return ok != 0;
+}
+
+// Bounded wait on a barrier that PEER CTAs arrive on (acquire at cluster scope).
+__device__ __forceinline__ bool mbar_wait_cluster_bounded(uint32_t bar, uint32_t parity, long long limit) {
+    if (mbar_try_wait_cluster(bar, parity, 0u)) return true;
+    const long long t0 = clock64();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 8; ++i)
+            if (mbar_try_wait_cluster(bar, parity, 4000u)) return true;
+        if (clock64() - t0 > limit) return false;
+    }
+}
+
 // Barrier among the consumer warps only (the producer warp never joins it).
 __device__ __forceinline__ void consumer_sync(uint32_t consumers) {
     asm volatile("bar.sync 1, %0;" ::"r"(consumers) : "memory");
@@ -341,8 +383,8 @@ gn_resident_kernel(const ResidentArgs a) {
     uint64_t *full = reinterpret_cast<uint64_t *>(smem);                  // [kMaxSlots]
     uint64_t *empty = reinterpret_cast<uint64_t *>(smem + 128);           // [kMaxSlots]
     Moments *warp_m = reinterpret_cast<Moments *>(smem + 256);            // [31]
-    float *bcast = reinterpret_cast<float *>(smem + 640);                 // mean, rstd
-    float *pub = reinterpret_cast<float *>(smem + 704);                   // [2][2] read by peers
+    uint64_t *stat_bar = reinterpret_cast<uint64_t *>(smem + 640);        // [2] peers arrive here
+    float *peer_stats = reinterpret_cast<float *>(smem + 704);            // [2][16][2] written by peers
     unsigned char *data = smem + kHeaderBytes;
 
     // This CTA's share of every slab: vectors [v0, v0 + nv), cut into `nchunks` chunks.
@@ -360,9 +402,13 @@ gn_resident_kernel(const ResidentArgs a) {
             mbar_init(smem_addr(&full[k]), 1);
             mbar_init(smem_addr(&empty[k]), cwarps);
         }
+        mbar_init(smem_addr(&stat_bar[0]), csize);
+        mbar_init(smem_addr(&stat_bar[1]), csize);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    __syncthreads();
+    // Peers signal this CTA's stat barriers: every CTA of the cluster must have initialised its
+    // barriers before anyone proceeds.  This is the only full cluster barrier of the kernel.
+    cluster.sync();
 
     if (warp == cwarps) {
         // ---------------- producer warp ----------------------------------------------------------
@@ -370,10 +416,6 @@ gn_resident_kernel(const ResidentArgs a) {
         uint32_t n = 0, slot = 0, round = 0, it = 0;
         const uint64_t keep = policy_evict_last(), drop = policy_evict_first();
         for (uint32_t unit = cluster_id; unit < a.units; unit += nclusters, ++it) {
-            // Take part in the consumers' one cluster barrier per slab without ever blocking
-            // ahead of them: arrive for slab `it` now, wait for it before the next arrive.
-            if (it > 0) cluster.barrier_wait();
-            cluster.barrier_arrive();
             if (lane == 0) {
                 const unsigned char *gsrc = static_cast<const unsigned char *>(a.in) +
                                             (static_cast<size_t>(unit) * a.slab_vecs + v0) * 16u;
@@ -397,9 +439,7 @@ gn_resident_kernel(const ResidentArgs a) {
             }
             __syncwarp();
         }
-        if (it > 0) cluster.barrier_wait();
         if (timed_out && lane == 0) atomicOr(&g_gn_status, 1u);
-        cluster.sync();                      // nobody leaves while peers may read its moments
         return;
     }
 
@@ -445,33 +485,38 @@ gn_resident_kernel(const ResidentArgs a) {
         if (lane == 0) warp_m[warp] = m;
         consumer_sync(consumers);
         if (warp == 0) {
+            // This CTA's moments -> slot [par][rank] of every CTA of the cluster (itself
+            // included), one lane per destination, then one arrival on that CTA's barrier.
             Moments t = lane < cwarps ? warp_m[lane] : Moments{0.f, 0.f, 0.f};
             t = warp_merge(t);
-            if (lane == 0) {
-                pub[2 * par] = t.mean;
-                pub[2 * par + 1] = t.m2;
+            const float cta_mean = __shfl_sync(0xffffffffu, t.mean, 0);
+            const float cta_m2 = __shfl_sync(0xffffffffu, t.m2, 0);
+            if (lane < csize) {
+                st_peer_f32x2(map_to_rank(smem_addr(&peer_stats[(par * 16u + rank) * 2u]), lane),
+                              cta_mean, cta_m2);
+                mbar_arrive_peer(map_to_rank(smem_addr(&stat_bar[par]), lane));
             }
         }
-        cluster.sync();                       // every CTA's moments of this slab are published
-        if (warp == 0) {
+        // All csize CTAs have written their pair once the barrier's phase completes.  Every
+        // warp folds the pairs itself (same order everywhere -> same bits everywhere).
+        if (!mbar_wait_cluster_bounded(smem_addr(&stat_bar[par]), (it >> 1) & 1u,
+                                       timed_out ? kWaitCyclesAfterTimeout : kWaitCycles))
+            timed_out = true;
+        float mean, rstd;
+        {
             Moments t{0.f, 0.f, 0.f};
             if (lane < csize) {
-                const float *peer = cluster.map_shared_rank(pub, lane);
                 const uint32_t p0 = static_cast<uint32_t>((static_cast<uint64_t>(a.slab_vecs) * lane) / csize);
                 const uint32_t p1 = static_cast<uint32_t>((static_cast<uint64_t>(a.slab_vecs) * (lane + 1)) / csize);
                 t.n = static_cast<float>(p1 - p0) * VEC;
-                t.mean = peer[2 * par];
-                t.m2 = peer[2 * par + 1];
+                t.mean = peer_stats[(par * 16u + lane) * 2u];
+                t.m2 = peer_stats[(par * 16u + lane) * 2u + 1u];
             }
             t = warp_merge(t);
-            if (lane == 0) {
-                const float var = t.m2 / static_cast<float>(a.slab_elems);   // biased: group_norm.cl:53-55
-                bcast[0] = t.mean;
-                bcast[1] = 1.0f / sqrtf(var + a.eps);
-            }
+            const float var = __shfl_sync(0xffffffffu, t.m2, 0) / static_cast<float>(a.slab_elems);   // biased: group_norm.cl:53-55
+            mean = __shfl_sync(0xffffffffu, t.mean, 0);
+            rstd = 1.0f / sqrtf(var + a.eps);
         }
-        consumer_sync(consumers);
-        const float mean = bcast[0], rstd = bcast[1];
 
         // pass 2: normalise + affine (+ activation) from shared memory to global; each slot is
         // handed back to the producer as soon as this warp is done with it
@@ -527,7 +572,8 @@ gn_resident_kernel(const ResidentArgs a) {
         }
     }
     if (timed_out && lane == 0) atomicOr(&g_gn_status, 1u);
-    cluster.sync();                           // nobody leaves while peers may read its moments
+    // No barrier at exit: nobody reads a peer's shared memory; a CTA's own slots are written
+    // only by peers whose arrivals it has already waited for.
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -846,7 +892,12 @@ cudaError_t gn_make_plan(const GnShape &s, const void *in, const void *out, int 
         for (; c >= 1; c = (k_cluster > 0 ? 0 : c / 2)) {
             const int64_t part_vecs = (slab_vecs + c - 1) / c;
             const int64_t part_bytes = part_vecs * 16;
-            int64_t chunk_vecs = k_chunk_kb > 0 ? k_chunk_kb * 64 : (part_bytes >= 256 * 1024 ? 2048 : 1024);
+            // One slab per cluster at most (a single wave, e.g. one image per GPU): the launch is
+            // a fill / exchange / drain latency chain, where fewer, larger chunks and more
+            // consumer warps won in the sweeps, and shares up to 96 KB stay resident.
+            const bool single_wave = units * c <= 2 * 128 && part_bytes >= 64 * 1024;
+            const bool large = part_bytes >= 256 * 1024 || single_wave;
+            int64_t chunk_vecs = k_chunk_kb > 0 ? k_chunk_kb * 64 : (large ? 2048 : 1024);
             if (chunk_vecs > part_vecs) chunk_vecs = part_vecs;
             const int64_t chunks = (part_vecs + chunk_vecs - 1) / chunk_vecs;
             const int64_t chunk_bytes = chunk_vecs * 16;
@@ -859,7 +910,7 @@ cudaError_t gn_make_plan(const GnShape &s, const void *in, const void *out, int 
             if (nslots < chunks && nslots < 2) { if (k_cluster > 0) break; continue; }
             const size_t smem = kHeaderBytes + static_cast<size_t>(nslots * chunk_bytes);
             int consumers = k_cwarps > 0 ? k_cwarps * 32
-                                         : (part_bytes >= 256 * 1024 ? 352 : part_bytes >= 8 * 1024 ? 224 : 96);
+                                         : (large ? 352 : part_bytes >= 8 * 1024 ? 224 : 96);
             if (consumers > 992) consumers = 992;
             const int threads = consumers + 32;
             int active = 0;
@@ -1002,6 +1053,30 @@ cudaError_t gn_launch_static_scratch(const GnShape &s, const GnPlan &plan, const
     // Nothing in the scratch has to start at zero: the statistics kernel overwrites every
     // (mean, M2) pair the apply kernel reads, and the two run in stream order.
     return gn_launch(s, plan, in, out, w, b, ptr, stream);
+}
+
+namespace {
+// One warp waits, with a short limit, on an mbarrier that nothing will ever complete; the wait
+// must give up by itself and raise the status word, leaving the context usable.
+__global__ void wait_selftest_kernel(long long limit_cycles) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_addr(&bar), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    const bool ok = mbar_wait_bounded(smem_addr(&bar), 0, limit_cycles);
+    if (!ok && threadIdx.x == 0) atomicOr(&g_gn_status, 1u);
+}
+}  // namespace
+
+cudaError_t gn_wait_selftest(long long limit_cycles, cudaStream_t stream) {
+    if (limit_cycles < 1000) limit_cycles = 1000;
+    if (limit_cycles > 2000000000LL) limit_cycles = 2000000000LL;
+    wait_selftest_kernel<<<1, 32, 0, stream>>>(limit_cycles);
+    cudaError_t err = cudaGetLastError();
+    if (err == cudaSuccess) g_launches.fetch_add(1);
+    return err;
 }
 
 cudaError_t gn_read_status(unsigned int *value, bool clear, cudaStream_t stream) {

@@ -59,6 +59,10 @@ cudaError_t gn_launch_static_scratch(const GnShape &s, const GnPlan &plan, const
 // copy ran out).  Reads it, optionally clears it.
 cudaError_t gn_read_status(unsigned int *value, bool clear, cudaStream_t stream);
 
+// Enqueues a one-warp kernel whose bounded wait is bound to run out (nothing completes its
+// barrier): the wait ends after `limit_cycles` clock cycles and raises bit 0 of the status word.
+cudaError_t gn_wait_selftest(long long limit_cycles, cudaStream_t stream);
+
 // Stand-alone statistics / apply kernels that keep the reference's three-launch call sequence.
 cudaError_t stats_mean_launch(const void *in, float *out, int64_t groups, int64_t n, int dtype,
                               cudaStream_t stream);

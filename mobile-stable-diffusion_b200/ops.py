@@ -17,6 +17,7 @@ __all__ = [
     "groupnorm", "groupnorm_noalloc", "groupnorm_plan", "layernorm", "gelu_multiply", "silu", "gelu", "quick_gelu",
     "elemwise_add", "token_embedding", "timestep_embedding", "local_reduction_mean",
     "local_reduction_variance", "group_norm_apply", "layer_norm_apply", "device_status",
+    "selftest_bounded_wait",
     "launch_count", "HostPipeline", "GN_AUTO", "GN_RESIDENT", "GN_SPLIT",
 ]
 
@@ -69,6 +70,11 @@ def device_status(clear: bool = True, stream=None) -> int:
     v = C.c_uint(0)
     check(lib.sdfl_device_status(C.byref(v), int(clear), _stream(stream)), "sdfl_device_status")
     return int(v.value)
+
+
+def selftest_bounded_wait(limit_cycles: int = 2_000_000, stream=None) -> None:
+    """Enqueue the kernel whose bounded wait must run out (see sdfl_selftest_bounded_wait)."""
+    check(lib.sdfl_selftest_bounded_wait(int(limit_cycles), _stream(stream)), "sdfl_selftest_bounded_wait")
 
 
 def groupnorm_plan(batch: int, channels: int, hw: int, num_groups: int, dtype: torch.dtype,

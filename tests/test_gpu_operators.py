@@ -104,3 +104,33 @@ def test_sharded_pieces_reproduce_the_whole_tensor(sdfl, world):
             y = sdfl.ops.groupnorm(sub, dg[c0:c1].contiguous(), db[c0:c1].contiguous(), ng, 1e-5, True)
             out[first:first + n_img, c0:c1] = y
     assert torch.equal(out, whole)
+
+
+def test_a_wait_that_cannot_be_satisfied_ends_by_itself_and_is_reported(sdfl):
+    """Failure detection without a GPU fault: the kernels' waits are bounded.  A wait on a
+    barrier that nothing completes gives up after its limit, the status word says so, and the
+    device keeps working."""
+    assert sdfl.ops.device_status(clear=True) == 0
+    import time
+    t0 = time.perf_counter()
+    sdfl.ops.selftest_bounded_wait(2_000_000)            # ~1 ms at ~2 GHz
+    torch.cuda.synchronize()
+    assert time.perf_counter() - t0 < 5.0
+    assert sdfl.ops.device_status(clear=True) & 1
+    assert sdfl.ops.device_status(clear=False) == 0      # cleared
+    x, gamma, beta = gn_inputs(rng_for(1, 77), (1, 64, 16, 16), "float32")
+    got = sdfl.ops.groupnorm(to_dev(x), to_dev(gamma), to_dev(beta), 32, 1e-5, True)
+    assert_close(to_np(got), oracle_group_norm(x, gamma, beta, 32, 1e-5, True), 1e-5, "after the time-out")
+    assert sdfl.ops.device_status() == 0
+
+
+def test_cpp_operator_classes_against_the_oracle():
+    """operators.hpp (the C++ mirror of the reference's GroupNorm / LayerNorm / GEGLU classes)
+    compiled into tests/cpp/test_operators by __graft_entry__.build()."""
+    import os
+    import subprocess
+    exe = os.path.join(os.path.dirname(__file__), "cpp", "test_operators")
+    if not os.path.exists(exe):
+        pytest.skip("tests/cpp/test_operators not built (run __graft_entry__.build())")
+    r = subprocess.run([exe], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0 and r.stdout.strip().endswith("ok"), r.stdout + r.stderr
