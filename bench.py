@@ -470,7 +470,7 @@ def op_cases(torch, ops, dev):
         y = torch.empty_like(x)
         g, b = 1 + 0.1 * rnd((C,), f32), 0.1 * rnd((C,), f32)
         nbytes = 2 * x.numel() * x.element_size() + 2 * C * 4
-        cases.append((name, nbytes, lambda: ops.groupnorm(x, g, b, 32, eps, True, out=y)))
+        cases.append((name, nbytes, lambda: ops.groupnorm(x, g, b, 32, eps, True, out=y), ("gn", B, C, H, eps)))
 
     gn("cfg1 GN+SiLU f32 [1,320,64,64]", 1, 320, 64, f32, 1e-5)
     for C, H in [(320, 64), (640, 32), (1280, 16), (1280, 8), (640, 64), (960, 64), (960, 32),
@@ -487,7 +487,7 @@ def op_cases(torch, ops, dev):
         y = torch.empty_like(x)
         g, b = 1 + 0.1 * rnd((D,), f32), 0.1 * rnd((D,), f32)
         nbytes = 2 * x.numel() * x.element_size() + 2 * D * 4
-        cases.append((name, nbytes, lambda: ops.layernorm(x, g, b, 1e-5, out=y)))
+        cases.append((name, nbytes, lambda: ops.layernorm(x, g, b, 1e-5, out=y), ("ln", rows, D)))
 
     ln("cfg2 LN f32 [2,77,768]", 154, 768, f32)
     ln("cfg2 LN f32 [1,77,1024] (reference width)", 77, 1024, f32)
@@ -499,7 +499,7 @@ def op_cases(torch, ops, dev):
         ab = rnd((rows, 2 * D), dtype)
         y = torch.empty((rows, D), device=dev, dtype=dtype)
         nbytes = 3 * rows * D * ab.element_size()
-        cases.append((name, nbytes, lambda: ops.gelu_multiply(ab, out=y)))
+        cases.append((name, nbytes, lambda: ops.gelu_multiply(ab, out=y), ("geglu", rows, D)))
 
     geglu("cfg4 GEGLU f16 [2,4096,2560]->[2,4096,1280]", 8192, 1280, f16)
     geglu("GEGLU f16 [16,4096,2560] (large)", 65536, 1280, f16)
@@ -508,7 +508,7 @@ def op_cases(torch, ops, dev):
     def act(name, fn, n, dtype):
         x = rnd((n,), dtype)
         y = torch.empty_like(x)
-        cases.append((name, 2 * n * x.element_size(), lambda: fn(x, out=y)))
+        cases.append((name, 2 * n * x.element_size(), lambda: fn(x, out=y), ("act", fn.__name__, n)))
 
     act("cfg2 quick_gelu f32 [2,77,3072]", ops.quick_gelu, 2 * 77 * 3072, f32)
     act("cfg2 gelu(erf) f32 [2,77,3072]", ops.gelu, 2 * 77 * 3072, f32)
@@ -524,16 +524,83 @@ def op_cases(torch, ops, dev):
         out = torch.empty((2, 77, D), device=dev, dtype=f32)
         nbytes = 2 * 77 * 8 + 2 * (2 * 77 * D * 4) + 77 * D * 4
         cases.append((f"cfg2 token+pos embedding f32 [2,77]->[2,77,{D}]", nbytes,
-                      lambda ids=ids, table=table, pos=pos, out=out: ops.token_embedding(ids, table, pos, out=out)))
+                      lambda ids=ids, table=table, pos=pos, out=out: ops.token_embedding(ids, table, pos, out=out),
+                      ("emb", D)))
     t = torch.randint(0, 1000, (2,), device=dev, generator=gen, dtype=torch.int64)
     emb = torch.empty((2, 320), device=dev, dtype=f16)
     cases.append(("cfg4 timestep embedding f16 [2]->[2,320]", 2 * 8 + 2 * 320 * 2,
-                  lambda: ops.timestep_embedding(t, 320, out=emb)))
+                  lambda: ops.timestep_embedding(t, 320, out=emb), ("ts",)))
     a_, b_ = rnd((1 << 27,), f32), rnd((1 << 27,), f32)
     c_ = torch.empty_like(a_)
     cases.append(("elemwise_add f32 128M elements (large)", 3 * (1 << 27) * 4,
-                  lambda: ops.elemwise_add(a_, b_, out=c_)))
+                  lambda: ops.elemwise_add(a_, b_, out=c_), ("add", 1 << 27)))
     return cases
+
+
+def cpu_reference_case(spec) -> dict:
+    """The reference's CPU implementation of one case on this machine's host cores
+    (oracle/_ref when built, else the plain-C port), on a bounded sample scaled linearly to the
+    case's size.  fp32 arithmetic whatever the GPU case's storage type."""
+    import numpy as np
+    import oracle
+    backend = "ref" if oracle.have_ref() else "port"
+    rng = np.random.Generator(np.random.PCG64(99))
+    kind = spec[0]
+
+    def timed(fn, reps=3):
+        fn()
+        best = 1e30
+        for _ in range(reps):
+            t0 = time.perf_counter()
+            fn()
+            best = min(best, time.perf_counter() - t0)
+        return best
+
+    scale, note = 1.0, "full size"
+    if kind == "gn":
+        _, B, C, H, eps = spec
+        x = rng.standard_normal((1, C, H, H), dtype=np.float32)
+        g, b = np.ones(C, np.float32), np.zeros(C, np.float32)
+        t = timed(lambda: oracle.group_norm(x, g, b, 32, eps, True, backend=backend), reps=2)
+        scale, note = float(B), f"one image x {B}"
+    elif kind == "ln":
+        _, rows, D = spec
+        r = min(rows, 8192)
+        x = rng.standard_normal((r, D), dtype=np.float32)
+        g, b = np.ones(D, np.float32), np.zeros(D, np.float32)
+        t = timed(lambda: oracle.layer_norm(x, g, b, 1e-5, backend=backend if D % 64 == 0 else "port"))
+        scale, note = rows / r, f"{r} rows scaled"
+    elif kind == "geglu":
+        _, rows, D = spec
+        r = min(rows, 8192)
+        ab = rng.standard_normal((r, 2 * D), dtype=np.float32)
+        t = timed(lambda: oracle.gelu_multiply(ab, backend=backend))
+        scale, note = rows / r, f"{r} rows scaled"
+    elif kind == "act":
+        _, fname, n = spec
+        m = min(n, 1 << 24)
+        x = rng.standard_normal(m, dtype=np.float32)
+        be = "port" if fname == "quick_gelu" else backend
+        t = timed(lambda: getattr(oracle, fname)(x, backend=be))
+        scale, note = n / m, f"{m} elements scaled"
+    elif kind == "add":
+        n = spec[1]
+        m = min(n, 1 << 24)
+        x, y = rng.standard_normal(m, dtype=np.float32), rng.standard_normal(m, dtype=np.float32)
+        t = timed(lambda: oracle.elemwise_add(x, y, backend=backend))
+        scale, note = n / m, f"{m} elements scaled"
+    elif kind == "emb":
+        D = spec[1]
+        table = rng.standard_normal((49408, D), dtype=np.float32)
+        pos = rng.standard_normal((77, D), dtype=np.float32)
+        ids = rng.integers(0, 49408, (2, 77), dtype=np.int64)
+        t = timed(lambda: oracle.token_embedding(ids, table, pos))
+    else:
+        tt = np.array([981, 17], np.int64)
+        t = timed(lambda: oracle.timestep_embedding(tt, 320))
+    return {"cpu_ms": round(t * scale * 1e3, 4), "cpu_cores": oracle.num_threads(backend),
+            "cpu_kind": "reference kernels compiled as C++" if backend == "ref" else "plain-C port",
+            "cpu_sample": note}
 
 
 def run_ops(args) -> None:
@@ -550,7 +617,7 @@ def run_ops(args) -> None:
     peak, peak_kind = measured_peak()
     flush = torch.empty(2 * L2_BYTES, dtype=torch.uint8, device=dev)
     reps = max(args.steps, 1) if args.case else 9
-    for name, nbytes, fn in op_cases(torch, ops, dev):
+    for name, nbytes, fn, spec in op_cases(torch, ops, dev):
         if args.case and args.case not in name:
             continue
         for _ in range(max(args.warmup, 1)):
@@ -566,10 +633,12 @@ def run_ops(args) -> None:
             times.append(a.elapsed_time(b))
         t = statistics.median(times)
         gbs = nbytes / (t * 1e-3) / 1e9
-        print(json.dumps({"case": name, "bytes": nbytes, "us": round(t * 1e3, 2), "gbs": round(gbs, 1),
-                          "frac_of_peak": round(gbs / peak, 4), "peak": peak, "peak_source": f"of {peak_kind}",
-                          "timing": "CUDA events around one launch, L2 flushed before it, median"}),
-              flush=True)
+        line = {"case": name, "bytes": nbytes, "us": round(t * 1e3, 2), "gbs": round(gbs, 1),
+                "frac_of_peak": round(gbs / peak, 4), "peak": peak, "peak_source": f"of {peak_kind}",
+                "timing": "CUDA events around one launch, L2 flushed before it, median"}
+        if args.cpu:
+            line.update(cpu_reference_case(spec))
+        print(json.dumps(line), flush=True)
     assert ops.device_status() == 0
 
 
@@ -582,6 +651,7 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--ops", action="store_true", help="per-kernel table over all named shapes")
     ap.add_argument("--case", default="", help="with --ops: only cases whose name contains this")
+    ap.add_argument("--cpu", action="store_true", help="with --ops: also time the reference on the host cores")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
