@@ -378,7 +378,7 @@ def run_ours(args) -> None:
 
     # ---- end to end through the host-buffer C-ABI call ------------------------------------------
     e2e_steps = max(2, min(K, 5))
-    pipe = ops.HostPipeline(max_slot_bytes=32 << 20, depth=4, device=local_rank)
+    pipe = ops.HostPipeline(max_slot_bytes=16 << 20, depth=6, device=local_rank)
     host = []
     for (C, H), (x, gamma, beta, y) in zip(SHAPES, sets[0]):
         h_in = torch.empty(x.shape, dtype=torch.float16, pin_memory=True)
@@ -386,9 +386,10 @@ def run_ours(args) -> None:
         host.append((h_in, torch.empty(x.shape, dtype=torch.float16, pin_memory=True), gamma, beta))
 
     def e2e_step():
-        for h_in, h_out, gamma, beta in host:
-            pipe.groupnorm(h_in, gamma, beta, GROUPS, EPS, True, h_out=h_out)
-        return float(host[0][1][0, 0, 0, 0])            # the step's result is read on the host
+        for h_in, h_out, gamma, beta in host:            # queue the four tensors, then one wait
+            pipe.groupnorm(h_in, gamma, beta, GROUPS, EPS, True, h_out=h_out, wait=False)
+        pipe.sync()
+        return float(host[-1][1][-1, -1, -1, -1])        # the step's result is read on the host
 
     e2e_step()
     if world > 1:

@@ -219,6 +219,14 @@ int sdfl_groupnorm_forward_host(sdfl_host_pipeline *pipe, const void *h_in, void
                                 const float *gamma, const float *beta, int64_t batch,
                                 int64_t channels, int64_t hw, int64_t num_groups, float eps,
                                 int fuse_silu, int dtype);
+/* The same without the final wait: enqueues the copies and kernels of one tensor on the
+ * pipeline's streams and returns; several tensors can be queued back to back and
+ * sdfl_host_pipeline_sync() waits for all of them (h_out buffers are complete after it). */
+int sdfl_groupnorm_forward_host_async(sdfl_host_pipeline *pipe, const void *h_in, void *h_out,
+                                      const float *gamma, const float *beta, int64_t batch,
+                                      int64_t channels, int64_t hw, int64_t num_groups, float eps,
+                                      int fuse_silu, int dtype);
+int sdfl_host_pipeline_sync(sdfl_host_pipeline *pipe);
 int sdfl_host_alloc(void **h_ptr, size_t bytes);
 int sdfl_host_free(void *h_ptr);
 

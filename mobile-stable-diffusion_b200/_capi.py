@@ -67,6 +67,8 @@ SIGNATURES = {
     "sdfl_host_pipeline_create": (_i, [C.POINTER(_p), _sz, _i]),
     "sdfl_host_pipeline_destroy": (_i, [_p]),
     "sdfl_groupnorm_forward_host": (_i, [_p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _f, _i, _i]),
+    "sdfl_groupnorm_forward_host_async": (_i, [_p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _f, _i, _i]),
+    "sdfl_host_pipeline_sync": (_i, [_p]),
     "sdfl_host_alloc": (_i, [C.POINTER(_p), _sz]),
     "sdfl_host_free": (_i, [_p]),
 }

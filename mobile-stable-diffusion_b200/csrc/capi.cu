@@ -94,6 +94,7 @@ struct sdfl_host_pipeline {
     std::vector<Slot> slots;
     size_t slot_bytes = 0;
     size_t ws_bytes = 0;
+    size_t next = 0;      // round-robin slot cursor
     int device = 0;
 };
 
@@ -349,10 +350,10 @@ int sdfl_host_pipeline_destroy(sdfl_host_pipeline *pipe) {
     return SDFL_OK;
 }
 
-int sdfl_groupnorm_forward_host(sdfl_host_pipeline *pipe, const void *h_in, void *h_out,
-                                const float *gamma, const float *beta, int64_t batch,
-                                int64_t channels, int64_t hw, int64_t num_groups, float eps,
-                                int fuse_silu, int dtype) {
+int sdfl_groupnorm_forward_host_async(sdfl_host_pipeline *pipe, const void *h_in, void *h_out,
+                                      const float *gamma, const float *beta, int64_t batch,
+                                      int64_t channels, int64_t hw, int64_t num_groups, float eps,
+                                      int fuse_silu, int dtype) {
     if (!pipe) return SDFL_ERR_INVALID_POINTER;
     int rc = gn_validate(h_in, h_out, gamma, beta, batch, channels, hw, num_groups, eps, dtype);
     if (rc != SDFL_OK) return rc;
@@ -371,12 +372,11 @@ int sdfl_groupnorm_forward_host(sdfl_host_pipeline *pipe, const void *h_in, void
     if (gps > num_groups) gps = num_groups;
     const char *src = static_cast<const char *>(h_in);
     char *dst = static_cast<char *>(h_out);
-    size_t step = 0;
     cudaError_t e = cudaSuccess;
     for (int64_t n = 0; n < batch && rc == SDFL_OK && e == cudaSuccess; ++n) {
-        for (int64_t g0 = 0; g0 < num_groups; g0 += gps, ++step) {
+        for (int64_t g0 = 0; g0 < num_groups; g0 += gps) {
             const int64_t ng = g0 + gps <= num_groups ? gps : num_groups - g0;
-            auto &s = pipe->slots[step % pipe->slots.size()];
+            auto &s = pipe->slots[pipe->next++ % pipe->slots.size()];
             const size_t off = static_cast<size_t>((n * num_groups + g0) * group_bytes);
             const size_t bytes = static_cast<size_t>(ng * group_bytes);
             e = cudaMemcpyAsync(s.d_in, src + off, bytes, cudaMemcpyHostToDevice, s.stream);
@@ -388,12 +388,28 @@ int sdfl_groupnorm_forward_host(sdfl_host_pipeline *pipe, const void *h_in, void
             if (e != cudaSuccess) break;
         }
     }
+    if (rc != SDFL_OK) return rc;
+    return wrap(e);
+}
+
+int sdfl_host_pipeline_sync(sdfl_host_pipeline *pipe) {
+    if (!pipe) return SDFL_ERR_INVALID_POINTER;
+    cudaError_t e = cudaSuccess;
     for (auto &s : pipe->slots) {
         cudaError_t se = cudaStreamSynchronize(s.stream);
         if (e == cudaSuccess) e = se;
     }
-    if (rc != SDFL_OK) return rc;
     return wrap(e);
+}
+
+int sdfl_groupnorm_forward_host(sdfl_host_pipeline *pipe, const void *h_in, void *h_out,
+                                const float *gamma, const float *beta, int64_t batch,
+                                int64_t channels, int64_t hw, int64_t num_groups, float eps,
+                                int fuse_silu, int dtype) {
+    const int rc = sdfl_groupnorm_forward_host_async(pipe, h_in, h_out, gamma, beta, batch, channels, hw,
+                                                     num_groups, eps, fuse_silu, dtype);
+    const int rs = sdfl_host_pipeline_sync(pipe);      // drain also after a failed enqueue
+    return rc != SDFL_OK ? rc : rs;
 }
 
 int sdfl_host_alloc(void **h_ptr, size_t bytes) {

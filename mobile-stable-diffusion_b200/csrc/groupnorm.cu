@@ -344,6 +344,7 @@ struct ResidentArgs {
     uint32_t groups;
     uint32_t chunk_vecs;   // vectors per ring chunk
     uint32_t nslots;       // chunk slots in the shared-memory ring
+    uint32_t hold;         // chunks kept in their slots between the two passes (re-read mode)
     uint32_t vec_uniform;  // hw % lanes-per-vector == 0
     uint32_t hw_vecs;      // hw / lanes-per-vector (when vec_uniform)
     float eps;
@@ -387,75 +388,102 @@ gn_resident_kernel(const ResidentArgs a) {
     float *peer_stats = reinterpret_cast<float *>(smem + 704);            // [2][16][2] written by peers
     unsigned char *data = smem + kHeaderBytes;
 
-    // This CTA's share of every slab: vectors [v0, v0 + nv), cut into `nchunks` chunks.
+    // This CTA's share of every slab: vectors [v0, v0 + nv), cut into P chunks that move through
+    // a ring of S slots.  Loads are numbered 0, 1, 2, ... over the whole kernel ("positions");
+    // position p uses slot p % S, phase (p / S) & 1 of that slot's barriers.  Per slab:
+    //   positions p0 .. p0+P-1        first read of chunks 0 .. P-1        (moments pass)
+    //   positions p0+P .. p0+2P-H-1   second read of chunks 0 .. P-H-1     (normalise pass)
+    // The last H = min(S-1, P) chunks of the first read are not released after the moments
+    // pass: they are still in their slots when the normalise pass starts, which therefore
+    // begins without waiting and reads P-H instead of P chunks again.  P <= S means H = P:
+    // the share is resident and nothing is read twice.
     const uint32_t v0 = static_cast<uint32_t>((static_cast<uint64_t>(a.slab_vecs) * rank) / csize);
     const uint32_t v1 = static_cast<uint32_t>((static_cast<uint64_t>(a.slab_vecs) * (rank + 1)) / csize);
     const uint32_t nv = v1 - v0;
     const uint32_t cv = a.chunk_vecs;
-    const uint32_t nchunks = (nv + cv - 1) / cv;
-    const uint32_t nslots = a.nslots;
-    const bool resident = nchunks <= nslots;
+    const uint32_t P = (nv + cv - 1) / cv;
+    const uint32_t S = a.nslots;
+    const uint32_t H = P <= S ? P : min(a.hold, S - 1u);
+    const uint32_t loads_per_slab = 2u * P - H;
     const uint32_t chunk_bytes = cv * 16u;
-
-    if (tid == 0) {
-        for (uint32_t k = 0; k < nslots; ++k) {
-            mbar_init(smem_addr(&full[k]), 1);
-            mbar_init(smem_addr(&empty[k]), cwarps);
-        }
-        mbar_init(smem_addr(&stat_bar[0]), csize);
-        mbar_init(smem_addr(&stat_bar[1]), csize);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    // Peers signal this CTA's stat barriers: every CTA of the cluster must have initialised its
-    // barriers before anyone proceeds.  This is the only full cluster barrier of the kernel.
-    cluster.sync();
 
     if (warp == cwarps) {
         // ---------------- producer warp ----------------------------------------------------------
         bool timed_out = false;
-        uint32_t n = 0, slot = 0, round = 0, it = 0;
         const uint64_t keep = policy_evict_last(), drop = policy_evict_first();
-        for (uint32_t unit = cluster_id; unit < a.units; unit += nclusters, ++it) {
-            if (lane == 0) {
-                const unsigned char *gsrc = static_cast<const unsigned char *>(a.in) +
-                                            (static_cast<size_t>(unit) * a.slab_vecs + v0) * 16u;
-                const uint32_t loads = resident ? nchunks : 2u * nchunks;
-                for (uint32_t l = 0; l < loads; ++l, ++n) {
-                    const uint32_t j = l < nchunks ? l : l - nchunks;
-                    if (round > 0) {
-                        if (!mbar_wait_bounded(smem_addr(&empty[slot]), (round - 1) & 1u,
-                                               timed_out ? kWaitCyclesAfterTimeout : kWaitCycles))
-                            timed_out = true;
-                    }
-                    const uint32_t lo = j * cv;
-                    const uint32_t bytes = (min(nv, lo + cv) - lo) * 16u;
-                    const uint32_t bar = smem_addr(&full[slot]);
-                    mbar_expect_tx(bar, bytes);
-                    // the first of two reads should stay in L2; a last read need not
-                    bulk_load_hint(smem_addr(data + slot * chunk_bytes), gsrc + lo * 16u, bytes, bar,
-                                   (!resident && l < nchunks) ? keep : drop);
-                    if (++slot == nslots) { slot = 0; ++round; }
-                }
+        uint32_t unit = cluster_id, l = 0, slot = 0, round = 0;
+        // Issue the next load of the sequence; false when all slabs are done.
+        auto issue_next = [&]() -> bool {
+            if (unit >= a.units) return false;
+            const uint32_t j = l < P ? l : l - P;
+            if (round > 0) {       // the slot's previous occupant must have been released
+                if (!mbar_wait_bounded(smem_addr(&empty[slot]), (round - 1) & 1u,
+                                       timed_out ? kWaitCyclesAfterTimeout : kWaitCycles))
+                    timed_out = true;
             }
-            __syncwarp();
+            const unsigned char *gsrc = static_cast<const unsigned char *>(a.in) +
+                                        (static_cast<size_t>(unit) * a.slab_vecs + v0) * 16u;
+            const uint32_t lo = j * cv;
+            const uint32_t bytes = (min(nv, lo + cv) - lo) * 16u;
+            const uint32_t bar = smem_addr(&full[slot]);
+            mbar_expect_tx(bar, bytes);
+            // a chunk that will be read a second time should stay in L2; a last read need not
+            bulk_load_hint(smem_addr(data + slot * chunk_bytes), gsrc + lo * 16u, bytes, bar,
+                           (l < P && j + H < P) ? keep : drop);
+            if (++slot == S) { slot = 0; ++round; }
+            if (++l == loads_per_slab) { l = 0; unit += nclusters; }
+            return true;
+        };
+        if (lane == 0) {
+            for (uint32_t k = 0; k < S; ++k) {
+                mbar_init(smem_addr(&full[k]), 1);
+                mbar_init(smem_addr(&empty[k]), cwarps);
+            }
+            mbar_init(smem_addr(&stat_bar[0]), csize);
+            mbar_init(smem_addr(&stat_bar[1]), csize);
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // inits before the copy engine's arrivals
+            // The first S loads need no release: start them before the barrier below, so the
+            // first HBM round trip overlaps the cluster's start-up.
+            for (uint32_t k = 0; k < S; ++k)
+                if (!issue_next()) break;
         }
-        if (timed_out && lane == 0) atomicOr(&g_gn_status, 1u);
+        __syncwarp();
+        cluster.sync();            // see the consumers' side
+        if (lane == 0) {
+            while (issue_next()) {}
+            if (timed_out) atomicOr(&g_gn_status, 1u);
+        }
         return;
     }
 
     // ---------------- consumer warps -------------------------------------------------------------
     const uint32_t hwv = a.hw_vecs;          // vectors per channel (valid when vec_uniform)
+    {
+        // warm L2 with the first slab's scale and shift while the first chunks are in flight
+        const uint32_t g0 = (cluster_id % a.groups) * a.cpg;
+        const uint32_t c_lo = a.hw_div.div(v0 * VEC), c_hi = a.hw_div.div((v0 + nv) * VEC - 1u);
+        for (uint32_t c = c_lo + tid; c <= c_hi && c < a.cpg; c += consumers) {
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(a.w + g0 + c));
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(a.b + g0 + c));
+        }
+    }
+    // Peers signal this CTA's stat barriers and the consumers use the barriers the producer
+    // initialised: one full cluster barrier, the only one of the kernel.
+    cluster.sync();
+
     bool timed_out = false;
-    uint32_t slot = 0, round = 0, it = 0;    // position of the next chunk to consume
+    uint32_t pos = 0, it = 0;                // position of the slab's first load
     for (uint32_t unit = cluster_id; unit < a.units; unit += nclusters, ++it) {
         const uint32_t par = it & 1u;
-        const uint32_t slot0 = slot, round0 = round;
+        const uint32_t p0 = pos;
 
         // pass 1: shifted sums, chunk by chunk as the copies land
         float s[2] = {0.f, 0.f}, q[2] = {0.f, 0.f};
         float shift = 0.f;
         uint32_t nvec_mine = 0;
-        for (uint32_t j = 0; j < nchunks; ++j) {
+        for (uint32_t j = 0; j < P; ++j) {
+            const uint32_t p = p0 + j, slot = p % S, round = p / S;
             if (!mbar_wait_bounded(smem_addr(&full[slot]), round & 1u,
                                    timed_out ? kWaitCyclesAfterTimeout : kWaitCycles))
                 timed_out = true;
@@ -467,11 +495,10 @@ gn_resident_kernel(const ResidentArgs a) {
                 stats_vec<T>(sv[i], shift, s, q);
                 ++nvec_mine;
             }
-            if (!resident) {
+            if (j + H < P) {       // not one of the chunks held for pass 2
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_addr(&empty[slot]));
             }
-            if (++slot == nslots) { slot = 0; ++round; }
         }
         Moments m;
         {
@@ -506,9 +533,9 @@ gn_resident_kernel(const ResidentArgs a) {
         {
             Moments t{0.f, 0.f, 0.f};
             if (lane < csize) {
-                const uint32_t p0 = static_cast<uint32_t>((static_cast<uint64_t>(a.slab_vecs) * lane) / csize);
-                const uint32_t p1 = static_cast<uint32_t>((static_cast<uint64_t>(a.slab_vecs) * (lane + 1)) / csize);
-                t.n = static_cast<float>(p1 - p0) * VEC;
+                const uint32_t q0 = static_cast<uint32_t>((static_cast<uint64_t>(a.slab_vecs) * lane) / csize);
+                const uint32_t q1 = static_cast<uint32_t>((static_cast<uint64_t>(a.slab_vecs) * (lane + 1)) / csize);
+                t.n = static_cast<float>(q1 - q0) * VEC;
                 t.mean = peer_stats[(par * 16u + lane) * 2u];
                 t.m2 = peer_stats[(par * 16u + lane) * 2u + 1u];
             }
@@ -519,13 +546,17 @@ gn_resident_kernel(const ResidentArgs a) {
         }
 
         // pass 2: normalise + affine (+ activation) from shared memory to global; each slot is
-        // handed back to the producer as soon as this warp is done with it
-        if (resident) { slot = slot0; round = round0; }
+        // handed back to the producer as soon as this warp is done with it.  Held chunks
+        // (P-H .. P-1, already in their slots) first, then chunks 0 .. P-H-1 as they come back.
         const uint32_t ch0 = (unit % a.groups) * a.cpg;
         uint4 *gv = reinterpret_cast<uint4 *>(static_cast<unsigned char *>(a.out) +
                                               (static_cast<size_t>(unit) * a.slab_vecs + v0) * 16u);
-        for (uint32_t j = 0; j < nchunks; ++j) {
-            if (!resident) {
+        for (uint32_t k = 0; k < P; ++k) {
+            const bool held = k < H;
+            const uint32_t j = held ? P - H + k : k - H;          // chunk of the share
+            const uint32_t p = held ? p0 + j : p0 + P + j;        // its position in the ring
+            const uint32_t slot = p % S, round = p / S;
+            if (!held) {
                 if (!mbar_wait_bounded(smem_addr(&full[slot]), round & 1u,
                                        timed_out ? kWaitCyclesAfterTimeout : kWaitCycles))
                     timed_out = true;
@@ -568,8 +599,8 @@ gn_resident_kernel(const ResidentArgs a) {
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_addr(&empty[slot]));
-            if (++slot == nslots) { slot = 0; ++round; }
         }
+        pos = p0 + loads_per_slab;
     }
     if (timed_out && lane == 0) atomicOr(&g_gn_status, 1u);
     // No barrier at exit: nobody reads a peer's shared memory; a CTA's own slots are written
@@ -880,7 +911,7 @@ cudaError_t gn_make_plan(const GnShape &s, const void *in, const void *out, int 
         // well inside L2, and with few slabs so that every SM still gets a CTA.
         const int64_t slab_vecs = slab_bytes / 16;
         const int k_cluster = force_cluster & 0xff, k_slots = (force_cluster >> 8) & 0xff;
-        const int k_chunk_kb = (force_cluster >> 16) & 0xff, k_cwarps = (force_cluster >> 24) & 0x3f;
+        const int k_chunk_kb = (force_cluster >> 16) & 0xff, k_cwarps = (force_cluster >> 24) & 0xf;
         int c = slab_bytes <= 192 * 1024 ? 2 : slab_bytes <= 768 * 1024 ? 4 : 8;
         const int64_t want_ctas = 2 * kSmCount;
         // (not beyond 8: only about half as many 16-CTA clusters can be co-resident)
@@ -927,6 +958,7 @@ cudaError_t gn_make_plan(const GnShape &s, const void *in, const void *out, int 
             plan->nclusters = static_cast<int>((units + waves - 1) / waves);
             plan->chunk_vecs = static_cast<int>(chunk_vecs);
             plan->nslots = static_cast<int>(nslots);
+            plan->hold = (force_cluster >> 28) & 3 ? ((force_cluster >> 28) & 3) - 1 : static_cast<int>(nslots) - 1;
             return cudaSuccess;
         }
         if (force_path == kGnResident) return cudaErrorInvalidConfiguration;
@@ -974,6 +1006,7 @@ cudaError_t gn_launch(const GnShape &s, const GnPlan &plan, const void *in, void
         a.groups = static_cast<uint32_t>(s.groups);
         a.chunk_vecs = static_cast<uint32_t>(plan.chunk_vecs);
         a.nslots = static_cast<uint32_t>(plan.nslots);
+        a.hold = static_cast<uint32_t>(plan.hold);
         a.vec_uniform = s.hw % vec == 0;
         a.hw_vecs = a.vec_uniform ? static_cast<uint32_t>(s.hw / vec) : 1u;
         a.eps = s.eps;

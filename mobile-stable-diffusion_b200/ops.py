@@ -293,18 +293,25 @@ class HostPipeline:
             pass
 
     def groupnorm(self, h_x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor, num_groups: int,
-                  eps: float = 1e-5, silu: bool = False, h_out: torch.Tensor | None = None):
+                  eps: float = 1e-5, silu: bool = False, h_out: torch.Tensor | None = None,
+                  wait: bool = True):
+        """wait=False only enqueues (sdfl_groupnorm_forward_host_async); call sync() before
+        reading h_out."""
         if h_x.is_cuda or not h_x.is_contiguous():
             raise TypeError("h_x must be a contiguous host tensor")
         h_out = torch.empty_like(h_x, pin_memory=h_x.is_pinned()) if h_out is None else h_out
         B, Cc = h_x.shape[0], h_x.shape[1]
         hw = h_x.numel() // (B * Cc) if B * Cc else 0
+        fn = lib.sdfl_groupnorm_forward_host if wait else lib.sdfl_groupnorm_forward_host_async
         with torch.cuda.device(self.device):
-            check(lib.sdfl_groupnorm_forward_host(
-                self._h, h_x.data_ptr(), h_out.data_ptr(), _f32(gamma, "gamma"), _f32(beta, "beta"),
-                B, Cc, hw, num_groups, eps, int(silu), _dtype_code(h_x)),
-                "sdfl_groupnorm_forward_host")
+            check(fn(self._h, h_x.data_ptr(), h_out.data_ptr(), _f32(gamma, "gamma"), _f32(beta, "beta"),
+                     B, Cc, hw, num_groups, eps, int(silu), _dtype_code(h_x)),
+                  "sdfl_groupnorm_forward_host")
         return h_out
+
+    def sync(self) -> None:
+        with torch.cuda.device(self.device):
+            check(lib.sdfl_host_pipeline_sync(self._h), "sdfl_host_pipeline_sync")
 
 
 _ = (_capi, SdflError)

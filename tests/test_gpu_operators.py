@@ -134,3 +134,19 @@ def test_cpp_operator_classes_against_the_oracle():
         pytest.skip("tests/cpp/test_operators not built (run __graft_entry__.build())")
     r = subprocess.run([exe], capture_output=True, text=True, timeout=120)
     assert r.returncode == 0 and r.stdout.strip().endswith("ok"), r.stdout + r.stderr
+
+
+def test_host_pipeline_async_queue_of_tensors(sdfl):
+    """Several tensors queued without waiting, one sync at the end (what bench.py's e2e leg does)."""
+    pipe = sdfl.ops.HostPipeline(max_slot_bytes=256 << 10, depth=3)
+    cases = []
+    for i, shape in enumerate([(2, 64, 32, 32), (1, 128, 16, 16), (3, 32, 8, 8)]):
+        x, gamma, beta = gn_inputs(rng_for(5, 40 + i), shape, "float16")
+        h_x = torch.from_numpy(x).pin_memory()
+        h_y = torch.empty_like(h_x).pin_memory()
+        pipe.groupnorm(h_x, to_dev(gamma), to_dev(beta), 32, 1e-6, True, h_out=h_y, wait=False)
+        cases.append((x, gamma, beta, h_x, h_y))
+    pipe.sync()
+    pipe.close()
+    for x, gamma, beta, _, h_y in cases:
+        assert_close(h_y.numpy(), oracle_group_norm(x, gamma, beta, 32, 1e-6, True), TOL["float16"], "queued")
