@@ -496,6 +496,17 @@ def op_cases(torch, ops, dev):
     ln("LN f16 [16,4096,1280] (large)", 65536, 1280, f16)
     ln("LN f32 [16,4096,320] (large)", 65536, 320, f32)
 
+    def add_ln(name, rows, D, dtype):
+        x, r = rnd((rows, D), dtype), rnd((rows, D), dtype)
+        ssum, y = torch.empty_like(x), torch.empty_like(x)
+        g, b = 1 + 0.1 * rnd((D,), f32), 0.1 * rnd((D,), f32)
+        nbytes = 4 * x.numel() * x.element_size() + 2 * D * 4
+        cases.append((name, nbytes, lambda: ops.add_layernorm(x, r, g, b, 1e-5, sum_out=ssum, out=y),
+                      ("addln", rows, D)))
+
+    add_ln("next: add+LN f16 [2,4096,320]", 8192, 320, f16)
+    add_ln("next: add+LN f16 [16,4096,1280] (large)", 65536, 1280, f16)
+
     def geglu(name, rows, D, dtype):
         ab = rnd((rows, 2 * D), dtype)
         y = torch.empty((rows, D), device=dev, dtype=dtype)
@@ -570,6 +581,15 @@ def cpu_reference_case(spec) -> dict:
         x = rng.standard_normal((r, D), dtype=np.float32)
         g, b = np.ones(D, np.float32), np.zeros(D, np.float32)
         t = timed(lambda: oracle.layer_norm(x, g, b, 1e-5, backend=backend if D % 64 == 0 else "port"))
+        scale, note = rows / r, f"{r} rows scaled"
+    elif kind == "addln":
+        _, rows, D = spec
+        r = min(rows, 8192)
+        x = rng.standard_normal((r, D), dtype=np.float32)
+        y = rng.standard_normal((r, D), dtype=np.float32)
+        g, b = np.ones(D, np.float32), np.zeros(D, np.float32)
+        t = timed(lambda: oracle.layer_norm(oracle.elemwise_add(x, y, backend=backend), g, b, 1e-5,
+                                            backend=backend if D % 64 == 0 else "port"))
         scale, note = rows / r, f"{r} rows scaled"
     elif kind == "geglu":
         _, rows, D = spec

@@ -126,6 +126,16 @@ int sdfl_groupnorm_forward_noalloc(const void *in, void *out, const float *gamma
 int sdfl_layernorm_forward(const void *in, void *out, const float *gamma, const float *beta,
                            int64_t rows, int64_t dim, float eps, int dtype, void *stream);
 
+/* Residual add fused into the LayerNorm that follows it: sum_out = a + b, out = LayerNorm(sum_out).
+ * Replaces the elemwise_add launch + LayerNorm::forward pairs of the transformer block
+ * (NN/BasicTransformerBlock.cpp:126-136 and :149-158: the sum is kept as the next residual, the
+ * normalised tensor feeds the next attention / feed-forward).  Five tensor passes become four.
+ * sum_out may be a or b (the reference adds in place); out must not overlap sum_out.  The sum is
+ * rounded to the storage type before it is normalised, exactly as the two separate steps do. */
+int sdfl_add_layernorm_forward(const void *a, const void *b, void *sum_out, void *out,
+                               const float *gamma, const float *beta, int64_t rows, int64_t dim,
+                               float eps, int dtype, void *stream);
+
 /* Token + position embedding: out[b,t,:] = table[ids[b,t],:] + pos[t,:].
  * Replaces TextEncoder::createTokenEmbeddingBuffer (M/TextEncoder.cpp:105-125, a host loop
  * over a host-resident table) followed by elemwise_add with the positional table

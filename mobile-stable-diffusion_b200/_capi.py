@@ -51,6 +51,7 @@ SIGNATURES = {
     "sdfl_groupnorm_forward_noalloc": (_i, [_p, _p, _p, _p, _i64, _i64, _i64, _i64, _f, _i, _i, _p]),
     "sdfl_groupnorm_plan": (_i, [_i64, _i64, _i64, _i64, _i, _i, _i, C.POINTER(_i64)]),
     "sdfl_layernorm_forward": (_i, [_p, _p, _p, _p, _i64, _i64, _f, _i, _p]),
+    "sdfl_add_layernorm_forward": (_i, [_p, _p, _p, _p, _p, _p, _i64, _i64, _f, _i, _p]),
     "sdfl_token_embedding": (_i, [_p, _p, _p, _p, _i64, _i64, _i64, _i64, _i, _p, _p]),
     "sdfl_timestep_embedding": (_i, [_p, _p, _i64, _i64, _f, _i, _p]),
     "sdfl_local_reduction_mean": (_i, [_p, _p, _i64, _i64, _i, _p]),

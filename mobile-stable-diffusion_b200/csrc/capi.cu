@@ -212,6 +212,22 @@ int sdfl_layernorm_forward(const void *in, void *out, const float *gamma, const 
     return wrap(sdfl::ln_launch(in, out, gamma, beta, rows, dim, eps, dtype, as_stream(stream)));
 }
 
+int sdfl_add_layernorm_forward(const void *a, const void *b, void *sum_out, void *out,
+                               const float *gamma, const float *beta, int64_t rows, int64_t dim,
+                               float eps, int dtype, void *stream) {
+    if (!dtype_ok(dtype) || rows < 0 || dim <= 0 || !(eps >= 0.f)) return SDFL_ERR_INVALID_VALUE;
+    if (dim >= (1ll << 31)) return SDFL_ERR_UNSUPPORTED;
+    if (rows == 0) return SDFL_OK;
+    if (!a || !b || !sum_out || !out || !gamma || !beta) return SDFL_ERR_INVALID_POINTER;
+    const int64_t bytes = rows * dim * esize(dtype);
+    // sum_out may be a or b (the reference adds in place); out may be a or b but not sum_out
+    if (partial_overlap(a, bytes, sum_out, bytes) || partial_overlap(b, bytes, sum_out, bytes) ||
+        partial_overlap(a, bytes, out, bytes) || partial_overlap(b, bytes, out, bytes) ||
+        any_overlap(sum_out, bytes, out, bytes))
+        return SDFL_ERR_OVERLAP;
+    return wrap(sdfl::add_ln_launch(a, b, sum_out, out, gamma, beta, rows, dim, eps, dtype, as_stream(stream)));
+}
+
 int sdfl_token_embedding(const int64_t *ids, const void *table, const void *pos, void *out,
                          int64_t batch, int64_t seq_len, int64_t dim, int64_t vocab, int dtype,
                          int *d_status, void *stream) {

@@ -80,6 +80,11 @@ cudaError_t ln_apply_launch(const void *in, const float *mean, const float *var,
 cudaError_t ln_launch(const void *in, void *out, const float *w, const float *b, int64_t rows,
                       int64_t dim, float eps, int dtype, cudaStream_t stream);
 
+// sum_out = a + b (rounded to the storage type), out = LayerNorm(sum_out); one launch when possible.
+cudaError_t add_ln_launch(const void *a, const void *b2, void *sum_out, void *out, const float *w,
+                          const float *b, int64_t rows, int64_t dim, float eps, int dtype,
+                          cudaStream_t stream);
+
 // ---- Elementwise ------------------------------------------------------------------------------
 cudaError_t geglu_launch(const void *ab, void *dst, int64_t rows, int64_t d, int dtype,
                          cudaStream_t stream);

@@ -18,95 +18,145 @@ namespace {
 constexpr int kLnThreads = 256;
 constexpr int kLnWarps = kLnThreads / 32;
 
-// PREFETCH: the next row of the warp is already on its way into a second register set while
-// the current one is reduced and written, so two rows per warp are in flight (the kernel is
-// bound by load latency otherwise).  Only for short rows, where the registers allow it.
+// Per-vector arithmetic.  For fp16 storage the mixed-precision add / sub (f16 operand, f32
+// result) widens and combines in one instruction, so no separate conversions are issued.
+template <typename T> struct LnVec;
+
+template <> struct LnVec<float> {
+    static __device__ __forceinline__ void sum(const uint4 &v, float (&s)[2]) {
+        s[0] += __uint_as_float(v.x); s[1] += __uint_as_float(v.y);
+        s[0] += __uint_as_float(v.z); s[1] += __uint_as_float(v.w);
+    }
+    static __device__ __forceinline__ void sq(const uint4 &v, float mean, float (&q)[2]) {
+        const float d0 = __uint_as_float(v.x) - mean, d1 = __uint_as_float(v.y) - mean;
+        const float d2 = __uint_as_float(v.z) - mean, d3 = __uint_as_float(v.w) - mean;
+        q[0] = fmaf(d0, d0, q[0]); q[1] = fmaf(d1, d1, q[1]);
+        q[0] = fmaf(d2, d2, q[0]); q[1] = fmaf(d3, d3, q[1]);
+    }
+    static __device__ __forceinline__ uint4 norm(const uint4 &v, float mean, float rstd,
+                                                 const float *w, const float *b) {
+        const float4 ww = *reinterpret_cast<const float4 *>(w);
+        const float4 bb = *reinterpret_cast<const float4 *>(b);
+        uint4 o;
+        o.x = __float_as_uint(fmaf((__uint_as_float(v.x) - mean) * rstd, ww.x, bb.x));
+        o.y = __float_as_uint(fmaf((__uint_as_float(v.y) - mean) * rstd, ww.y, bb.y));
+        o.z = __float_as_uint(fmaf((__uint_as_float(v.z) - mean) * rstd, ww.z, bb.z));
+        o.w = __float_as_uint(fmaf((__uint_as_float(v.w) - mean) * rstd, ww.w, bb.w));
+        return o;
+    }
+};
+
+__device__ __forceinline__ void ln_sum_half2(uint32_t packed, float (&s)[2]) {
+    asm("{\n .reg .b16 lo, hi;\n mov.b32 {lo, hi}, %2;\n"
+        " add.rn.f32.f16 %0, lo, %0;\n add.rn.f32.f16 %1, hi, %1;\n}\n"
+        : "+f"(s[0]), "+f"(s[1]) : "r"(packed));
+}
+__device__ __forceinline__ void ln_sq_half2(uint32_t packed, float mean, float (&q)[2]) {
+    asm("{\n .reg .b16 lo, hi;\n .reg .f32 d0, d1;\n mov.b32 {lo, hi}, %2;\n"
+        " sub.rn.f32.f16 d0, lo, %3;\n sub.rn.f32.f16 d1, hi, %3;\n"
+        " fma.rn.f32 %0, d0, d0, %0;\n fma.rn.f32 %1, d1, d1, %1;\n}\n"
+        : "+f"(q[0]), "+f"(q[1]) : "r"(packed), "f"(mean));
+}
+// (x - mean) for both halves of a packed pair
+__device__ __forceinline__ void ln_center_half2(uint32_t packed, float mean, float &d0, float &d1) {
+    asm("{\n .reg .b16 lo, hi;\n mov.b32 {lo, hi}, %2;\n"
+        " sub.rn.f32.f16 %0, lo, %3;\n sub.rn.f32.f16 %1, hi, %3;\n}\n"
+        : "=f"(d0), "=f"(d1) : "r"(packed), "f"(mean));
+}
+
+template <> struct LnVec<__half> {
+    static __device__ __forceinline__ void sum(const uint4 &v, float (&s)[2]) {
+        ln_sum_half2(v.x, s); ln_sum_half2(v.y, s); ln_sum_half2(v.z, s); ln_sum_half2(v.w, s);
+    }
+    static __device__ __forceinline__ void sq(const uint4 &v, float mean, float (&q)[2]) {
+        ln_sq_half2(v.x, mean, q); ln_sq_half2(v.y, mean, q);
+        ln_sq_half2(v.z, mean, q); ln_sq_half2(v.w, mean, q);
+    }
+    static __device__ __forceinline__ uint4 norm(const uint4 &v, float mean, float rstd,
+                                                 const float *w, const float *b) {
+        const float4 w0 = *reinterpret_cast<const float4 *>(w);
+        const float4 w1 = *(reinterpret_cast<const float4 *>(w) + 1);
+        const float4 b0 = *reinterpret_cast<const float4 *>(b);
+        const float4 b1 = *(reinterpret_cast<const float4 *>(b) + 1);
+        float d[8];
+        ln_center_half2(v.x, mean, d[0], d[1]);
+        ln_center_half2(v.y, mean, d[2], d[3]);
+        ln_center_half2(v.z, mean, d[4], d[5]);
+        ln_center_half2(v.w, mean, d[6], d[7]);
+        uint4 o;
+        __half2 *h = reinterpret_cast<__half2 *>(&o);
+        h[0] = __floats2half2_rn(fmaf(d[0] * rstd, w0.x, b0.x), fmaf(d[1] * rstd, w0.y, b0.y));
+        h[1] = __floats2half2_rn(fmaf(d[2] * rstd, w0.z, b0.z), fmaf(d[3] * rstd, w0.w, b0.w));
+        h[2] = __floats2half2_rn(fmaf(d[4] * rstd, w1.x, b1.x), fmaf(d[5] * rstd, w1.y, b1.y));
+        h[3] = __floats2half2_rn(fmaf(d[6] * rstd, w1.z, b1.z), fmaf(d[7] * rstd, w1.w, b1.w));
+        return o;
+    }
+};
+
 // Register budget: the more row vectors a lane holds, the fewer CTAs share an SM.
 constexpr int ln_min_blocks(int maxv) { return maxv <= 3 ? 6 : maxv <= 6 ? 4 : maxv <= 8 ? 3 : 2; }
 
-template <typename T, int MAXV, bool PREFETCH>
+// One warp per row; lane l keeps vectors l, l+32, ... of the row in registers, so the mean,
+// the exact two-pass variance and the normalised write cost one read and one write of the row.
+//
+// ADD: the row normalised is in + in2 (the residual add that precedes the norm in the
+// reference's transformer block, BasicTransformerBlock.cpp:126-136); the sum itself is also
+// written to `sum_out`, rounded to the storage type first, so the result equals the
+// reference's two steps (elemwise_add, then layer_norm on what was stored).
+// Scale and shift are fp32 (2 x 4 bytes per element against 2 bytes of fp16 data): read through
+// L1 for every row they saturate the L1 data path, so each CTA first copies them to shared
+// memory (dynamic, 2 * dim floats) and every row reads them from there.
+template <typename T, int MAXV, bool ADD>
 __global__ void __launch_bounds__(kLnThreads, ln_min_blocks(MAXV))
-ln_warp_kernel(const T *__restrict__ in, T *__restrict__ out, const float *__restrict__ w,
-               const float *__restrict__ b, long long rows, int nvec, int dim, float eps) {
+ln_warp_kernel(const T *in, const T *in2, T *sum_out, T *out, const float *__restrict__ gw,
+               const float *__restrict__ gb, long long rows, int nvec, int dim, float eps) {
     constexpr int VEC = VecOf<T>::N;
+    extern __shared__ __align__(16) float s_wb[];
+    float *w = s_wb, *b = s_wb + dim;
+    for (int i = threadIdx.x; i < dim / 4; i += kLnThreads) {
+        reinterpret_cast<float4 *>(w)[i] = __ldg(reinterpret_cast<const float4 *>(gw) + i);
+        reinterpret_cast<float4 *>(b)[i] = __ldg(reinterpret_cast<const float4 *>(gb) + i);
+    }
+    __syncthreads();
     const int lane = threadIdx.x & 31;
     const long long warp0 = static_cast<long long>(blockIdx.x) * kLnWarps + (threadIdx.x >> 5);
     const long long nwarps = static_cast<long long>(gridDim.x) * kLnWarps;
     const float inv_d = 1.0f / static_cast<float>(dim);
-    uint4 v[MAXV], nxt[PREFETCH ? MAXV : 1];
-
-    auto load_row = [&](uint4 (&dst)[MAXV], long long row) {
-        const uint4 *xr = reinterpret_cast<const uint4 *>(in + row * dim);
-#pragma unroll
-        for (int i = 0; i < MAXV; ++i) {
-            const int idx = lane + 32 * i;
-            if (idx < nvec) dst[i] = ld_stream(xr + idx);
-        }
-    };
-
-    if (warp0 < rows) load_row(v, warp0);
     for (long long row = warp0; row < rows; row += nwarps) {
-        if (PREFETCH) {
-            if (row + nwarps < rows) {
-                const uint4 *xr = reinterpret_cast<const uint4 *>(in + (row + nwarps) * dim);
-#pragma unroll
-                for (int i = 0; i < MAXV; ++i) {
-                    const int idx = lane + 32 * i;
-                    if (idx < nvec) nxt[i] = ld_stream(xr + idx);
-                }
-            }
-        } else if (row != warp0) {
-            load_row(v, row);
-        }
+        const uint4 *xr = reinterpret_cast<const uint4 *>(in + row * dim);
         uint4 *yr = reinterpret_cast<uint4 *>(out + row * dim);
-        float s = 0.f;
-#pragma unroll
-        for (int i = 0; i < MAXV; ++i) {
-            if (lane + 32 * i < nvec) {
-                float f[VEC];
-                unpack<T>(v[i], f);
-#pragma unroll
-                for (int j = 0; j < VEC; ++j) s += f[j];
-            }
-        }
-        const float mean = warp_sum(s) * inv_d;
-        float q = 0.f;
-#pragma unroll
-        for (int i = 0; i < MAXV; ++i) {
-            if (lane + 32 * i < nvec) {
-                float f[VEC];
-                unpack<T>(v[i], f);
-#pragma unroll
-                for (int j = 0; j < VEC; ++j) {
-                    const float d = f[j] - mean;
-                    q = fmaf(d, d, q);
-                }
-            }
-        }
-        const float var = warp_sum(q) * inv_d;
-        const float rstd = 1.0f / sqrtf(var + eps);
+        uint4 v[MAXV];
 #pragma unroll
         for (int i = 0; i < MAXV; ++i) {
             const int idx = lane + 32 * i;
             if (idx < nvec) {
-                float f[VEC];
-                unpack<T>(v[i], f);
-                const float4 *wv = reinterpret_cast<const float4 *>(w + idx * VEC);
-                const float4 *bv = reinterpret_cast<const float4 *>(b + idx * VEC);
+                v[i] = ld_stream(xr + idx);
+                if (ADD) {
+                    float fa[VEC], fb[VEC];
+                    unpack<T>(v[i], fa);
+                    unpack<T>(ld_stream(reinterpret_cast<const uint4 *>(in2 + row * dim) + idx), fb);
 #pragma unroll
-                for (int h = 0; h < VEC / 4; ++h) {
-                    const float4 ww = __ldg(wv + h), bb = __ldg(bv + h);
-                    f[4 * h + 0] = fmaf((f[4 * h + 0] - mean) * rstd, ww.x, bb.x);
-                    f[4 * h + 1] = fmaf((f[4 * h + 1] - mean) * rstd, ww.y, bb.y);
-                    f[4 * h + 2] = fmaf((f[4 * h + 2] - mean) * rstd, ww.z, bb.z);
-                    f[4 * h + 3] = fmaf((f[4 * h + 3] - mean) * rstd, ww.w, bb.w);
+                    for (int j = 0; j < VEC; ++j) fa[j] += fb[j];
+                    v[i] = pack<T>(fa);
+                    st_stream(reinterpret_cast<uint4 *>(sum_out + row * dim) + idx, v[i]);
                 }
-                st_stream(yr + idx, pack<T>(f));
             }
         }
-        if (PREFETCH) {
+        float s[2] = {0.f, 0.f};
 #pragma unroll
-            for (int i = 0; i < MAXV; ++i) v[i] = nxt[i];
+        for (int i = 0; i < MAXV; ++i)
+            if (lane + 32 * i < nvec) LnVec<T>::sum(v[i], s);
+        const float mean = warp_sum(s[0] + s[1]) * inv_d;
+        float q[2] = {0.f, 0.f};
+#pragma unroll
+        for (int i = 0; i < MAXV; ++i)
+            if (lane + 32 * i < nvec) LnVec<T>::sq(v[i], mean, q);
+        const float var = warp_sum(q[0] + q[1]) * inv_d;
+        const float rstd = 1.0f / sqrtf(var + eps);
+#pragma unroll
+        for (int i = 0; i < MAXV; ++i) {
+            const int idx = lane + 32 * i;
+            if (idx < nvec) st_stream(yr + idx, LnVec<T>::norm(v[i], mean, rstd, w + idx * VEC, b + idx * VEC));
         }
     }
 }
@@ -137,43 +187,60 @@ ln_block_kernel(const T *__restrict__ in, T *__restrict__ out, const float *__re
 }
 
 template <typename T, int MAXV>
-void launch_warp(const void *in, void *out, const float *w, const float *b, int64_t rows,
-                 int nvec, int dim, float eps, cudaStream_t stream) {
+void launch_warp(const void *in, const void *in2, void *sum_out, void *out, const float *w,
+                 const float *b, int64_t rows, int nvec, int dim, float eps, cudaStream_t stream) {
+    // persistent grid: as many CTAs as fit the SMs at once, so the staged scale / shift are
+    // reused for many rows
     int64_t blocks = (rows + kLnWarps - 1) / kLnWarps;
-    const int64_t cap = 148 * 8 * 4;
+    const int64_t cap = 148 * ln_min_blocks(MAXV);
     if (blocks > cap) blocks = cap;
-    ln_warp_kernel<T, MAXV, false><<<static_cast<unsigned>(blocks), kLnThreads, 0, stream>>>(
-        static_cast<const T *>(in), static_cast<T *>(out), w, b, rows, nvec, dim, eps);
+    const size_t smem = 2 * static_cast<size_t>(dim) * sizeof(float);
+    if (in2)
+        ln_warp_kernel<T, MAXV, true><<<static_cast<unsigned>(blocks), kLnThreads, smem, stream>>>(
+            static_cast<const T *>(in), static_cast<const T *>(in2), static_cast<T *>(sum_out),
+            static_cast<T *>(out), w, b, rows, nvec, dim, eps);
+    else
+        ln_warp_kernel<T, MAXV, false><<<static_cast<unsigned>(blocks), kLnThreads, smem, stream>>>(
+            static_cast<const T *>(in), nullptr, nullptr, static_cast<T *>(out), w, b, rows, nvec, dim, eps);
+}
+
+inline bool al16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Returns cudaErrorNotSupported when the row-in-registers kernel cannot take the shape.
+template <typename T>
+cudaError_t ln_warp_dispatch(const void *in, const void *in2, void *sum_out, void *out, const float *w,
+                             const float *b, int64_t rows, int64_t dim, float eps, cudaStream_t stream) {
+    constexpr int VEC = VecOf<T>::N;
+    const bool vec_ok = dim % VEC == 0 && al16(in) && al16(out) && al16(w) && al16(b) &&
+                        (!in2 || (al16(in2) && al16(sum_out)));
+    const int64_t nvec = dim / VEC;
+    if (!vec_ok || nvec > 32 * 16) return cudaErrorNotSupported;
+    const int need = static_cast<int>((nvec + 31) / 32);
+    const int nv = static_cast<int>(nvec), d = static_cast<int>(dim);
+    if (need <= 1) launch_warp<T, 1>(in, in2, sum_out, out, w, b, rows, nv, d, eps, stream);
+    else if (need <= 2) launch_warp<T, 2>(in, in2, sum_out, out, w, b, rows, nv, d, eps, stream);
+    else if (need <= 3) launch_warp<T, 3>(in, in2, sum_out, out, w, b, rows, nv, d, eps, stream);
+    else if (need <= 4) launch_warp<T, 4>(in, in2, sum_out, out, w, b, rows, nv, d, eps, stream);
+    else if (need <= 5) launch_warp<T, 5>(in, in2, sum_out, out, w, b, rows, nv, d, eps, stream);
+    else if (need <= 6) launch_warp<T, 6>(in, in2, sum_out, out, w, b, rows, nv, d, eps, stream);
+    else if (need <= 8) launch_warp<T, 8>(in, in2, sum_out, out, w, b, rows, nv, d, eps, stream);
+    else if (need <= 10) launch_warp<T, 10>(in, in2, sum_out, out, w, b, rows, nv, d, eps, stream);
+    else if (need <= 12) launch_warp<T, 12>(in, in2, sum_out, out, w, b, rows, nv, d, eps, stream);
+    else launch_warp<T, 16>(in, in2, sum_out, out, w, b, rows, nv, d, eps, stream);
+    cudaError_t err = cudaGetLastError();
+    if (err == cudaSuccess) g_launches.fetch_add(1);
+    return err;
 }
 
 template <typename T>
 cudaError_t ln_dispatch(const void *in, void *out, const float *w, const float *b, int64_t rows,
                         int64_t dim, float eps, cudaStream_t stream) {
-    constexpr int VEC = VecOf<T>::N;
-    const bool vec_ok = dim % VEC == 0 && (reinterpret_cast<uintptr_t>(in) & 15u) == 0 &&
-                        (reinterpret_cast<uintptr_t>(out) & 15u) == 0 &&
-                        (reinterpret_cast<uintptr_t>(w) & 15u) == 0 &&
-                        (reinterpret_cast<uintptr_t>(b) & 15u) == 0;
-    const int64_t nvec = dim / VEC;
-    if (vec_ok && nvec <= 32 * 16) {
-        const int need = static_cast<int>((nvec + 31) / 32);
-        const int nv = static_cast<int>(nvec), d = static_cast<int>(dim);
-        if (need <= 1) launch_warp<T, 1>(in, out, w, b, rows, nv, d, eps, stream);
-        else if (need <= 2) launch_warp<T, 2>(in, out, w, b, rows, nv, d, eps, stream);
-        else if (need <= 3) launch_warp<T, 3>(in, out, w, b, rows, nv, d, eps, stream);
-        else if (need <= 4) launch_warp<T, 4>(in, out, w, b, rows, nv, d, eps, stream);
-        else if (need <= 5) launch_warp<T, 5>(in, out, w, b, rows, nv, d, eps, stream);
-        else if (need <= 6) launch_warp<T, 6>(in, out, w, b, rows, nv, d, eps, stream);
-        else if (need <= 8) launch_warp<T, 8>(in, out, w, b, rows, nv, d, eps, stream);
-        else if (need <= 10) launch_warp<T, 10>(in, out, w, b, rows, nv, d, eps, stream);
-        else if (need <= 12) launch_warp<T, 12>(in, out, w, b, rows, nv, d, eps, stream);
-        else launch_warp<T, 16>(in, out, w, b, rows, nv, d, eps, stream);
-    } else {
-        int64_t blocks = rows < 148 * 8 ? rows : 148 * 8;
-        ln_block_kernel<T><<<static_cast<unsigned>(blocks), kLnThreads, 0, stream>>>(
-            static_cast<const T *>(in), static_cast<T *>(out), w, b, rows, dim, eps);
-    }
-    cudaError_t err = cudaGetLastError();
+    cudaError_t err = ln_warp_dispatch<T>(in, nullptr, nullptr, out, w, b, rows, dim, eps, stream);
+    if (err != cudaErrorNotSupported) return err;
+    int64_t blocks = rows < 148 * 8 ? rows : 148 * 8;
+    ln_block_kernel<T><<<static_cast<unsigned>(blocks), kLnThreads, 0, stream>>>(
+        static_cast<const T *>(in), static_cast<T *>(out), w, b, rows, dim, eps);
+    err = cudaGetLastError();
     if (err == cudaSuccess) g_launches.fetch_add(1);
     return err;
 }
@@ -185,6 +252,21 @@ cudaError_t ln_launch(const void *in, void *out, const float *w, const float *b,
     if (rows == 0 || dim == 0) return cudaSuccess;
     return dtype == kF16 ? ln_dispatch<__half>(in, out, w, b, rows, dim, eps, stream)
                          : ln_dispatch<float>(in, out, w, b, rows, dim, eps, stream);
+}
+
+// sum_out = a + b, out = LayerNorm(sum_out).  One launch when the row-in-registers kernel takes
+// the shape; otherwise the add kernel followed by the LayerNorm fallback (same results).
+cudaError_t add_ln_launch(const void *a, const void *b2, void *sum_out, void *out, const float *w,
+                          const float *b, int64_t rows, int64_t dim, float eps, int dtype,
+                          cudaStream_t stream) {
+    if (rows == 0 || dim == 0) return cudaSuccess;
+    cudaError_t err = dtype == kF16
+                          ? ln_warp_dispatch<__half>(a, b2, sum_out, out, w, b, rows, dim, eps, stream)
+                          : ln_warp_dispatch<float>(a, b2, sum_out, out, w, b, rows, dim, eps, stream);
+    if (err != cudaErrorNotSupported) return err;
+    err = add_launch(a, b2, sum_out, rows * dim, dtype, stream);
+    if (err != cudaSuccess) return err;
+    return ln_launch(sum_out, out, w, b, rows, dim, eps, dtype, stream);
 }
 
 }  // namespace sdfl

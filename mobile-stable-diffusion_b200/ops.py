@@ -14,7 +14,7 @@ from . import _capi
 from ._capi import F16, F32, GN_AUTO, GN_RESIDENT, GN_SPLIT, SdflError, check, lib
 
 __all__ = [
-    "groupnorm", "groupnorm_noalloc", "groupnorm_plan", "layernorm", "gelu_multiply", "silu", "gelu", "quick_gelu",
+    "groupnorm", "groupnorm_noalloc", "groupnorm_plan", "layernorm", "add_layernorm", "gelu_multiply", "silu", "gelu", "quick_gelu",
     "elemwise_add", "token_embedding", "timestep_embedding", "local_reduction_mean",
     "local_reduction_variance", "group_norm_apply", "layer_norm_apply", "device_status",
     "selftest_bounded_wait",
@@ -143,6 +143,24 @@ def layernorm(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor, eps: flo
                                          _f32(beta, "beta"), rows, D, eps, _dtype_code(x),
                                          _stream(stream)), "sdfl_layernorm_forward")
     return out
+
+
+def add_layernorm(a: torch.Tensor, b: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor,
+                  eps: float = 1e-5, sum_out: torch.Tensor | None = None,
+                  out: torch.Tensor | None = None, stream=None):
+    """sum = a + b (may be written over a), out = LayerNorm(sum); returns (sum, out)."""
+    if a.shape != b.shape or a.dtype != b.dtype:
+        raise ValueError("a and b must match")
+    sum_out = torch.empty_like(a) if sum_out is None else sum_out
+    out = torch.empty_like(a) if out is None else out
+    D = a.shape[-1]
+    rows = a.numel() // D if D else 0
+    with torch.cuda.device(a.device):
+        check(lib.sdfl_add_layernorm_forward(_dev(a, "a"), _dev(b, "b"), _dev(sum_out, "sum_out"),
+                                             _dev(out, "out"), _f32(gamma, "gamma"), _f32(beta, "beta"),
+                                             rows, D, eps, _dtype_code(a), _stream(stream)),
+              "sdfl_add_layernorm_forward")
+    return sum_out, out
 
 
 def gelu_multiply(ab: torch.Tensor, out: torch.Tensor | None = None, stream=None) -> torch.Tensor:

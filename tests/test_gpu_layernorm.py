@@ -107,3 +107,29 @@ def test_full_size_rows_have_zero_mean_unit_variance(sdfl):
     assert float(mean.abs().max()) < 2e-3 and float((var - 1).abs().max()) < 5e-3
     assert torch.equal(y, sdfl.ops.layernorm(x, torch.ones(D, device="cuda"),
                                              torch.zeros(D, device="cuda"), 1e-5))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "float16"])
+@pytest.mark.parametrize("rows,D", [(8192, 320), (1024, 640), (256, 1280), (154, 768), (7, 100), (3, 16384)])
+def test_add_then_layernorm_equals_the_reference_two_steps(sdfl, rows, D, dtype):
+    """elemwise_add into the residual, then LayerNorm of it (BasicTransformerBlock.cpp:126-136)."""
+    rng = rng_for(4, rows + D)
+    a = (rng.standard_normal((rows, D)) * 1.2).astype(np.float32).astype(NP_DTYPE[dtype])
+    b = (rng.standard_normal((rows, D)) * 0.7 + 0.1).astype(np.float32).astype(NP_DTYPE[dtype])
+    gamma = (1.0 + 0.1 * rng.standard_normal(D)).astype(np.float32)
+    beta = (0.1 * rng.standard_normal(D)).astype(np.float32)
+    want_sum = oracle.elemwise_add(a.astype(np.float32), b.astype(np.float32)).astype(NP_DTYPE[dtype])
+    want = oracle.layer_norm(want_sum.astype(np.float32), gamma, beta, 1e-5)
+    da = to_dev(a)
+    s, y = sdfl.ops.add_layernorm(da, to_dev(b), to_dev(gamma), to_dev(beta), 1e-5, sum_out=da)
+    assert s.data_ptr() == da.data_ptr()                 # the sum went over `a`, as the reference does
+    assert to_np(s).tobytes() == want_sum.tobytes(), "the residual sum must be bit exact"
+    assert_close(to_np(y), want, TOL[dtype], f"add+LN {rows}x{D} {dtype}")
+
+
+def test_add_layernorm_rejects_out_overlapping_the_sum(sdfl):
+    a = torch.zeros((4, 64), device="cuda")
+    g = torch.ones(64, device="cuda")
+    with pytest.raises(sdfl.SdflError) as e:
+        sdfl.ops.add_layernorm(a, torch.zeros_like(a), g, g, sum_out=a, out=a)
+    assert e.value.status == sdfl._capi.ERR_OVERLAP
