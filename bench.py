@@ -483,6 +483,18 @@ def op_cases(torch, ops, dev):
     gn("profiling size GN+SiLU f16 [4,128,512,512]", 4, 128, 512, f16, 1e-6)
     gn("GN+SiLU f32 [8,256,256,256]", 8, 256, 256, f32, 1e-6)
 
+    def gn_bias(name, B, C, H, dtype, eps):
+        x, e = rnd((B, C, H, H), dtype), rnd((B, C), dtype)
+        y = torch.empty_like(x)
+        g, b = 1 + 0.1 * rnd((C,), f32), 0.1 * rnd((C,), f32)
+        nbytes = 2 * x.numel() * x.element_size() + 2 * C * 4 + e.numel() * e.element_size()
+        cases.append((name, nbytes, lambda: ops.groupnorm_bias(x, e, g, b, 32, eps, True, out=y),
+                      ("gnbias", B, C, H, eps)))
+
+    gn_bias("next: chunkwise_add+GN+SiLU f16 [2,320,64,64]", 2, 320, 64, f16, 1e-5)
+    gn_bias("next: chunkwise_add+GN+SiLU f16 [2,1280,16,16]", 2, 1280, 16, f16, 1e-5)
+    gn_bias("next: chunkwise_add+GN+SiLU f16 [8,256,256,256] (large)", 8, 256, 256, f16, 1e-5)
+
     def ln(name, rows, D, dtype):
         x = rnd((rows, D), dtype)
         y = torch.empty_like(x)
@@ -574,6 +586,14 @@ def cpu_reference_case(spec) -> dict:
         x = rng.standard_normal((1, C, H, H), dtype=np.float32)
         g, b = np.ones(C, np.float32), np.zeros(C, np.float32)
         t = timed(lambda: oracle.group_norm(x, g, b, 32, eps, True, backend=backend), reps=2)
+        scale, note = float(B), f"one image x {B}"
+    elif kind == "gnbias":
+        _, B, C, H, eps = spec
+        x = rng.standard_normal((C, H, H), dtype=np.float32)
+        e = rng.standard_normal(C, dtype=np.float32)
+        g, b = np.ones(C, np.float32), np.zeros(C, np.float32)
+        t = timed(lambda: oracle.group_norm(oracle.chunkwise_add(x, e, H * H, backend=backend)[None],
+                                            g, b, 32, eps, True, backend=backend), reps=2)
         scale, note = float(B), f"one image x {B}"
     elif kind == "ln":
         _, rows, D = spec

@@ -119,6 +119,22 @@ int sdfl_groupnorm_forward_noalloc(const void *in, void *out, const float *gamma
                                    int64_t batch, int64_t channels, int64_t hw, int64_t num_groups,
                                    float eps, int fuse_silu, int dtype, void *stream);
 
+/* GroupNorm(+SiLU) of x + e, where e[n, c] is a per-(image, channel) addend of the storage type
+ * ([batch, channels]): the time-embedding broadcast add that precedes the out-norm of a ResBlock,
+ * fused into the norm.  Replaces chunkwise_add (K/util.cl:136-148, launched at
+ * NN/ResBlock.cpp:188-199) + GroupNorm::forward (NN/ResBlock.cpp:222) + silu (:225-231): six
+ * more tensor passes saved on top of the plain fusion.  The sum is formed in fp32 and is not
+ * written back.  Workspace as for sdfl_groupnorm_forward. */
+int sdfl_groupnorm_bias_forward(const void *in, const void *channel_bias, void *out, const float *gamma,
+                                const float *beta, int64_t batch, int64_t channels, int64_t hw,
+                                int64_t num_groups, float eps, int fuse_silu, int dtype, void *workspace,
+                                size_t workspace_bytes, void *stream);
+
+/* K/util.cl:136-148  chunkwise_add(A, chunk, C, chunk_size) over n work-items:
+ * C[i] = A[i] + chunk[i / chunk_size]; C may be A (NN/ResBlock.cpp:188-191). */
+int sdfl_chunkwise_add(const void *A, const void *chunk, void *C, int64_t n, int64_t chunk_size,
+                       int dtype, void *stream);
+
 /* LayerNorm over the last dimension of [rows, dim].
  * Replaces LayerNorm::forward (NN/LayerNorm.cpp:66-162; K/layer_norm.cl:1-78).  eps is an
  * argument; the reference fixes it at 1e-5 (K/layer_norm.cl:58).  The reference demands

@@ -49,6 +49,8 @@ SIGNATURES = {
                                        _i, _i, _p]),
     "sdfl_groupnorm_workspace_bytes_ex": (_sz, [_i64, _i64, _i64, _i64, _i, _i, _i]),
     "sdfl_groupnorm_forward_noalloc": (_i, [_p, _p, _p, _p, _i64, _i64, _i64, _i64, _f, _i, _i, _p]),
+    "sdfl_groupnorm_bias_forward": (_i, [_p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _f, _i, _i, _p, _sz, _p]),
+    "sdfl_chunkwise_add": (_i, [_p, _p, _p, _i64, _i64, _i, _p]),
     "sdfl_groupnorm_plan": (_i, [_i64, _i64, _i64, _i64, _i, _i, _i, C.POINTER(_i64)]),
     "sdfl_layernorm_forward": (_i, [_p, _p, _p, _p, _i64, _i64, _f, _i, _p]),
     "sdfl_add_layernorm_forward": (_i, [_p, _p, _p, _p, _p, _p, _i64, _i64, _f, _i, _p]),

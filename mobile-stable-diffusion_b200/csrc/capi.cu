@@ -58,7 +58,8 @@ int gn_validate(const void *in, const void *out, const float *gamma, const float
 
 int gn_forward(const void *in, void *out, const float *gamma, const float *beta, int64_t batch,
                int64_t channels, int64_t hw, int64_t groups, float eps, int fuse_silu, int dtype,
-               void *workspace, size_t workspace_bytes, int path, int cluster, cudaStream_t stream) {
+               void *workspace, size_t workspace_bytes, int path, int cluster, cudaStream_t stream,
+               const void *bias = nullptr) {
     int rc = gn_validate(in, out, gamma, beta, batch, channels, hw, groups, eps, dtype);
     if (rc != SDFL_OK) return rc;
     if (batch == 0 || hw == 0) return SDFL_OK;
@@ -71,7 +72,7 @@ int gn_forward(const void *in, void *out, const float *gamma, const float *beta,
     if (e != cudaSuccess) return cuda_fail(e);
     if (plan.path == sdfl::kGnSplit && (workspace == nullptr || workspace_bytes < plan.workspace))
         return SDFL_ERR_WORKSPACE;
-    return wrap(sdfl::gn_launch(s, plan, in, out, gamma, beta, workspace, stream));
+    return wrap(sdfl::gn_launch(s, plan, in, out, gamma, beta, workspace, stream, bias));
 }
 
 int unary(int act, const void *src, void *dst, int64_t n, int dtype, void *stream) {
@@ -153,6 +154,24 @@ int sdfl_groupnorm_forward_noalloc(const void *in, void *out, const float *gamma
     if (e != cudaSuccess) return cuda_fail(e);
     if (plan.workspace > sdfl::kGnStaticScratchBytes) return SDFL_ERR_WORKSPACE;   // beyond the fixed array
     return wrap(sdfl::gn_launch_static_scratch(s, plan, in, out, gamma, beta, as_stream(stream)));
+}
+
+int sdfl_groupnorm_bias_forward(const void *in, const void *channel_bias, void *out, const float *gamma,
+                                const float *beta, int64_t batch, int64_t channels, int64_t hw,
+                                int64_t num_groups, float eps, int fuse_silu, int dtype, void *workspace,
+                                size_t workspace_bytes, void *stream) {
+    if (!channel_bias && batch > 0 && hw > 0) return SDFL_ERR_INVALID_POINTER;
+    return gn_forward(in, out, gamma, beta, batch, channels, hw, num_groups, eps, fuse_silu, dtype,
+                      workspace, workspace_bytes, SDFL_GN_AUTO, 0, as_stream(stream), channel_bias);
+}
+
+int sdfl_chunkwise_add(const void *A, const void *chunk, void *C, int64_t n, int64_t chunk_size,
+                       int dtype, void *stream) {
+    if (!dtype_ok(dtype) || n < 0 || chunk_size <= 0) return SDFL_ERR_INVALID_VALUE;
+    if (n == 0) return SDFL_OK;
+    if (!A || !chunk || !C) return SDFL_ERR_INVALID_POINTER;
+    if (partial_overlap(A, n * esize(dtype), C, n * esize(dtype))) return SDFL_ERR_OVERLAP;
+    return wrap(sdfl::chunkwise_add_launch(A, chunk, C, n, chunk_size, dtype, as_stream(stream)));
 }
 
 int sdfl_groupnorm_plan(int64_t batch, int64_t channels, int64_t hw, int64_t num_groups, int dtype,

@@ -173,7 +173,32 @@ cudaError_t add_dispatch(const void *a, const void *b, void *c, int64_t n, cudaS
     return err;
 }
 
+// ---- C[i] = A[i] + chunk[i / chunk_size] ------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(kEwThreads)
+chunkwise_add_kernel(const T *a, const T *__restrict__ chunk, T *c, unsigned long long n,
+                     unsigned long long chunk_size) {
+    const unsigned long long stride = static_cast<unsigned long long>(gridDim.x) * kEwThreads;
+    for (unsigned long long i = static_cast<unsigned long long>(blockIdx.x) * kEwThreads + threadIdx.x;
+         i < n; i += stride)
+        c[i] = from_float<T>(to_float<T>(a[i]) + to_float<T>(chunk[i / chunk_size]));
+}
+
 }  // namespace
+
+cudaError_t chunkwise_add_launch(const void *a, const void *chunk, void *c, int64_t n,
+                                 int64_t chunk_size, int dtype, cudaStream_t stream) {
+    if (n == 0) return cudaSuccess;
+    if (dtype == kF16)
+        chunkwise_add_kernel<__half><<<ew_grid(n), kEwThreads, 0, stream>>>(
+            static_cast<const __half *>(a), static_cast<const __half *>(chunk), static_cast<__half *>(c), n, chunk_size);
+    else
+        chunkwise_add_kernel<float><<<ew_grid(n), kEwThreads, 0, stream>>>(
+            static_cast<const float *>(a), static_cast<const float *>(chunk), static_cast<float *>(c), n, chunk_size);
+    cudaError_t err = cudaGetLastError();
+    if (err == cudaSuccess) g_launches.fetch_add(1);
+    return err;
+}
 
 cudaError_t act_launch(int act, const void *src, void *dst, int64_t n, int dtype, cudaStream_t stream) {
     if (n == 0) return cudaSuccess;

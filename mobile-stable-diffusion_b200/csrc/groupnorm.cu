@@ -347,14 +347,19 @@ struct ResidentArgs {
     uint32_t hold;         // chunks kept in their slots between the two passes (re-read mode)
     uint32_t vec_uniform;  // hw % lanes-per-vector == 0
     uint32_t hw_vecs;      // hw / lanes-per-vector (when vec_uniform)
+    uint32_t channels;     // C (row length of `bias`)
+    const void *bias;      // [batch, C] addend of the storage type, or nullptr
     float eps;
     FastDiv hw_div;        // element offset -> channel
     FastDiv hwv_div;       // vector offset -> channel (when vec_uniform)
 };
 
-// blockDim.x = consumer threads (a multiple of 32) + one producer warp.  BIG: one CTA of up to
-// 1024 threads per SM; otherwise up to 512 threads and at least three CTAs per SM, which caps
-// the kernel at 40 registers per thread.
+// blockDim.x = consumer threads (a multiple of 32, at most 480) + one producer warp; at least
+// two CTAs per SM, i.e. up to 64 registers per thread.
+// BIAS: a per-(image, channel) addend is applied before the statistics (the reference's
+// chunkwise_add in front of the out-norm of a ResBlock, ResBlock.cpp:188-231).  x + e only
+// moves the shift of the shifted sums and the mean of the normalise pass, so it costs no
+// instruction per element.
 //
 // Shared memory is a ring of `nslots` chunk slots.  The producer numbers its chunk loads
 // n = 0, 1, 2, ... across slabs; load n goes to slot n % nslots and completes phase
@@ -365,8 +370,8 @@ struct ResidentArgs {
 //             with the next slab's chunks meanwhile.
 //   otherwise the chunks are released after the moments pass and loaded a second time for the
 //             normalise pass (this second read is served by L2 when the clusters' slabs fit it).
-template <typename T, int ACT, bool BIG>
-__global__ void __launch_bounds__(BIG ? 1024 : 512, BIG ? 1 : 2)
+template <typename T, int ACT, bool BIAS>
+__global__ void __launch_bounds__(512, 2)
 gn_resident_kernel(const ResidentArgs a) {
     constexpr int VEC = VecOf<T>::N;
     constexpr bool HALF = sizeof(T) == 2;
@@ -477,6 +482,10 @@ gn_resident_kernel(const ResidentArgs a) {
     for (uint32_t unit = cluster_id; unit < a.units; unit += nclusters, ++it) {
         const uint32_t par = it & 1u;
         const uint32_t p0 = pos;
+        // this slab's addends: bias[image, group's first channel ...]
+        const T *erow = BIAS ? static_cast<const T *>(a.bias) +
+                                   static_cast<size_t>(unit / a.groups) * a.channels + (unit % a.groups) * a.cpg
+                             : nullptr;
 
         // pass 1: shifted sums, chunk by chunk as the copies land
         float s[2] = {0.f, 0.f}, q[2] = {0.f, 0.f};
@@ -490,10 +499,45 @@ gn_resident_kernel(const ResidentArgs a) {
             const uint4 *sv = reinterpret_cast<const uint4 *>(data + slot * chunk_bytes);
             if (j == 0) shift = to_float<T>(reinterpret_cast<const T *>(sv)[0]);
             const uint32_t cnt = min(cv, nv - j * cv);
+            if (!BIAS) {
 #pragma unroll 2
-            for (uint32_t i = tid; i < cnt; i += consumers) {
-                stats_vec<T>(sv[i], shift, s, q);
-                ++nvec_mine;
+                for (uint32_t i = tid; i < cnt; i += consumers) {
+                    stats_vec<T>(sv[i], shift, s, q);
+                    ++nvec_mine;
+                }
+            } else if (a.vec_uniform && hwv >= consumers) {
+                // (x + e_c) - shift = x - (shift - e_c): walk channel by channel
+                const uint32_t lo = j * cv, hi = lo + cnt;
+                uint32_t i0 = lo;
+                while (i0 < hi) {
+                    const uint32_t c = a.hwv_div.div(v0 + i0);
+                    const uint32_t seg_end = min(hi, (c + 1) * hwv - v0);
+                    const float e = to_float<T>(erow[c]);
+                    if (j == 0 && i0 == lo) shift += e;          // shift = first value of x + e
+                    const float sh = shift - e;
+#pragma unroll 2
+                    for (uint32_t i = i0 + tid; i < seg_end; i += consumers) {
+                        stats_vec<T>(sv[i - lo], sh, s, q);
+                        ++nvec_mine;
+                    }
+                    i0 = seg_end;
+                }
+            } else {
+                const uint32_t lo = j * cv;
+                for (uint32_t i = tid; i < cnt; i += consumers) {
+                    float f[VEC];
+                    unpack<T>(sv[i], f);
+                    const uint32_t e0 = (v0 + lo + i) * VEC;
+                    float sl[2] = {0.f, 0.f}, ql[2] = {0.f, 0.f};
+#pragma unroll
+                    for (int l = 0; l < VEC; ++l) {
+                        const float d = f[l] + to_float<T>(erow[a.hw_div.div(e0 + l)]) - shift;
+                        sl[l & 1] += d;
+                        ql[l & 1] = fmaf(d, d, ql[l & 1]);
+                    }
+                    s[0] += sl[0]; s[1] += sl[1]; q[0] += ql[0]; q[1] += ql[1];
+                    ++nvec_mine;
+                }
             }
             if (j + H < P) {       // not one of the chunks held for pass 2
                 __syncwarp();
@@ -570,7 +614,8 @@ gn_resident_kernel(const ResidentArgs a) {
                 while (i0 < hi) {
                     const uint32_t c = a.hwv_div.div(v0 + i0);
                     const uint32_t seg_end = min(hi, (c + 1) * hwv - v0);
-                    const Affine<T> af = make_affine<T, ACT>(mean, rstd, __ldg(a.w + ch0 + c),
+                    const float mc = BIAS ? mean - to_float<T>(erow[c]) : mean;
+                    const Affine<T> af = make_affine<T, ACT>(mc, rstd, __ldg(a.w + ch0 + c),
                                                             __ldg(a.b + ch0 + c));
 #pragma unroll 2
                     for (uint32_t i = i0 + tid; i < seg_end; i += consumers)
@@ -579,8 +624,9 @@ gn_resident_kernel(const ResidentArgs a) {
                 }
             } else if (a.vec_uniform) {
                 for (uint32_t i = lo + tid; i < hi; i += consumers) {
-                    const uint32_t c = ch0 + a.hwv_div.div(v0 + i);
-                    const Affine<T> af = make_affine<T, ACT>(mean, rstd, __ldg(a.w + c), __ldg(a.b + c));
+                    const uint32_t cl = a.hwv_div.div(v0 + i), c = ch0 + cl;
+                    const float mc = BIAS ? mean - to_float<T>(erow[cl]) : mean;
+                    const Affine<T> af = make_affine<T, ACT>(mc, rstd, __ldg(a.w + c), __ldg(a.b + c));
                     st_stream(&gv[i], norm_vec<T, ACT>(sv[i - lo], af));
                 }
             } else {
@@ -590,9 +636,10 @@ gn_resident_kernel(const ResidentArgs a) {
                     const uint32_t e = (v0 + i) * VEC;
 #pragma unroll
                     for (int l = 0; l < VEC; ++l) {
-                        const uint32_t c = ch0 + a.hw_div.div(e + l);
+                        const uint32_t cl = a.hw_div.div(e + l), c = ch0 + cl;
+                        const float mc = BIAS ? mean - to_float<T>(erow[cl]) : mean;
                         f[l] = activate<ACT, HALF>(
-                            fmaf((f[l] - mean) * rstd, __ldg(a.w + c), __ldg(a.b + c)));
+                            fmaf((f[l] - mc) * rstd, __ldg(a.w + c), __ldg(a.b + c)));
                     }
                     st_stream(&gv[i], pack<T>(f));
                 }
@@ -617,6 +664,8 @@ struct SplitArgs {
     void *out;
     const float *w;
     const float *b;
+    const void *bias;      // [batch, C] addend of the storage type, or nullptr
+    uint32_t channels;     // C
     float *partial;        // [units * splits * 2]  (mean, M2) per chunk
     uint32_t slab_elems;
     uint32_t chunk_elems;  // multiple of the vector width when `vec` is set
@@ -636,17 +685,25 @@ __global__ void __launch_bounds__(kSplitThreads) gn_split_stats_kernel(const Spl
     const uint32_t e0 = split * a.chunk_elems;
     const uint32_t e1 = min(a.slab_elems, e0 + a.chunk_elems);
     const T *x = static_cast<const T *>(a.in) + static_cast<size_t>(unit) * a.slab_elems;
+    const T *erow = a.bias ? static_cast<const T *>(a.bias) +
+                                 static_cast<size_t>(unit / a.groups) * a.channels + (unit % a.groups) * a.cpg
+                           : nullptr;
     Shifted sh{0.f, 0.f, 0.f, 0.f};
     if (a.vec) {
         const uint4 *xv = reinterpret_cast<const uint4 *>(x);
         for (uint32_t i = e0 / VEC + threadIdx.x; i < e1 / VEC; i += kSplitThreads) {
             float f[VEC];
             unpack<T>(__ldg(xv + i), f);
+            if (erow) {
+#pragma unroll
+                for (int j = 0; j < VEC; ++j) f[j] += to_float<T>(erow[a.hw_div.div(i * VEC + j)]);
+            }
 #pragma unroll
             for (int j = 0; j < VEC; ++j) sh.add(f[j]);
         }
     } else {
-        for (uint32_t i = e0 + threadIdx.x; i < e1; i += kSplitThreads) sh.add(to_float<T>(x[i]));
+        for (uint32_t i = e0 + threadIdx.x; i < e1; i += kSplitThreads)
+            sh.add(to_float<T>(x[i]) + (erow ? to_float<T>(erow[a.hw_div.div(i)]) : 0.f));
     }
     Moments m = warp_merge(sh.done());
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -696,6 +753,9 @@ __global__ void __launch_bounds__(kSplitThreads) gn_split_apply_kernel(const Spl
     const size_t base = static_cast<size_t>(unit) * a.slab_elems;
     const T *x = static_cast<const T *>(a.in) + base;
     T *y = static_cast<T *>(a.out) + base;
+    const T *erow = a.bias ? static_cast<const T *>(a.bias) +
+                                 static_cast<size_t>(unit / a.groups) * a.channels + ch0
+                           : nullptr;
     if (a.vec) {
         const uint4 *xv = reinterpret_cast<const uint4 *>(x);
         uint4 *yv = reinterpret_cast<uint4 *>(y);
@@ -703,25 +763,28 @@ __global__ void __launch_bounds__(kSplitThreads) gn_split_apply_kernel(const Spl
             float f[VEC];
             unpack<T>(ld_stream(xv + i), f);
             if (a.vec_uniform) {
-                const uint32_t c = ch0 + a.hw_div.div(i * VEC);
+                const uint32_t cl = a.hw_div.div(i * VEC), c = ch0 + cl;
                 const float wv = __ldg(a.w + c), bv = __ldg(a.b + c);
+                const float mc = erow ? mean - to_float<T>(erow[cl]) : mean;
 #pragma unroll
                 for (int j = 0; j < VEC; ++j)
-                    f[j] = activate<ACT, HALF>(fmaf((f[j] - mean) * rstd, wv, bv));
+                    f[j] = activate<ACT, HALF>(fmaf((f[j] - mc) * rstd, wv, bv));
             } else {
 #pragma unroll
                 for (int j = 0; j < VEC; ++j) {
-                    const uint32_t c = ch0 + a.hw_div.div(i * VEC + j);
+                    const uint32_t cl = a.hw_div.div(i * VEC + j), c = ch0 + cl;
+                    const float mc = erow ? mean - to_float<T>(erow[cl]) : mean;
                     f[j] = activate<ACT, HALF>(
-                        fmaf((f[j] - mean) * rstd, __ldg(a.w + c), __ldg(a.b + c)));
+                        fmaf((f[j] - mc) * rstd, __ldg(a.w + c), __ldg(a.b + c)));
                 }
             }
             st_stream(yv + i, pack<T>(f));
         }
     } else {
         for (uint32_t i = e0 + threadIdx.x; i < e1; i += kSplitThreads) {
-            const uint32_t c = ch0 + a.hw_div.div(i);
-            const float v = fmaf((to_float<T>(x[i]) - mean) * rstd, __ldg(a.w + c), __ldg(a.b + c));
+            const uint32_t cl = a.hw_div.div(i), c = ch0 + cl;
+            const float mc = erow ? mean - to_float<T>(erow[cl]) : mean;
+            const float v = fmaf((to_float<T>(x[i]) - mc) * rstd, __ldg(a.w + c), __ldg(a.b + c));
             y[i] = from_float<T>(activate<ACT, HALF>(v));
         }
     }
@@ -794,14 +857,14 @@ inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 
 // the opt-in for 16-CTA clusters), so that launches themselves make no attribute calls.
 constexpr int kMaxDevices = 64;
 
-template <typename T, int ACT, bool BIG>
+template <typename T, int ACT, bool BIAS>
 cudaError_t ensure_resident_attrs() {
     static std::atomic<bool> done[kMaxDevices];
     int dev = 0;
     cudaError_t err = cudaGetDevice(&dev);
     if (err != cudaSuccess) return err;
     if (dev >= 0 && dev < kMaxDevices && done[dev].load(std::memory_order_acquire)) return cudaSuccess;
-    auto kernel = gn_resident_kernel<T, ACT, BIG>;
+    auto kernel = gn_resident_kernel<T, ACT, BIAS>;
     err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                static_cast<int>(kHeaderBytes + kMaxPartBytes));
     if (err != cudaSuccess) return err;
@@ -826,23 +889,23 @@ inline void cluster_config(cudaLaunchConfig_t *cfg, cudaLaunchAttribute *attr, u
     cfg->numAttrs = 1;
 }
 
-template <typename T, int ACT, bool BIG>
+template <typename T, int ACT, bool BIAS>
 cudaError_t launch_resident_as(const ResidentArgs &a, const GnPlan &plan, cudaStream_t stream) {
-    cudaError_t err = ensure_resident_attrs<T, ACT, BIG>();
+    cudaError_t err = ensure_resident_attrs<T, ACT, BIAS>();
     if (err != cudaSuccess) return err;
     cudaLaunchConfig_t cfg;
     cudaLaunchAttribute attr[1];
     cluster_config(&cfg, attr, static_cast<unsigned>(plan.nclusters * plan.cluster), plan.cluster,
                    plan.threads, plan.smem, stream);
-    err = cudaLaunchKernelEx(&cfg, gn_resident_kernel<T, ACT, BIG>, a);
+    err = cudaLaunchKernelEx(&cfg, gn_resident_kernel<T, ACT, BIAS>, a);
     if (err == cudaSuccess) g_launches.fetch_add(1);
     return err;
 }
 
 template <typename T, int ACT>
 cudaError_t launch_resident(const ResidentArgs &a, const GnPlan &plan, cudaStream_t stream) {
-    return plan.threads > 512 ? launch_resident_as<T, ACT, true>(a, plan, stream)
-                              : launch_resident_as<T, ACT, false>(a, plan, stream);
+    return a.bias ? launch_resident_as<T, ACT, true>(a, plan, stream)
+                  : launch_resident_as<T, ACT, false>(a, plan, stream);
 }
 
 // How many clusters of this size, block size and shared-memory footprint can be resident at
@@ -864,16 +927,13 @@ cudaError_t resident_active_clusters(int cluster, int threads, size_t smem, int 
         auto it = cache.find(key);
         if (it != cache.end()) { *active = it->second; return cudaSuccess; }
     }
-    err = threads > 512 ? ensure_resident_attrs<T, kActSilu, true>()
-                        : ensure_resident_attrs<T, kActSilu, false>();
+    err = ensure_resident_attrs<T, kActSilu, false>();
     if (err != cudaSuccess) return err;
     cudaLaunchConfig_t cfg;
     cudaLaunchAttribute attr[1];
     cluster_config(&cfg, attr, static_cast<unsigned>(cluster), cluster, threads, smem, nullptr);
     int n = 0;
-    err = threads > 512
-              ? cudaOccupancyMaxActiveClusters(&n, gn_resident_kernel<T, kActSilu, true>, &cfg)
-              : cudaOccupancyMaxActiveClusters(&n, gn_resident_kernel<T, kActSilu, false>, &cfg);
+    err = cudaOccupancyMaxActiveClusters(&n, gn_resident_kernel<T, kActSilu, false>, &cfg);
     if (err != cudaSuccess) return err;
     *active = n;
     std::lock_guard<std::mutex> lock(mu);
@@ -942,7 +1002,7 @@ cudaError_t gn_make_plan(const GnShape &s, const void *in, const void *out, int 
             const size_t smem = kHeaderBytes + static_cast<size_t>(nslots * chunk_bytes);
             int consumers = k_cwarps > 0 ? k_cwarps * 32
                                          : (large ? 352 : part_bytes >= 8 * 1024 ? 224 : 96);
-            if (consumers > 992) consumers = 992;
+            if (consumers > 480) consumers = 480;
             const int threads = consumers + 32;
             int active = 0;
             cudaError_t err = s.dtype == kF16
@@ -988,7 +1048,8 @@ cudaError_t gn_make_plan(const GnShape &s, const void *in, const void *out, int 
 }
 
 cudaError_t gn_launch(const GnShape &s, const GnPlan &plan, const void *in, void *out,
-                      const float *w, const float *b, void *workspace, cudaStream_t stream) {
+                      const float *w, const float *b, void *workspace, cudaStream_t stream,
+                      const void *bias) {
     const int64_t esz = s.dtype == kF16 ? 2 : 4;
     const int64_t vec = 16 / esz;
     const int64_t cpg = s.channels / s.groups;
@@ -1007,6 +1068,8 @@ cudaError_t gn_launch(const GnShape &s, const GnPlan &plan, const void *in, void
         a.chunk_vecs = static_cast<uint32_t>(plan.chunk_vecs);
         a.nslots = static_cast<uint32_t>(plan.nslots);
         a.hold = static_cast<uint32_t>(plan.hold);
+        a.channels = static_cast<uint32_t>(s.channels);
+        a.bias = bias;
         a.vec_uniform = s.hw % vec == 0;
         a.hw_vecs = a.vec_uniform ? static_cast<uint32_t>(s.hw / vec) : 1u;
         a.eps = s.eps;
@@ -1023,6 +1086,8 @@ cudaError_t gn_launch(const GnShape &s, const GnPlan &plan, const void *in, void
     SplitArgs a;
     a.in = in; a.out = out; a.w = w; a.b = b;
     a.partial = static_cast<float *>(workspace);
+    a.bias = bias;
+    a.channels = static_cast<uint32_t>(s.channels);
     a.slab_elems = static_cast<uint32_t>(slab_elems);
     a.splits = static_cast<uint32_t>(plan.splits);
     int64_t chunk = (slab_elems + plan.splits - 1) / plan.splits;
@@ -1085,7 +1150,7 @@ cudaError_t gn_launch_static_scratch(const GnShape &s, const GnPlan &plan, const
     }
     // Nothing in the scratch has to start at zero: the statistics kernel overwrites every
     // (mean, M2) pair the apply kernel reads, and the two run in stream order.
-    return gn_launch(s, plan, in, out, w, b, ptr, stream);
+    return gn_launch(s, plan, in, out, w, b, ptr, stream, nullptr);
 }
 
 namespace {

@@ -46,8 +46,10 @@ struct GnShape {
 cudaError_t gn_make_plan(const GnShape &s, const void *in, const void *out, int force_path,
                          int force_cluster, GnPlan *plan);
 
+// bias: optional [batch, channels] addend of the storage type, applied before the statistics.
 cudaError_t gn_launch(const GnShape &s, const GnPlan &plan, const void *in, void *out,
-                      const float *w, const float *b, void *workspace, cudaStream_t stream);
+                      const float *w, const float *b, void *workspace, cudaStream_t stream,
+                      const void *bias = nullptr);
 
 // The split path with its scratch in a fixed array inside the library (64 KiB per device: up to
 // 8192 (mean, M2) pairs, i.e. batch * groups * chunks-per-slab <= 8192).  Allocates nothing; the
@@ -92,6 +94,9 @@ cudaError_t act_launch(int act, const void *src, void *dst, int64_t n, int dtype
                        cudaStream_t stream);
 cudaError_t add_launch(const void *a, const void *b, void *c, int64_t n, int dtype,
                        cudaStream_t stream);
+// C[i] = A[i] + chunk[i / chunk_size]   (util.cl:136-148)
+cudaError_t chunkwise_add_launch(const void *a, const void *chunk, void *c, int64_t n,
+                                 int64_t chunk_size, int dtype, cudaStream_t stream);
 
 // ---- Embeddings -------------------------------------------------------------------------------
 cudaError_t token_embedding_launch(const int64_t *ids, const void *table, const void *pos,

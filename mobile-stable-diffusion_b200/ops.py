@@ -14,7 +14,7 @@ from . import _capi
 from ._capi import F16, F32, GN_AUTO, GN_RESIDENT, GN_SPLIT, SdflError, check, lib
 
 __all__ = [
-    "groupnorm", "groupnorm_noalloc", "groupnorm_plan", "layernorm", "add_layernorm", "gelu_multiply", "silu", "gelu", "quick_gelu",
+    "groupnorm", "groupnorm_bias", "chunkwise_add", "groupnorm_noalloc", "groupnorm_plan", "layernorm", "add_layernorm", "gelu_multiply", "silu", "gelu", "quick_gelu",
     "elemwise_add", "token_embedding", "timestep_embedding", "local_reduction_mean",
     "local_reduction_variance", "group_norm_apply", "layer_norm_apply", "device_status",
     "selftest_bounded_wait",
@@ -108,6 +108,35 @@ def groupnorm(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor, num_grou
             _dev(x, "x"), _dev(out, "out"), _f32(gamma, "gamma"), _f32(beta, "beta"), B, Cc, hw,
             num_groups, eps, int(silu), code, ws.data_ptr(), ws.numel(), path, cluster_or_splits,
             _stream(stream)), "sdfl_groupnorm_forward")
+    return out
+
+
+def groupnorm_bias(x: torch.Tensor, channel_bias: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor,
+                   num_groups: int, eps: float = 1e-5, silu: bool = False,
+                   out: torch.Tensor | None = None, stream=None) -> torch.Tensor:
+    """act(GroupNorm(x + channel_bias[:, :, None, None])); channel_bias is [B, C] of x's dtype."""
+    _dev(x, "x")
+    out = torch.empty_like(x) if out is None else out
+    B, Cc = x.shape[0], x.shape[1]
+    if channel_bias.shape != (B, Cc) or channel_bias.dtype != x.dtype:
+        raise ValueError("channel_bias must be [batch, channels] of x's dtype")
+    hw = x.numel() // (B * Cc) if B * Cc else 0
+    code = _dtype_code(x)
+    ws = _workspace(x.device, lib.sdfl_groupnorm_workspace_bytes(B, Cc, hw, num_groups, code))
+    with torch.cuda.device(x.device):
+        check(lib.sdfl_groupnorm_bias_forward(
+            _dev(x, "x"), _dev(channel_bias, "channel_bias"), _dev(out, "out"), _f32(gamma, "gamma"),
+            _f32(beta, "beta"), B, Cc, hw, num_groups, eps, int(silu), code, ws.data_ptr(), ws.numel(),
+            _stream(stream)), "sdfl_groupnorm_bias_forward")
+    return out
+
+
+def chunkwise_add(a: torch.Tensor, chunk: torch.Tensor, chunk_size: int, out: torch.Tensor | None = None,
+                  stream=None) -> torch.Tensor:
+    out = torch.empty_like(a) if out is None else out
+    with torch.cuda.device(a.device):
+        check(lib.sdfl_chunkwise_add(_dev(a, "a"), _dev(chunk, "chunk"), _dev(out, "out"), a.numel(),
+                                     chunk_size, _dtype_code(a), _stream(stream)), "sdfl_chunkwise_add")
     return out
 
 

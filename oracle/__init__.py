@@ -70,6 +70,7 @@ def port_lib():
         for name in ("oracle_gelu", "oracle_silu", "oracle_quick_gelu"):
             getattr(lib, name).argtypes = [_f32p, _f32p, _sz]
         lib.oracle_elemwise_add.argtypes = [_f32p, _f32p, _f32p, _sz]
+        lib.oracle_chunkwise_add.argtypes = [_f32p, _f32p, _f32p, _sz, _sz]
         lib.oracle_token_embedding.argtypes = [_i64p, _f32p, _f32p, _f32p, _sz, _sz, _sz, _sz]
         lib.oracle_token_embedding.restype = C.c_int
         lib.oracle_timestep_embedding.argtypes = [_i64p, _f32p, _sz, _sz, C.c_float]
@@ -103,6 +104,7 @@ def ref_lib():
         lib.ref_silu.argtypes = [_f32p, _f32p, _sz]
         lib.ref_gelu.argtypes = [_f32p, _f32p, _sz]
         lib.ref_elemwise_add.argtypes = [_f32p, _f32p, _f32p, _sz]
+        lib.ref_chunkwise_add.argtypes = [_f32p, _f32p, _f32p, _sz, _sz]
         _ref = lib
     return _ref
 
@@ -250,6 +252,17 @@ def elemwise_add(a, b, backend: str = "port"):
         ref_lib().ref_elemwise_add(_fp(a), _fp(b), _fp(out), a.size)
     else:
         port_lib().oracle_elemwise_add(_fp(a), _fp(b), _fp(out), a.size)
+    return out
+
+
+def chunkwise_add(a, chunk, chunk_size: int, backend: str = "port"):
+    """out[i] = a[i] + chunk[i // chunk_size] over the flattened a."""
+    a, chunk = _c32(a), _c32(chunk)
+    out = np.empty_like(a)
+    if backend == "ref":
+        ref_lib().ref_chunkwise_add(_fp(a), _fp(chunk), _fp(out), a.size, chunk_size)
+    else:
+        port_lib().oracle_chunkwise_add(_fp(a), _fp(chunk), _fp(out), a.size, chunk_size)
     return out
 
 

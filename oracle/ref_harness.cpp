@@ -352,6 +352,12 @@ void ref_gelu(const float *src, float *dst, size_t n) {
     enqueue_1d_flat(n, [=] { ref_util::gelu(const_cast<float *>(src), dst); });
 }
 
+void ref_chunkwise_add(const float *A, const float *chunk, float *C, size_t n, size_t chunk_size) {
+    enqueue_1d_flat(n, [=] {
+        ref_util::chunkwise_add(const_cast<float *>(A), const_cast<float *>(chunk), C, chunk_size);
+    });
+}
+
 void ref_elemwise_add(const float *A, const float *B, float *C, size_t n) {
     enqueue_1d_flat(n, [=] {
         ref_util::elemwise_add(const_cast<float *>(A), const_cast<float *>(B), C);

@@ -219,6 +219,13 @@ void oracle_elemwise_add(const float *A, const float *B, float *C, size_t n) {
     for (long i = 0; i < (long)n; ++i) C[i] = A[i] + B[i];
 }
 
+/* util.cl:136-148: C[i] = A[i] + chunk[i / chunk_size] (the time-embedding broadcast add of
+ * nn/ResBlock.cpp:188-199, chunk_size = H*W). */
+void oracle_chunkwise_add(const float *A, const float *chunk, float *C, size_t n, size_t chunk_size) {
+#pragma omp parallel for schedule(static)
+    for (long i = 0; i < (long)n; ++i) C[i] = A[i] + chunk[(size_t)i / chunk_size];
+}
+
 /* TextEncoder::createTokenEmbeddingBuffer (TextEncoder.cpp:105-125): out[i,:] = table[token[i],:]
  * copied row by row (:117-120), then elemwise_add with the positional table in place
  * (TextEncoder.cpp:141-151).  Batch > 1 repeats the positional table per sequence.

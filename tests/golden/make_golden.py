@@ -73,6 +73,10 @@ def main() -> None:
     data["act.silu"] = oracle.silu(x, backend="ref")
     data["act.gelu"] = oracle.gelu(x, backend="ref")
     data["act.add"] = oracle.elemwise_add(x, other, backend="ref")
+    a = rng.standard_normal((6, 40)).astype(np.float32)
+    chunk = rng.standard_normal(6).astype(np.float32)
+    data["chunk.a"], data["chunk.chunk"] = a, chunk
+    data["chunk.y"] = oracle.chunkwise_add(a, chunk, 40, backend="ref")
     np.savez_compressed(OUT, **data)
     print(f"wrote {OUT}: {len(data)} arrays, {os.path.getsize(OUT)} bytes")
 

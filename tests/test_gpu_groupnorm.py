@@ -8,6 +8,8 @@ import torch
 from conftest import TOL, assert_close, rng_for
 from gpu_util import Guarded, gn_inputs, oracle_group_norm, to_dev, to_np
 
+import oracle
+
 pytestmark = pytest.mark.gpu
 
 GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "reference_kernels.npz")
@@ -201,3 +203,38 @@ def test_full_size_vae_tensor_properties(sdfl):
     diff = (ys.float() - ref.float()).abs()
     assert float((diff - 2e-3 * ref.float().abs()).max()) <= 2e-3
     assert sdfl.ops.device_status() == 0
+
+
+def oracle_bias_group_norm(x, e, gamma, beta, G, eps, silu):
+    """Reference sequence on one image at a time: chunkwise_add (util.cl:136-148) with
+    chunk_size = H*W, then GroupNorm::forward, then silu; fp32 throughout."""
+    B, C = x.shape[:2]
+    hw = int(np.prod(x.shape[2:]))
+    xs = np.stack([oracle.chunkwise_add(x[n].astype(np.float32), e[n].astype(np.float32), hw)
+                   for n in range(B)])
+    return oracle.group_norm(xs, gamma, beta, G, eps, silu)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "float16"])
+@pytest.mark.parametrize("shape,G", [((2, 320, 64, 64), 32), ((2, 1280, 8, 8), 32), ((2, 640, 32, 32), 32),
+                                     ((1, 128, 256, 256), 32), ((3, 6, 5, 7), 3), ((2, 64, 33, 31), 8)])
+def test_time_embedding_add_fused_into_the_norm(sdfl, shape, G, dtype):
+    """chunkwise_add -> out_group_norm -> silu of a ResBlock (nn/ResBlock.cpp:188-231) as one call."""
+    rng = rng_for(3, 700 + sum(shape))
+    x, gamma, beta = gn_inputs(rng, shape, dtype)
+    e = (rng.standard_normal(shape[:2]) * 0.8).astype(np.float32).astype(x.dtype)
+    for silu in (True, False):
+        want = oracle_bias_group_norm(x, e, gamma, beta, G, 1e-5, silu)
+        out = Guarded(shape, getattr(torch, dtype))
+        sdfl.ops.groupnorm_bias(to_dev(x), to_dev(e), to_dev(gamma), to_dev(beta), G, 1e-5, silu,
+                                out=out.tensor)
+        out.check()
+        assert_close(to_np(out.tensor), want, TOL[dtype], f"bias GN {shape} silu={silu}")
+    # the stand-alone kernel with the reference's name and argument order
+    hw = int(np.prod(shape[2:]))
+    got = sdfl.ops.chunkwise_add(to_dev(x[0]), to_dev(e[0]), hw)
+    want = oracle.chunkwise_add(x[0].astype(np.float32), e[0].astype(np.float32), hw)
+    if dtype == "float32":
+        assert to_np(got).tobytes() == want.tobytes()
+    else:
+        assert to_np(got).tobytes() == want.astype(np.float16).tobytes()

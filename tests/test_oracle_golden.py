@@ -52,3 +52,5 @@ def test_geglu_and_activations_match_reference_kernels(golden, oracle_mod):
     assert_bit_equal(oracle_mod.silu(x), golden["act.silu"], "silu")
     assert_bit_equal(oracle_mod.gelu(x), golden["act.gelu"], "gelu")
     assert_bit_equal(oracle_mod.elemwise_add(x, golden["act.other"]), golden["act.add"], "add")
+    assert_bit_equal(oracle_mod.chunkwise_add(golden["chunk.a"], golden["chunk.chunk"], 40),
+                     golden["chunk.y"], "chunkwise_add")
