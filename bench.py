@@ -457,7 +457,9 @@ def run_ours(args) -> None:
 # ---------------------------------------------------------------------------------------------
 def op_cases(torch, ops, dev):
     """Every kernel of the path at the workload's named shapes (BASELINE configs 1-5).
-    Each case: name, algorithmic bytes, a closure that enqueues one launch."""
+    Each case: name, algorithmic bytes, a factory and a spec for the CPU leg.  The factory
+    allocates one set of buffers and returns a closure that enqueues one launch on them, so
+    the caller can build a ring of buffer sets larger than L2."""
     gen = torch.Generator(device=dev).manual_seed(1234)
 
     def rnd(shape, dtype, scale=1.0):
@@ -467,11 +469,14 @@ def op_cases(torch, ops, dev):
     cases = []
 
     def gn(name, B, C, H, dtype, eps):
-        x = rnd((B, C, H, H), dtype)
-        y = torch.empty_like(x)
-        g, b = 1 + 0.1 * rnd((C,), f32), 0.1 * rnd((C,), f32)
-        nbytes = 2 * x.numel() * x.element_size() + 2 * C * 4
-        cases.append((name, nbytes, lambda: ops.groupnorm(x, g, b, 32, eps, True, out=y), ("gn", B, C, H, eps)))
+        esz = 2 if dtype == f16 else 4
+
+        def make():
+            x = rnd((B, C, H, H), dtype)
+            y = torch.empty_like(x)
+            g, b = 1 + 0.1 * rnd((C,), f32), 0.1 * rnd((C,), f32)
+            return lambda: ops.groupnorm(x, g, b, 32, eps, True, out=y)
+        cases.append((name, 2 * B * C * H * H * esz + 2 * C * 4, make, ("gn", B, C, H, eps)))
 
     gn("cfg1 GN+SiLU f32 [1,320,64,64]", 1, 320, 64, f32, 1e-5)
     for C, H in [(320, 64), (640, 32), (1280, 16), (1280, 8), (640, 64), (960, 64), (960, 32),
@@ -479,28 +484,34 @@ def op_cases(torch, ops, dev):
         gn(f"cfg3 GN+SiLU f16 [2,{C},{H},{H}]", 2, C, H, f16, 1e-5)
     for C, H in SHAPES:
         gn(f"cfg5 GN+SiLU f16 [8,{C},{H},{H}]", 8, C, H, f16, 1e-6)
-    gn("cfg5 GN+SiLU f16 [1,128,512,512] (8-GPU shard)", 1, 128, 512, f16, 1e-6)
+    for C, H in SHAPES:
+        gn(f"cfg5 GN+SiLU f16 [1,{C},{H},{H}] (8-GPU shard)", 1, C, H, f16, 1e-6)
     gn("profiling size GN+SiLU f16 [4,128,512,512]", 4, 128, 512, f16, 1e-6)
     gn("GN+SiLU f32 [8,256,256,256]", 8, 256, 256, f32, 1e-6)
 
     def gn_bias(name, B, C, H, dtype, eps):
-        x, e = rnd((B, C, H, H), dtype), rnd((B, C), dtype)
-        y = torch.empty_like(x)
-        g, b = 1 + 0.1 * rnd((C,), f32), 0.1 * rnd((C,), f32)
-        nbytes = 2 * x.numel() * x.element_size() + 2 * C * 4 + e.numel() * e.element_size()
-        cases.append((name, nbytes, lambda: ops.groupnorm_bias(x, e, g, b, 32, eps, True, out=y),
-                      ("gnbias", B, C, H, eps)))
+        esz = 2 if dtype == f16 else 4
+
+        def make():
+            x, e = rnd((B, C, H, H), dtype), rnd((B, C), dtype)
+            y = torch.empty_like(x)
+            g, b = 1 + 0.1 * rnd((C,), f32), 0.1 * rnd((C,), f32)
+            return lambda: ops.groupnorm_bias(x, e, g, b, 32, eps, True, out=y)
+        cases.append((name, 2 * B * C * H * H * esz + 2 * C * 4 + B * C * esz, make, ("gnbias", B, C, H, eps)))
 
     gn_bias("next: chunkwise_add+GN+SiLU f16 [2,320,64,64]", 2, 320, 64, f16, 1e-5)
     gn_bias("next: chunkwise_add+GN+SiLU f16 [2,1280,16,16]", 2, 1280, 16, f16, 1e-5)
     gn_bias("next: chunkwise_add+GN+SiLU f16 [8,256,256,256] (large)", 8, 256, 256, f16, 1e-5)
 
     def ln(name, rows, D, dtype):
-        x = rnd((rows, D), dtype)
-        y = torch.empty_like(x)
-        g, b = 1 + 0.1 * rnd((D,), f32), 0.1 * rnd((D,), f32)
-        nbytes = 2 * x.numel() * x.element_size() + 2 * D * 4
-        cases.append((name, nbytes, lambda: ops.layernorm(x, g, b, 1e-5, out=y), ("ln", rows, D)))
+        esz = 2 if dtype == f16 else 4
+
+        def make():
+            x = rnd((rows, D), dtype)
+            y = torch.empty_like(x)
+            g, b = 1 + 0.1 * rnd((D,), f32), 0.1 * rnd((D,), f32)
+            return lambda: ops.layernorm(x, g, b, 1e-5, out=y)
+        cases.append((name, 2 * rows * D * esz + 2 * D * 4, make, ("ln", rows, D)))
 
     ln("cfg2 LN f32 [2,77,768]", 154, 768, f32)
     ln("cfg2 LN f32 [1,77,1024] (reference width)", 77, 1024, f32)
@@ -509,30 +520,39 @@ def op_cases(torch, ops, dev):
     ln("LN f32 [16,4096,320] (large)", 65536, 320, f32)
 
     def add_ln(name, rows, D, dtype):
-        x, r = rnd((rows, D), dtype), rnd((rows, D), dtype)
-        ssum, y = torch.empty_like(x), torch.empty_like(x)
-        g, b = 1 + 0.1 * rnd((D,), f32), 0.1 * rnd((D,), f32)
-        nbytes = 4 * x.numel() * x.element_size() + 2 * D * 4
-        cases.append((name, nbytes, lambda: ops.add_layernorm(x, r, g, b, 1e-5, sum_out=ssum, out=y),
-                      ("addln", rows, D)))
+        esz = 2 if dtype == f16 else 4
+
+        def make():
+            x, r = rnd((rows, D), dtype), rnd((rows, D), dtype)
+            ssum, y = torch.empty_like(x), torch.empty_like(x)
+            g, b = 1 + 0.1 * rnd((D,), f32), 0.1 * rnd((D,), f32)
+            return lambda: ops.add_layernorm(x, r, g, b, 1e-5, sum_out=ssum, out=y)
+        cases.append((name, 4 * rows * D * esz + 2 * D * 4, make, ("addln", rows, D)))
 
     add_ln("next: add+LN f16 [2,4096,320]", 8192, 320, f16)
     add_ln("next: add+LN f16 [16,4096,1280] (large)", 65536, 1280, f16)
 
     def geglu(name, rows, D, dtype):
-        ab = rnd((rows, 2 * D), dtype)
-        y = torch.empty((rows, D), device=dev, dtype=dtype)
-        nbytes = 3 * rows * D * ab.element_size()
-        cases.append((name, nbytes, lambda: ops.gelu_multiply(ab, out=y), ("geglu", rows, D)))
+        esz = 2 if dtype == f16 else 4
+
+        def make():
+            ab = rnd((rows, 2 * D), dtype)
+            y = torch.empty((rows, D), device=dev, dtype=dtype)
+            return lambda: ops.gelu_multiply(ab, out=y)
+        cases.append((name, 3 * rows * D * esz, make, ("geglu", rows, D)))
 
     geglu("cfg4 GEGLU f16 [2,4096,2560]->[2,4096,1280]", 8192, 1280, f16)
     geglu("GEGLU f16 [16,4096,2560] (large)", 65536, 1280, f16)
     geglu("GEGLU f32 [8,4096,2560] (large)", 32768, 1280, f32)
 
     def act(name, fn, n, dtype):
-        x = rnd((n,), dtype)
-        y = torch.empty_like(x)
-        cases.append((name, 2 * n * x.element_size(), lambda: fn(x, out=y), ("act", fn.__name__, n)))
+        esz = 2 if dtype == f16 else 4
+
+        def make():
+            x = rnd((n,), dtype)
+            y = torch.empty_like(x)
+            return lambda: fn(x, out=y)
+        cases.append((name, 2 * n * esz, make, ("act", fn.__name__, n)))
 
     act("cfg2 quick_gelu f32 [2,77,3072]", ops.quick_gelu, 2 * 77 * 3072, f32)
     act("cfg2 gelu(erf) f32 [2,77,3072]", ops.gelu, 2 * 77 * 3072, f32)
@@ -541,23 +561,33 @@ def op_cases(torch, ops, dev):
     act("gelu(erf) f32 128M elements (large)", ops.gelu, 1 << 27, f32)
     act("quick_gelu f16 256M elements (large)", ops.quick_gelu, 1 << 28, f16)
 
-    for D in (768, 1024):
-        table = rnd((49408, D), f32, 0.02)
-        pos = rnd((77, D), f32, 0.02)
-        ids = torch.randint(0, 49408, (2, 77), device=dev, generator=gen, dtype=torch.int64)
-        out = torch.empty((2, 77, D), device=dev, dtype=f32)
+    tables = {}
+
+    def emb(D):
+        def make():
+            if D not in tables:            # the 152-202 MB table is shared by the ring's sets
+                tables[D] = (rnd((49408, D), f32, 0.02), rnd((77, D), f32, 0.02))
+            table, pos = tables[D]
+            ids = torch.randint(0, 49408, (2, 77), device=dev, generator=gen, dtype=torch.int64)
+            out = torch.empty((2, 77, D), device=dev, dtype=f32)
+            return lambda: ops.token_embedding(ids, table, pos, out=out)
         nbytes = 2 * 77 * 8 + 2 * (2 * 77 * D * 4) + 77 * D * 4
-        cases.append((f"cfg2 token+pos embedding f32 [2,77]->[2,77,{D}]", nbytes,
-                      lambda ids=ids, table=table, pos=pos, out=out: ops.token_embedding(ids, table, pos, out=out),
-                      ("emb", D)))
-    t = torch.randint(0, 1000, (2,), device=dev, generator=gen, dtype=torch.int64)
-    emb = torch.empty((2, 320), device=dev, dtype=f16)
-    cases.append(("cfg4 timestep embedding f16 [2]->[2,320]", 2 * 8 + 2 * 320 * 2,
-                  lambda: ops.timestep_embedding(t, 320, out=emb), ("ts",)))
-    a_, b_ = rnd((1 << 27,), f32), rnd((1 << 27,), f32)
-    c_ = torch.empty_like(a_)
-    cases.append(("elemwise_add f32 128M elements (large)", 3 * (1 << 27) * 4,
-                  lambda: ops.elemwise_add(a_, b_, out=c_), ("add", 1 << 27)))
+        cases.append((f"cfg2 token+pos embedding f32 [2,77]->[2,77,{D}]", nbytes, make, ("emb", D)))
+
+    emb(768)
+    emb(1024)
+
+    def ts_make():
+        t = torch.randint(0, 1000, (2,), device=dev, generator=gen, dtype=torch.int64)
+        out = torch.empty((2, 320), device=dev, dtype=f16)
+        return lambda: ops.timestep_embedding(t, 320, out=out)
+    cases.append(("cfg4 timestep embedding f16 [2]->[2,320]", 2 * 8 + 2 * 320 * 2, ts_make, ("ts",)))
+
+    def add_make():
+        a_, b_ = rnd((1 << 27,), f32), rnd((1 << 27,), f32)
+        c_ = torch.empty_like(a_)
+        return lambda: ops.elemwise_add(a_, b_, out=c_)
+    cases.append(("elemwise_add f32 128M elements (large)", 3 * (1 << 27) * 4, add_make, ("add", 1 << 27)))
     return cases
 
 
@@ -658,9 +688,14 @@ def run_ops(args) -> None:
     peak, peak_kind = measured_peak()
     flush = torch.empty(2 * L2_BYTES, dtype=torch.uint8, device=dev)
     reps = max(args.steps, 1) if args.case else 9
-    for name, nbytes, fn, spec in op_cases(torch, ops, dev):
+    stream = torch.cuda.Stream(device=dev)
+    for name, nbytes, make, spec in op_cases(torch, ops, dev):
         if args.case and args.case not in name:
             continue
+        ring_timing = not args.case or args.ring
+        nring = min(64, max(2, -(-4 * L2_BYTES // nbytes))) if ring_timing else 1
+        fns = [make() for _ in range(nring)]
+        fn = fns[0]
         for _ in range(max(args.warmup, 1)):
             fn()
         times = []
@@ -674,12 +709,47 @@ def run_ops(args) -> None:
             times.append(a.elapsed_time(b))
         t = statistics.median(times)
         gbs = nbytes / (t * 1e-3) / 1e9
-        line = {"case": name, "bytes": nbytes, "us": round(t * 1e3, 2), "gbs": round(gbs, 1),
-                "frac_of_peak": round(gbs / peak, 4), "peak": peak, "peak_source": f"of {peak_kind}",
-                "timing": "CUDA events around one launch, L2 flushed before it, median"}
+        line = {"case": name, "bytes": nbytes, "single_launch_us": round(t * 1e3, 2),
+                "single_launch_gbs": round(gbs, 1),
+                "single_launch_timing": "CUDA events around one launch, L2 flushed before it, median "
+                                        "(an empty launch costs about 6 us this way)",
+                "peak": peak, "peak_source": f"of {peak_kind}"}
+        if ring_timing:
+            # K launches back to back as one CUDA graph, cycling through the ring of buffer sets
+            # (a set comes back after >= 4 x L2 of other traffic unless the case is tiny)
+            K = max(nring, 32)
+            with torch.cuda.stream(stream):
+                for f in fns:
+                    f()
+                stream.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=stream):
+                    for i in range(K):
+                        fns[i % nring]()
+                g.replay()
+                stream.synchronize()
+                rt = []
+                for _ in range(21):
+                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    a.record(stream)
+                    g.replay()
+                    b.record(stream)
+                    stream.synchronize()
+                    rt.append(a.elapsed_time(b) / K)
+                del g
+            tr = statistics.median(rt)
+            line.update({"us": round(tr * 1e3, 2), "gbs": round(nbytes / (tr * 1e-3) / 1e9, 1),
+                         "frac_of_peak": round(nbytes / (tr * 1e-3) / 1e9 / peak, 4),
+                         "timing": f"CUDA graph of {K} back-to-back launches over a ring of {nring} buffer "
+                                   f"sets ({nring * nbytes / 1e6:.0f} MB), median of 21 replays, per launch"})
+        else:
+            line.update({"us": line["single_launch_us"], "gbs": line["single_launch_gbs"],
+                         "frac_of_peak": round(gbs / peak, 4), "timing": line["single_launch_timing"]})
         if args.cpu:
             line.update(cpu_reference_case(spec))
         print(json.dumps(line), flush=True)
+        del fns, fn
+        torch.cuda.empty_cache()
     assert ops.device_status() == 0
 
 
@@ -693,6 +763,7 @@ def main() -> None:
     ap.add_argument("--ops", action="store_true", help="per-kernel table over all named shapes")
     ap.add_argument("--case", default="", help="with --ops: only cases whose name contains this")
     ap.add_argument("--cpu", action="store_true", help="with --ops: also time the reference on the host cores")
+    ap.add_argument("--ring", action="store_true", help="with --case: also run the back-to-back graph timing")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

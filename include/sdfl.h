@@ -44,7 +44,7 @@ enum {
 };
 
 /* GroupNorm path selection for sdfl_groupnorm_forward_ex (tests and sweeps). */
-enum { SDFL_GN_AUTO = 0, SDFL_GN_RESIDENT = 1, SDFL_GN_SPLIT = 2 };
+enum { SDFL_GN_AUTO = 0, SDFL_GN_RESIDENT = 1, SDFL_GN_SPLIT = 2, SDFL_GN_REGISTER = 3 };
 
 const char *sdfl_version(void);
 const char *sdfl_status_string(int status);
@@ -129,6 +129,13 @@ int sdfl_groupnorm_bias_forward(const void *in, const void *channel_bias, void *
                                 const float *beta, int64_t batch, int64_t channels, int64_t hw,
                                 int64_t num_groups, float eps, int fuse_silu, int dtype, void *workspace,
                                 size_t workspace_bytes, void *stream);
+
+/* The same with the path and tuning knob of sdfl_groupnorm_forward_ex (tests and sweeps). */
+int sdfl_groupnorm_bias_forward_ex(const void *in, const void *channel_bias, void *out,
+                                   const float *gamma, const float *beta, int64_t batch,
+                                   int64_t channels, int64_t hw, int64_t num_groups, float eps,
+                                   int fuse_silu, int dtype, void *workspace, size_t workspace_bytes,
+                                   int path, int cluster_or_splits, void *stream);
 
 /* K/util.cl:136-148  chunkwise_add(A, chunk, C, chunk_size) over n work-items:
  * C[i] = A[i] + chunk[i / chunk_size]; C may be A (NN/ResBlock.cpp:188-191). */

@@ -12,7 +12,7 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(PKG, "lib", "libsdfl.so")
 
 F32, F16 = 0, 1
-GN_AUTO, GN_RESIDENT, GN_SPLIT = 0, 1, 2
+GN_AUTO, GN_RESIDENT, GN_SPLIT, GN_REGISTER = 0, 1, 2, 3
 
 OK = 0
 ERR_INVALID_VALUE = -1
@@ -50,6 +50,7 @@ SIGNATURES = {
     "sdfl_groupnorm_workspace_bytes_ex": (_sz, [_i64, _i64, _i64, _i64, _i, _i, _i]),
     "sdfl_groupnorm_forward_noalloc": (_i, [_p, _p, _p, _p, _i64, _i64, _i64, _i64, _f, _i, _i, _p]),
     "sdfl_groupnorm_bias_forward": (_i, [_p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _f, _i, _i, _p, _sz, _p]),
+    "sdfl_groupnorm_bias_forward_ex": (_i, [_p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _f, _i, _i, _p, _sz, _i, _i, _p]),
     "sdfl_chunkwise_add": (_i, [_p, _p, _p, _i64, _i64, _i, _p]),
     "sdfl_groupnorm_plan": (_i, [_i64, _i64, _i64, _i64, _i, _i, _i, C.POINTER(_i64)]),
     "sdfl_layernorm_forward": (_i, [_p, _p, _p, _p, _i64, _i64, _f, _i, _p]),

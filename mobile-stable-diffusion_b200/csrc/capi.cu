@@ -63,7 +63,7 @@ int gn_forward(const void *in, void *out, const float *gamma, const float *beta,
     int rc = gn_validate(in, out, gamma, beta, batch, channels, hw, groups, eps, dtype);
     if (rc != SDFL_OK) return rc;
     if (batch == 0 || hw == 0) return SDFL_OK;
-    if (path < SDFL_GN_AUTO || path > SDFL_GN_SPLIT || cluster < 0) return SDFL_ERR_INVALID_VALUE;
+    if (path < SDFL_GN_AUTO || path > SDFL_GN_REGISTER || cluster < 0) return SDFL_ERR_INVALID_VALUE;
     sdfl::GnShape s{batch, channels, hw, groups, dtype, eps,
                     fuse_silu ? sdfl::kActSilu : sdfl::kActNone};
     sdfl::GnPlan plan;
@@ -165,6 +165,16 @@ int sdfl_groupnorm_bias_forward(const void *in, const void *channel_bias, void *
                       workspace, workspace_bytes, SDFL_GN_AUTO, 0, as_stream(stream), channel_bias);
 }
 
+int sdfl_groupnorm_bias_forward_ex(const void *in, const void *channel_bias, void *out,
+                                   const float *gamma, const float *beta, int64_t batch,
+                                   int64_t channels, int64_t hw, int64_t num_groups, float eps,
+                                   int fuse_silu, int dtype, void *workspace, size_t workspace_bytes,
+                                   int path, int cluster_or_splits, void *stream) {
+    if (!channel_bias && batch > 0 && hw > 0) return SDFL_ERR_INVALID_POINTER;
+    return gn_forward(in, out, gamma, beta, batch, channels, hw, num_groups, eps, fuse_silu, dtype,
+                      workspace, workspace_bytes, path, cluster_or_splits, as_stream(stream), channel_bias);
+}
+
 int sdfl_chunkwise_add(const void *A, const void *chunk, void *C, int64_t n, int64_t chunk_size,
                        int dtype, void *stream) {
     if (!dtype_ok(dtype) || n < 0 || chunk_size <= 0) return SDFL_ERR_INVALID_VALUE;
@@ -179,7 +189,7 @@ int sdfl_groupnorm_plan(int64_t batch, int64_t channels, int64_t hw, int64_t num
     if (!plan) return SDFL_ERR_INVALID_POINTER;
     for (int i = 0; i < 8; ++i) plan[i] = 0;
     if (!dtype_ok(dtype) || batch < 0 || channels <= 0 || hw < 0 || num_groups <= 0 ||
-        channels % num_groups != 0 || path < SDFL_GN_AUTO || path > SDFL_GN_SPLIT ||
+        channels % num_groups != 0 || path < SDFL_GN_AUTO || path > SDFL_GN_REGISTER ||
         cluster_or_splits < 0)
         return SDFL_ERR_INVALID_VALUE;
     if (hw >= (1ll << 31) || (channels / num_groups) * hw >= (1ll << 31) ||

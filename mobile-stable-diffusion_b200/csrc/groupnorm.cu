@@ -370,8 +370,13 @@ struct ResidentArgs {
 //             with the next slab's chunks meanwhile.
 //   otherwise the chunks are released after the moments pass and loaded a second time for the
 //             normalise pass (this second read is served by L2 when the clusters' slabs fit it).
-template <typename T, int ACT, bool BIAS>
-__global__ void __launch_bounds__(512, 2)
+//
+// NV > 0: the launch has exactly 256 consumer threads and chunks of 256 * NV vectors, so a full
+// chunk that lies inside one channel is NV vectors per thread at compile-time offsets: the
+// loads are issued together and the loop, index and channel arithmetic disappear (they were
+// about 40 % of the instructions issued, and the consumer warps are issue-bound).
+template <typename T, int ACT, bool BIAS, int NV>
+__global__ void __launch_bounds__(NV == 4 ? 288 : 512, NV == 4 ? 4 : 2)
 gn_resident_kernel(const ResidentArgs a) {
     constexpr int VEC = VecOf<T>::N;
     constexpr bool HALF = sizeof(T) == 2;
@@ -499,7 +504,32 @@ gn_resident_kernel(const ResidentArgs a) {
             const uint4 *sv = reinterpret_cast<const uint4 *>(data + slot * chunk_bytes);
             if (j == 0) shift = to_float<T>(reinterpret_cast<const T *>(sv)[0]);
             const uint32_t cnt = min(cv, nv - j * cv);
-            if (!BIAS) {
+            bool fast = false;
+            if (NV > 0 && cnt == 256u * NV && consumers == 256u) {
+                uint32_t c = 0;
+                if (BIAS) {
+                    c = a.hwv_div.div(v0 + j * cv);
+                    fast = a.vec_uniform && c == a.hwv_div.div(v0 + j * cv + cnt - 1u);
+                } else {
+                    fast = true;
+                }
+                if (fast) {
+                    float sh = shift;
+                    if (BIAS) {
+                        const float e = to_float<T>(erow[c]);
+                        if (j == 0) shift += e;
+                        sh = shift - e;
+                    }
+                    uint4 v[NV > 0 ? NV : 1];
+#pragma unroll
+                    for (int k = 0; k < NV; ++k) v[k] = sv[tid + k * 256];
+#pragma unroll
+                    for (int k = 0; k < NV; ++k) stats_vec<T>(v[k], sh, s, q);
+                    nvec_mine += NV;
+                }
+            }
+            if (fast) {
+            } else if (!BIAS) {
 #pragma unroll 2
                 for (uint32_t i = tid; i < cnt; i += consumers) {
                     stats_vec<T>(sv[i], shift, s, q);
@@ -608,7 +638,24 @@ gn_resident_kernel(const ResidentArgs a) {
             const uint4 *sv = reinterpret_cast<const uint4 *>(data + slot * chunk_bytes);
             const uint32_t lo = j * cv;                 // part-relative vector index of the chunk
             const uint32_t hi = min(nv, lo + cv);
-            if (a.vec_uniform && hwv >= consumers) {
+            bool fast = false;
+            if (NV > 0 && hi - lo == 256u * NV && consumers == 256u && a.vec_uniform) {
+                const uint32_t c = a.hwv_div.div(v0 + lo);
+                if (c == a.hwv_div.div(v0 + hi - 1u)) {
+                    fast = true;
+                    const float mc = BIAS ? mean - to_float<T>(erow[c]) : mean;
+                    const Affine<T> af = make_affine<T, ACT>(mc, rstd, __ldg(a.w + ch0 + c),
+                                                            __ldg(a.b + ch0 + c));
+                    uint4 v[NV > 0 ? NV : 1];
+#pragma unroll
+                    for (int k = 0; k < NV; ++k) v[k] = sv[tid + k * 256];
+#pragma unroll
+                    for (int k = 0; k < NV; ++k)
+                        st_stream(&gv[lo + tid + k * 256], norm_vec<T, ACT>(v[k], af));
+                }
+            }
+            if (fast) {
+            } else if (a.vec_uniform && hwv >= consumers) {
                 // long channels: walk channel by channel, weights hoisted out of the vector loop
                 uint32_t i0 = lo;
                 while (i0 < hi) {
@@ -652,6 +699,123 @@ gn_resident_kernel(const ResidentArgs a) {
     if (timed_out && lane == 0) atomicOr(&g_gn_status, 1u);
     // No barrier at exit: nobody reads a peer's shared memory; a CTA's own slots are written
     // only by peers whose arrivals it has already waited for.
+}
+
+// ---------------------------------------------------------------------------------------------
+// Register path: one CTA per slab, the whole slab in the CTA's registers
+// ---------------------------------------------------------------------------------------------
+// For the slabs of the UNet (5-240 KB) the cluster kernel's fixed costs (cluster start-up, barrier
+// set-up, the exchange) are most of its time.  Here a CTA of 512 threads loads its slab with up to
+// NVT 16-byte vectors per thread, all loads in flight at once, folds the moments through one
+// __syncthreads and normalises from registers: one HBM read, one write, no shared-memory staging.
+// Every load of a slab precedes every store to it, so out == in is safe.
+constexpr int kRegThreads = 512;
+constexpr int kRegMaxVecs = 24;      // per thread: slabs up to 512 * 24 * 16 B = 192 KB
+
+struct RegArgs {
+    const void *in;
+    void *out;
+    const float *w;
+    const float *b;
+    const void *bias;      // [batch, C] addend of the storage type, or nullptr
+    uint32_t units, slab_vecs, slab_elems, cpg, groups, channels;
+    uint32_t vec_uniform;  // hw % lanes-per-vector == 0
+    float eps;
+    FastDiv hw_div;        // element offset in the slab -> channel of the group
+    FastDiv hwv_div;       // vector offset -> channel (when vec_uniform)
+};
+
+template <typename T, int ACT, bool BIAS, int NVT>
+__global__ void __launch_bounds__(kRegThreads, NVT <= 4 ? 2 : 1)
+gn_register_kernel(const RegArgs a) {
+    constexpr int VEC = VecOf<T>::N;
+    constexpr bool HALF = sizeof(T) == 2;
+    __shared__ Moments warp_m[kRegThreads / 32];
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    for (uint32_t unit = blockIdx.x; unit < a.units; unit += gridDim.x) {
+        const uint4 *src = reinterpret_cast<const uint4 *>(a.in) + static_cast<size_t>(unit) * a.slab_vecs;
+        uint4 *dst = reinterpret_cast<uint4 *>(a.out) + static_cast<size_t>(unit) * a.slab_vecs;
+        const T *erow = BIAS ? static_cast<const T *>(a.bias) +
+                                   static_cast<size_t>(unit / a.groups) * a.channels + (unit % a.groups) * a.cpg
+                             : nullptr;
+        uint4 v[NVT];
+#pragma unroll
+        for (int k = 0; k < NVT; ++k) {
+            const uint32_t idx = tid + k * kRegThreads;
+            if (idx < a.slab_vecs) v[k] = ld_stream(src + idx);
+        }
+        // this thread's moments, shifted by its first value
+        float s[2] = {0.f, 0.f}, q[2] = {0.f, 0.f};
+        float shift = 0.f;
+        uint32_t mine = 0;
+        if (tid < a.slab_vecs) {
+            shift = HALF ? __half2float(__ushort_as_half(static_cast<unsigned short>(v[0].x & 0xffffu)))
+                         : __uint_as_float(v[0].x);
+            if (BIAS) shift += to_float<T>(erow[a.hw_div.div(tid * VEC)]);
+        }
+#pragma unroll
+        for (int k = 0; k < NVT; ++k) {
+            const uint32_t idx = tid + k * kRegThreads;
+            if (idx < a.slab_vecs) {
+                if (!BIAS) {
+                    stats_vec<T>(v[k], shift, s, q);
+                } else if (a.vec_uniform) {
+                    stats_vec<T>(v[k], shift - to_float<T>(erow[a.hwv_div.div(idx)]), s, q);
+                } else {
+                    float f[VEC];
+                    unpack<T>(v[k], f);
+#pragma unroll
+                    for (int l = 0; l < VEC; ++l) {
+                        const float d = f[l] + to_float<T>(erow[a.hw_div.div(idx * VEC + l)]) - shift;
+                        s[l & 1] += d;
+                        q[l & 1] = fmaf(d, d, q[l & 1]);
+                    }
+                }
+                ++mine;
+            }
+        }
+        Moments m;
+        {
+            const float cnt = static_cast<float>(mine * VEC);
+            const float ss = s[0] + s[1], qq = q[0] + q[1];
+            m.n = cnt;
+            m.mean = mine ? shift + ss / cnt : 0.f;
+            m.m2 = mine ? fmaxf(qq - ss * ss / cnt, 0.f) : 0.f;
+        }
+        m = warp_merge(m);
+        if (lane == 0) warp_m[warp] = m;
+        __syncthreads();
+        // every warp folds the 16 per-warp moments itself, in the same order
+        Moments t = lane < kRegThreads / 32 ? warp_m[lane] : Moments{0.f, 0.f, 0.f};
+        t = warp_merge(t);
+        const float mean = __shfl_sync(0xffffffffu, t.mean, 0);
+        const float var = __shfl_sync(0xffffffffu, t.m2, 0) / static_cast<float>(a.slab_elems);   // biased
+        const float rstd = 1.0f / sqrtf(var + a.eps);
+        const uint32_t ch0 = (unit % a.groups) * a.cpg;
+#pragma unroll
+        for (int k = 0; k < NVT; ++k) {
+            const uint32_t idx = tid + k * kRegThreads;
+            if (idx < a.slab_vecs) {
+                if (a.vec_uniform) {
+                    const uint32_t cl = a.hwv_div.div(idx), c = ch0 + cl;
+                    const float mc = BIAS ? mean - to_float<T>(erow[cl]) : mean;
+                    const Affine<T> af = make_affine<T, ACT>(mc, rstd, __ldg(a.w + c), __ldg(a.b + c));
+                    st_stream(dst + idx, norm_vec<T, ACT>(v[k], af));
+                } else {
+                    float f[VEC];
+                    unpack<T>(v[k], f);
+#pragma unroll
+                    for (int l = 0; l < VEC; ++l) {
+                        const uint32_t cl = a.hw_div.div(idx * VEC + l), c = ch0 + cl;
+                        const float mc = BIAS ? mean - to_float<T>(erow[cl]) : mean;
+                        f[l] = activate<ACT, HALF>(fmaf((f[l] - mc) * rstd, __ldg(a.w + c), __ldg(a.b + c)));
+                    }
+                    st_stream(dst + idx, pack<T>(f));
+                }
+            }
+        }
+        __syncthreads();       // warp_m is reused by the next slab
+    }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -857,14 +1021,14 @@ inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 
 // the opt-in for 16-CTA clusters), so that launches themselves make no attribute calls.
 constexpr int kMaxDevices = 64;
 
-template <typename T, int ACT, bool BIAS>
+template <typename T, int ACT, bool BIAS, int NV>
 cudaError_t ensure_resident_attrs() {
     static std::atomic<bool> done[kMaxDevices];
     int dev = 0;
     cudaError_t err = cudaGetDevice(&dev);
     if (err != cudaSuccess) return err;
     if (dev >= 0 && dev < kMaxDevices && done[dev].load(std::memory_order_acquire)) return cudaSuccess;
-    auto kernel = gn_resident_kernel<T, ACT, BIAS>;
+    auto kernel = gn_resident_kernel<T, ACT, BIAS, NV>;
     err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                static_cast<int>(kHeaderBytes + kMaxPartBytes));
     if (err != cudaSuccess) return err;
@@ -889,17 +1053,32 @@ inline void cluster_config(cudaLaunchConfig_t *cfg, cudaLaunchAttribute *attr, u
     cfg->numAttrs = 1;
 }
 
-template <typename T, int ACT, bool BIAS>
-cudaError_t launch_resident_as(const ResidentArgs &a, const GnPlan &plan, cudaStream_t stream) {
-    cudaError_t err = ensure_resident_attrs<T, ACT, BIAS>();
+template <typename T, int ACT, bool BIAS, int NV>
+cudaError_t launch_resident_nv(const ResidentArgs &a, const GnPlan &plan, cudaStream_t stream) {
+    cudaError_t err = ensure_resident_attrs<T, ACT, BIAS, NV>();
     if (err != cudaSuccess) return err;
     cudaLaunchConfig_t cfg;
     cudaLaunchAttribute attr[1];
     cluster_config(&cfg, attr, static_cast<unsigned>(plan.nclusters * plan.cluster), plan.cluster,
                    plan.threads, plan.smem, stream);
-    err = cudaLaunchKernelEx(&cfg, gn_resident_kernel<T, ACT, BIAS>, a);
+    err = cudaLaunchKernelEx(&cfg, gn_resident_kernel<T, ACT, BIAS, NV>, a);
     if (err == cudaSuccess) g_launches.fetch_add(1);
     return err;
+}
+
+// The unrolled variants need 256 consumer threads and chunks of 256 * NV vectors.
+inline int plan_unroll(int threads, int chunk_vecs) {
+    if (threads != 288) return 0;
+    return chunk_vecs == 2048 ? 8 : chunk_vecs == 1024 ? 4 : 0;
+}
+
+template <typename T, int ACT, bool BIAS>
+cudaError_t launch_resident_as(const ResidentArgs &a, const GnPlan &plan, cudaStream_t stream) {
+    switch (plan_unroll(plan.threads, plan.chunk_vecs)) {
+        case 8: return launch_resident_nv<T, ACT, BIAS, 8>(a, plan, stream);
+        case 4: return launch_resident_nv<T, ACT, BIAS, 4>(a, plan, stream);
+        default: return launch_resident_nv<T, ACT, BIAS, 0>(a, plan, stream);
+    }
 }
 
 template <typename T, int ACT>
@@ -908,11 +1087,38 @@ cudaError_t launch_resident(const ResidentArgs &a, const GnPlan &plan, cudaStrea
                   : launch_resident_as<T, ACT, false>(a, plan, stream);
 }
 
+template <typename T, int ACT, bool BIAS>
+cudaError_t launch_register_as(const RegArgs &a, cudaStream_t stream) {
+    const uint32_t per_thread = (a.slab_vecs + kRegThreads - 1) / kRegThreads;
+    const unsigned grid = a.units < 148u * 64u ? a.units : 148u * 64u;
+    if (per_thread <= 4)
+        gn_register_kernel<T, ACT, BIAS, 4><<<grid, kRegThreads, 0, stream>>>(a);
+    else if (per_thread <= 12)
+        gn_register_kernel<T, ACT, BIAS, 12><<<grid, kRegThreads, 0, stream>>>(a);
+    else
+        gn_register_kernel<T, ACT, BIAS, kRegMaxVecs><<<grid, kRegThreads, 0, stream>>>(a);
+    cudaError_t err = cudaGetLastError();
+    if (err == cudaSuccess) g_launches.fetch_add(1);
+    return err;
+}
+
+template <typename T, int ACT>
+cudaError_t launch_register(const RegArgs &a, cudaStream_t stream) {
+    return a.bias ? launch_register_as<T, ACT, true>(a, stream) : launch_register_as<T, ACT, false>(a, stream);
+}
+
 // How many clusters of this size, block size and shared-memory footprint can be resident at
 // once (a cluster must fit inside one GPC).  Asked of the driver once per (device, dtype,
 // cluster, threads, shared-memory size in KiB) and remembered.
+template <typename T, int NV>
+cudaError_t active_clusters_nv(cudaLaunchConfig_t *cfg, int *n) {
+    cudaError_t err = ensure_resident_attrs<T, kActSilu, false, NV>();
+    if (err != cudaSuccess) return err;
+    return cudaOccupancyMaxActiveClusters(n, gn_resident_kernel<T, kActSilu, false, NV>, cfg);
+}
+
 template <typename T>
-cudaError_t resident_active_clusters(int cluster, int threads, size_t smem, int *active) {
+cudaError_t resident_active_clusters(int cluster, int threads, size_t smem, int chunk_vecs, int *active) {
     static std::mutex mu;
     static std::map<uint64_t, int> cache;
     int dev = 0;
@@ -921,19 +1127,22 @@ cudaError_t resident_active_clusters(int cluster, int threads, size_t smem, int 
     const uint64_t kb = (smem + 1023) / 1024;
     const uint64_t key = (static_cast<uint64_t>(dev) << 48) | (static_cast<uint64_t>(sizeof(T)) << 40) |
                          (static_cast<uint64_t>(cluster) << 32) |
-                         (static_cast<uint64_t>(threads) << 16) | kb;
+                         (static_cast<uint64_t>(threads) << 16) | kb |
+                         (static_cast<uint64_t>(plan_unroll(threads, chunk_vecs)) << 56);
     {
         std::lock_guard<std::mutex> lock(mu);
         auto it = cache.find(key);
         if (it != cache.end()) { *active = it->second; return cudaSuccess; }
     }
-    err = ensure_resident_attrs<T, kActSilu, false>();
-    if (err != cudaSuccess) return err;
     cudaLaunchConfig_t cfg;
     cudaLaunchAttribute attr[1];
     cluster_config(&cfg, attr, static_cast<unsigned>(cluster), cluster, threads, smem, nullptr);
     int n = 0;
-    err = cudaOccupancyMaxActiveClusters(&n, gn_resident_kernel<T, kActSilu, false>, &cfg);
+    switch (plan_unroll(threads, chunk_vecs)) {
+        case 8: err = active_clusters_nv<T, 8>(&cfg, &n); break;
+        case 4: err = active_clusters_nv<T, 4>(&cfg, &n); break;
+        default: err = active_clusters_nv<T, 0>(&cfg, &n); break;
+    }
     if (err != cudaSuccess) return err;
     *active = n;
     std::lock_guard<std::mutex> lock(mu);
@@ -942,6 +1151,14 @@ cudaError_t resident_active_clusters(int cluster, int threads, size_t smem, int 
 }
 
 constexpr int kSmCount = 148;
+
+// When the register path beats the cluster path (launches timed back to back on B200, fp16 and
+// fp32, 32-256 slabs of 5-240 KB): always for slabs up to 48 KB (3.5-6 us against 5.5-7); for
+// larger ones once there are at least 64 slabs, i.e. enough CTAs to pull on HBM from many SMs
+// (with 32 slabs of 60-160 KB a cluster of 8 per slab is 0.3-1 us faster).
+inline bool prefer_register(int64_t slab_bytes, int64_t units) {
+    return slab_bytes <= 48 * 1024 || units >= 64;
+}
 
 }  // namespace
 
@@ -962,20 +1179,34 @@ cudaError_t gn_make_plan(const GnShape &s, const void *in, const void *out, int 
                        units < (1ll << 27);
     if (force_path == kGnSplit) resident_ok = false;
 
+    // One CTA per slab with the slab in registers: no start-up or exchange latency.
+    const bool register_ok = resident_ok && slab_bytes <= static_cast<int64_t>(kRegThreads) * kRegMaxVecs * 16;
+    if (force_path == kGnRegister && !register_ok) return cudaErrorInvalidConfiguration;
+    if (register_ok && (force_path == kGnRegister || (force_path == kGnAuto && prefer_register(slab_bytes, units)))) {
+        plan->path = kGnRegister;
+        plan->cluster = 1;
+        plan->threads = kRegThreads;
+        plan->nclusters = static_cast<int>(units < 148 * 64 ? units : 148 * 64);
+        plan->chunk_vecs = static_cast<int>((slab_bytes / 16 + kRegThreads - 1) / kRegThreads);
+        return cudaSuccess;
+    }
+
     if (resident_ok) {
         // Ring geometry and cluster size, from sweeps on B200 (fp16 and fp32 behave alike per
-        // byte).  A small ring (3 slots of 16-32 KB, 7-11 consumer warps) with the second read
+        // byte).  A small ring (3 slots of 16-32 KB, 8 consumer warps) with the second read
         // served by L2 beats full shared-memory residency at every size tried: it keeps 2-4 CTAs
         // on each SM, so one CTA's cluster exchange hides behind the others' traffic.  The
-        // cluster grows with the slab so that the slabs in flight (clusters x slab bytes) stay
-        // well inside L2, and with few slabs so that every SM still gets a CTA.
+        // cluster grows with the slab so that a CTA's share is about 256 KB: the slabs in flight
+        // (256 CTAs x share = 64 MB) stay well inside L2; with few slabs it grows further so that
+        // every SM still gets a CTA.
         const int64_t slab_vecs = slab_bytes / 16;
         const int k_cluster = force_cluster & 0xff, k_slots = (force_cluster >> 8) & 0xff;
         const int k_chunk_kb = (force_cluster >> 16) & 0xff, k_cwarps = (force_cluster >> 24) & 0xf;
-        int c = slab_bytes <= 192 * 1024 ? 2 : slab_bytes <= 768 * 1024 ? 4 : 8;
-        const int64_t want_ctas = 2 * kSmCount;
-        // (not beyond 8: only about half as many 16-CTA clusters can be co-resident)
-        while (c < 8 && units * c < want_ctas && slab_bytes / (2 * c) >= 8 * 1024) c *= 2;
+        int c = slab_bytes <= 640 * 1024 ? 2 : slab_bytes <= 1280 * 1024 ? 4 : 8;
+        // Few slabs: grow the cluster while the grid stays within 256 CTAs (more CTAs than that
+        // only add start-up cost); not beyond 8, only about half as many 16-CTA clusters can
+        // be co-resident.
+        while (c < 8 && units * c * 2 <= 256 && slab_bytes / (2 * c) >= 8 * 1024) c *= 2;
         while (c > 1 && slab_bytes / c < 8 * 1024) c /= 2;
         if (k_cluster > 0) c = k_cluster;
         if (c > 16) c = 16;
@@ -1000,14 +1231,15 @@ cudaError_t gn_make_plan(const GnShape &s, const void *in, const void *out, int 
             }
             if (nslots < chunks && nslots < 2) { if (k_cluster > 0) break; continue; }
             const size_t smem = kHeaderBytes + static_cast<size_t>(nslots * chunk_bytes);
-            int consumers = k_cwarps > 0 ? k_cwarps * 32
-                                         : (large ? 352 : part_bytes >= 8 * 1024 ? 224 : 96);
+            // 256 consumer threads: full chunks are then 4 or 8 vectors per thread (the
+            // unrolled kernel variants)
+            int consumers = k_cwarps > 0 ? k_cwarps * 32 : part_bytes >= 8 * 1024 ? 256 : 96;
             if (consumers > 480) consumers = 480;
             const int threads = consumers + 32;
             int active = 0;
             cudaError_t err = s.dtype == kF16
-                                  ? resident_active_clusters<__half>(c, threads, smem, &active)
-                                  : resident_active_clusters<float>(c, threads, smem, &active);
+                                  ? resident_active_clusters<__half>(c, threads, smem, static_cast<int>(chunk_vecs), &active)
+                                  : resident_active_clusters<float>(c, threads, smem, static_cast<int>(chunk_vecs), &active);
             if (err != cudaSuccess) { (void)cudaGetLastError(); active = 0; }
             if (active <= 0) { if (k_cluster > 0) break; continue; }
             const int64_t waves = (units + active - 1) / active;
@@ -1056,6 +1288,26 @@ cudaError_t gn_launch(const GnShape &s, const GnPlan &plan, const void *in, void
     const int64_t slab_elems = cpg * s.hw;
     const int64_t units = s.batch * s.groups;
     if (units == 0 || slab_elems == 0) return cudaSuccess;
+
+    if (plan.path == kGnRegister) {
+        RegArgs a;
+        a.in = in; a.out = out; a.w = w; a.b = b; a.bias = bias;
+        a.units = static_cast<uint32_t>(units);
+        a.slab_vecs = static_cast<uint32_t>(slab_elems * esz / 16);
+        a.slab_elems = static_cast<uint32_t>(slab_elems);
+        a.cpg = static_cast<uint32_t>(cpg);
+        a.groups = static_cast<uint32_t>(s.groups);
+        a.channels = static_cast<uint32_t>(s.channels);
+        a.vec_uniform = s.hw % vec == 0;
+        a.eps = s.eps;
+        a.hw_div = FastDiv::make(static_cast<uint32_t>(s.hw));
+        a.hwv_div = FastDiv::make(a.vec_uniform ? static_cast<uint32_t>(s.hw / vec) : 1u);
+        if (s.dtype == kF16)
+            return s.act == kActSilu ? launch_register<__half, kActSilu>(a, stream)
+                                     : launch_register<__half, kActNone>(a, stream);
+        return s.act == kActSilu ? launch_register<float, kActSilu>(a, stream)
+                                 : launch_register<float, kActNone>(a, stream);
+    }
 
     if (plan.path == kGnResident) {
         ResidentArgs a;

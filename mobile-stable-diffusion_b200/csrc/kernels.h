@@ -19,10 +19,11 @@ extern std::atomic<long long> g_launches;
 //                and activation cost one HBM read and one HBM write.
 //   kGnSplit     two kernels with a caller-provided scratch of per-chunk (mean, M2) partials;
 //                any size, any alignment; one extra read of the tensor (mostly L2 for mid sizes).
-enum GnPath : int { kGnAuto = 0, kGnResident = 1, kGnSplit = 2 };
+//   kGnRegister  one CTA per slab, the slab in its registers (slabs up to 192 KB): lowest latency.
+enum GnPath : int { kGnAuto = 0, kGnResident = 1, kGnSplit = 2, kGnRegister = 3 };
 
 struct GnPlan {
-    int path;          // kGnResident or kGnSplit
+    int path;          // kGnResident, kGnSplit or kGnRegister
     int cluster;       // CTAs per slab (resident): 1..16
     int threads;       // threads per CTA (resident: consumer warps + one producer warp)
     int nclusters;     // persistent clusters launched (resident)

@@ -11,14 +11,14 @@ import ctypes as C
 import torch
 
 from . import _capi
-from ._capi import F16, F32, GN_AUTO, GN_RESIDENT, GN_SPLIT, SdflError, check, lib
+from ._capi import F16, F32, GN_AUTO, GN_REGISTER, GN_RESIDENT, GN_SPLIT, SdflError, check, lib
 
 __all__ = [
     "groupnorm", "groupnorm_bias", "chunkwise_add", "groupnorm_noalloc", "groupnorm_plan", "layernorm", "add_layernorm", "gelu_multiply", "silu", "gelu", "quick_gelu",
     "elemwise_add", "token_embedding", "timestep_embedding", "local_reduction_mean",
     "local_reduction_variance", "group_norm_apply", "layer_norm_apply", "device_status",
     "selftest_bounded_wait",
-    "launch_count", "HostPipeline", "GN_AUTO", "GN_RESIDENT", "GN_SPLIT",
+    "launch_count", "HostPipeline", "GN_AUTO", "GN_RESIDENT", "GN_SPLIT", "GN_REGISTER",
 ]
 
 
@@ -113,7 +113,8 @@ def groupnorm(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor, num_grou
 
 def groupnorm_bias(x: torch.Tensor, channel_bias: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor,
                    num_groups: int, eps: float = 1e-5, silu: bool = False,
-                   out: torch.Tensor | None = None, stream=None) -> torch.Tensor:
+                   out: torch.Tensor | None = None, stream=None, path: int = GN_AUTO,
+                   cluster_or_splits: int = 0) -> torch.Tensor:
     """act(GroupNorm(x + channel_bias[:, :, None, None])); channel_bias is [B, C] of x's dtype."""
     _dev(x, "x")
     out = torch.empty_like(x) if out is None else out
@@ -122,12 +123,13 @@ def groupnorm_bias(x: torch.Tensor, channel_bias: torch.Tensor, gamma: torch.Ten
         raise ValueError("channel_bias must be [batch, channels] of x's dtype")
     hw = x.numel() // (B * Cc) if B * Cc else 0
     code = _dtype_code(x)
-    ws = _workspace(x.device, lib.sdfl_groupnorm_workspace_bytes(B, Cc, hw, num_groups, code))
+    ws = _workspace(x.device, lib.sdfl_groupnorm_workspace_bytes_ex(B, Cc, hw, num_groups, code, path,
+                                                                    cluster_or_splits))
     with torch.cuda.device(x.device):
-        check(lib.sdfl_groupnorm_bias_forward(
+        check(lib.sdfl_groupnorm_bias_forward_ex(
             _dev(x, "x"), _dev(channel_bias, "channel_bias"), _dev(out, "out"), _f32(gamma, "gamma"),
             _f32(beta, "beta"), B, Cc, hw, num_groups, eps, int(silu), code, ws.data_ptr(), ws.numel(),
-            _stream(stream)), "sdfl_groupnorm_bias_forward")
+            path, cluster_or_splits, _stream(stream)), "sdfl_groupnorm_bias_forward")
     return out
 
 

@@ -79,9 +79,12 @@ def test_config5_vae_shapes_fp16(sdfl, shape):
     x, gamma, beta = gn_inputs(rng_for(5, shape[1]), shape, "float16")
     want = oracle_group_norm(x, gamma, beta, 32, 1e-6, True)
     plan = sdfl.ops.groupnorm_plan(shape[0], shape[1], shape[2] * shape[3], 32, torch.float16)
-    assert plan["path"] in (sdfl.ops.GN_RESIDENT, sdfl.ops.GN_SPLIT), plan
+    want_path = sdfl.ops.GN_REGISTER if shape[2] == 64 else sdfl.ops.GN_RESIDENT    # 128 KB slabs fit registers
+    assert plan["path"] == want_path, plan
     got = run_gn(sdfl, x, gamma, beta, 32, 1e-6, True)
     assert_close(got, want, TOL["float16"], f"{shape} automatic path {plan}")
+    got = run_gn(sdfl, x, gamma, beta, 32, 1e-6, True, path=sdfl.ops.GN_RESIDENT)
+    assert_close(got, want, TOL["float16"], f"{shape} cluster path")
     got = run_gn(sdfl, x, gamma, beta, 32, 1e-6, True, path=sdfl.ops.GN_SPLIT)
     assert_close(got, want, TOL["float16"], f"{shape} split")
     assert sdfl.ops.device_status() == 0
@@ -238,3 +241,86 @@ def test_time_embedding_add_fused_into_the_norm(sdfl, shape, G, dtype):
         assert to_np(got).tobytes() == want.tobytes()
     else:
         assert to_np(got).tobytes() == want.astype(np.float16).tobytes()
+
+
+def ring_knob(cluster, slots, chunk_kb, consumer_warps):
+    """Encoding of sdfl_groupnorm_forward_ex's `cluster_or_splits` for the cluster path."""
+    return cluster | (slots << 8) | (chunk_kb << 16) | (consumer_warps << 24)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "float16"])
+@pytest.mark.parametrize("shape,G,cluster,chunk_kb", [
+    ((2, 64, 64, 64), 8, 2, 16),       # whole chunks inside one channel
+    ((2, 64, 64, 64), 8, 4, 32),
+    ((1, 128, 128, 128), 32, 8, 16),   # several chunks per share, last ones held between the passes
+    ((2, 96, 40, 40), 8, 2, 16),       # chunks straddle channel ends: per-chunk fall-back to the loop
+    ((1, 32, 96, 96), 4, 3, 32),       # odd cluster size, ragged last chunk
+])
+def test_unrolled_chunks_with_256_consumer_threads(sdfl, shape, G, cluster, chunk_kb, dtype):
+    """The variants whose full chunks are a compile-time number of vectors per thread (8 consumer
+    warps, 16 or 32 KB chunks), with and without the fused per-channel addend."""
+    rng = rng_for(5, 900 + sum(shape) + cluster)
+    x, gamma, beta = gn_inputs(rng, shape, dtype)
+    e = (rng.standard_normal(shape[:2]) * 0.8).astype(np.float32).astype(x.dtype)
+    knob = ring_knob(cluster, 3, chunk_kb, 8)
+    kw = dict(path=sdfl.ops.GN_RESIDENT, cluster_or_splits=knob)
+    plan = sdfl.ops.groupnorm_plan(shape[0], shape[1], shape[2] * shape[3], G, getattr(torch, dtype),
+                                   sdfl.ops.GN_RESIDENT, knob)
+    assert plan["threads"] == 288 and plan["cluster"] == cluster
+    for silu in (True, False):
+        want = oracle_group_norm(x, gamma, beta, G, 1e-5, silu)
+        out = Guarded(shape, getattr(torch, dtype))
+        sdfl.ops.groupnorm(to_dev(x), to_dev(gamma), to_dev(beta), G, 1e-5, silu, out=out.tensor, **kw)
+        out.check()
+        assert_close(to_np(out.tensor), want, TOL[dtype], f"unrolled {shape} c={cluster} silu={silu}")
+        want = oracle_bias_group_norm(x, e, gamma, beta, G, 1e-5, silu)
+        out = Guarded(shape, getattr(torch, dtype))
+        sdfl.ops.groupnorm_bias(to_dev(x), to_dev(e), to_dev(gamma), to_dev(beta), G, 1e-5, silu,
+                                out=out.tensor, **kw)
+        out.check()
+        assert_close(to_np(out.tensor), want, TOL[dtype], f"unrolled+bias {shape} c={cluster} silu={silu}")
+    assert sdfl.ops.device_status() == 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "float16"])
+@pytest.mark.parametrize("shape,G", [
+    ((2, 320, 64, 64), 32), ((2, 1280, 8, 8), 32), ((2, 640, 32, 32), 32), ((2, 1920, 16, 16), 32),
+    ((1, 960, 32, 32), 32),
+    ((3, 12, 6, 6), 3),        # 4-channel groups of 36 elements: vectors straddle channels
+    ((2, 8, 2, 2), 2),         # one vector per slab (fp32) / half a vector's worth of threads
+    ((40, 64, 8, 8), 32),      # more slabs than CTAs in a wave
+])
+def test_register_path_one_cta_per_slab(sdfl, shape, G, dtype):
+    """Slabs up to 192 KB held in one CTA's registers: same results as the oracle, with and
+    without the fused per-channel addend, also in place."""
+    rng = rng_for(6, 1100 + sum(shape))
+    x, gamma, beta = gn_inputs(rng, shape, dtype)
+    e = (rng.standard_normal(shape[:2]) * 0.8).astype(np.float32).astype(x.dtype)
+    kw = dict(path=sdfl.ops.GN_REGISTER)
+    plan = sdfl.ops.groupnorm_plan(shape[0], shape[1], shape[2] * shape[3], G, getattr(torch, dtype),
+                                   sdfl.ops.GN_REGISTER, 0)
+    assert plan["path"] == sdfl.ops.GN_REGISTER
+    for silu in (True, False):
+        want = oracle_group_norm(x, gamma, beta, G, 1e-5, silu)
+        out = Guarded(shape, getattr(torch, dtype))
+        sdfl.ops.groupnorm(to_dev(x), to_dev(gamma), to_dev(beta), G, 1e-5, silu, out=out.tensor, **kw)
+        out.check()
+        assert_close(to_np(out.tensor), want, TOL[dtype], f"register {shape} silu={silu}")
+        buf = to_dev(x)
+        sdfl.ops.groupnorm(buf, to_dev(gamma), to_dev(beta), G, 1e-5, silu, out=buf, **kw)
+        assert_close(to_np(buf), want, TOL[dtype], f"register in place {shape} silu={silu}")
+        want = oracle_bias_group_norm(x, e, gamma, beta, G, 1e-5, silu)
+        out = Guarded(shape, getattr(torch, dtype))
+        sdfl.ops.groupnorm_bias(to_dev(x), to_dev(e), to_dev(gamma), to_dev(beta), G, 1e-5, silu,
+                                out=out.tensor, **kw)
+        out.check()
+        assert_close(to_np(out.tensor), want, TOL[dtype], f"register+bias {shape} silu={silu}")
+
+
+def test_register_path_refuses_large_slabs(sdfl):
+    x = torch.zeros((1, 32, 128, 128), device="cuda", dtype=torch.float32)     # 64 KB... per group 1 channel
+    g, b = torch.ones(32, device="cuda"), torch.zeros(32, device="cuda")
+    sdfl.ops.groupnorm(x, g, b, 32, 1e-5, False, path=sdfl.ops.GN_REGISTER)    # 64 KB slab: fine
+    big = torch.zeros((1, 32, 256, 256), device="cuda", dtype=torch.float32)   # 256 KB slabs
+    with pytest.raises(sdfl.SdflError):
+        sdfl.ops.groupnorm(big, g, b, 32, 1e-5, False, path=sdfl.ops.GN_REGISTER)
