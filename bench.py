@@ -503,6 +503,35 @@ def op_cases(torch, ops, dev):
     gn_bias("next: chunkwise_add+GN+SiLU f16 [2,1280,16,16]", 2, 1280, 16, f16, 1e-5)
     gn_bias("next: chunkwise_add+GN+SiLU f16 [8,256,256,256] (large)", 8, 256, 256, f16, 1e-5)
 
+    def gn_nhwc(name, B, C, H, dtype):
+        esz = 2 if dtype == f16 else 4
+
+        def make():
+            x = rnd((B, C, H, H), dtype)
+            y = torch.empty((B, H * H, C), device=dev, dtype=dtype)
+            g, b = 1 + 0.1 * rnd((C,), f32), 0.1 * rnd((C,), f32)
+            return lambda: ops.groupnorm_nhwc(x, g, b, 32, 1e-6, False, out=y)
+        cases.append((name, 2 * B * C * H * H * esz + 2 * C * 4, make, ("gnnhwc", B, C, H)))
+
+    gn_nhwc("next: GN + channels-last store f16 [2,320,64,64]", 2, 320, 64, f16)
+    gn_nhwc("next: GN + channels-last store f16 [2,1280,16,16]", 2, 1280, 16, f16)
+    gn_nhwc("next: GN + channels-last store f32 [1,320,64,64]", 1, 320, 64, f32)
+
+    def perm(name, I, J, K, dtype, add):
+        esz = 2 if dtype == f16 else 4
+
+        def make():
+            x = rnd((I, J, K), dtype)
+            r = rnd((I, K, J), dtype) if add else None
+            y = torch.empty((I, K, J), device=dev, dtype=dtype)
+            return (lambda: ops.permute_add(x, r, out=y)) if add else (lambda: ops.permute_021(x, out=y))
+        cases.append((name, (3 if add else 2) * I * J * K * esz, make, ("perm", I, J, K, add)))
+
+    perm("next: permute3D__0_2_1 f16 [2,320,4096]->[2,4096,320]", 2, 320, 4096, f16, False)
+    perm("next: permute + residual add f16 [2,4096,320]->[2,320,4096]", 2, 4096, 320, f16, True)
+    perm("next: permute + residual add f16 [64,4096,320] (large)", 64, 4096, 320, f16, True)
+    perm("next: permute3D__0_2_1 f32 [64,1280,1024] (large)", 64, 1280, 1024, f32, False)
+
     def ln(name, rows, D, dtype):
         esz = 2 if dtype == f16 else 4
 
@@ -625,6 +654,23 @@ def cpu_reference_case(spec) -> dict:
         t = timed(lambda: oracle.group_norm(oracle.chunkwise_add(x, e, H * H, backend=backend)[None],
                                             g, b, 32, eps, True, backend=backend), reps=2)
         scale, note = float(B), f"one image x {B}"
+    elif kind == "gnnhwc":
+        _, B, C, H = spec
+        x = rng.standard_normal((1, C, H, H), dtype=np.float32)
+        g, b = np.ones(C, np.float32), np.zeros(C, np.float32)
+        t = timed(lambda: oracle.permute_021(oracle.group_norm(x, g, b, 32, 1e-6, False, backend=backend)
+                                             .reshape(1, C, H * H), backend=backend), reps=2)
+        scale, note = float(B), f"one image x {B}"
+    elif kind == "perm":
+        _, I, J, K, add = spec
+        i = min(I, 4)
+        x = rng.standard_normal((i, J, K), dtype=np.float32)
+        r = rng.standard_normal((i, K, J), dtype=np.float32)
+        if add:
+            t = timed(lambda: oracle.elemwise_add(oracle.permute_021(x, backend=backend), r, backend=backend))
+        else:
+            t = timed(lambda: oracle.permute_021(x, backend=backend))
+        scale, note = I / i, f"{i} of {I} slices scaled"
     elif kind == "ln":
         _, rows, D = spec
         r = min(rows, 8192)

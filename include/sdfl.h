@@ -137,6 +137,32 @@ int sdfl_groupnorm_bias_forward_ex(const void *in, const void *channel_bias, voi
                                    int fuse_silu, int dtype, void *workspace, size_t workspace_bytes,
                                    int path, int cluster_or_splits, void *stream);
 
+/* GroupNorm(+SiLU) of an NCHW tensor written channels-last: out[n][p][c] ([batch, hw, channels]).
+ * Replaces GroupNorm::forward followed by permute3D__0_2_1 with global size {1, channels, hw}
+ * (NN/SpatialTransformer.cpp:127-140).  Slabs up to 48 KB in 16-byte aligned tensors: one kernel,
+ * one read and one write of the tensor.  Otherwise two kernels: the statistics (one read), then a
+ * tiled normalise-and-transpose over all SMs (a second read, from L2 for UNet sizes, and the
+ * write) -- against three reads and two writes for the reference's sequence.  The workspace
+ * (sdfl_groupnorm_nhwc_workspace_bytes, a few KB) holds the per-chunk moments.  in == out is an
+ * error: a transpose cannot run in place. */
+size_t sdfl_groupnorm_nhwc_workspace_bytes(int64_t batch, int64_t channels, int64_t hw,
+                                           int64_t num_groups, int dtype);
+int sdfl_groupnorm_nhwc_forward(const void *in, void *out, const float *gamma, const float *beta,
+                                int64_t batch, int64_t channels, int64_t hw, int64_t num_groups,
+                                float eps, int fuse_silu, int dtype, void *workspace,
+                                size_t workspace_bytes, void *stream);
+
+/* K/util.cl:47-64 permute3D__0_2_1(src, dst) with global size {I, J, K}: dst[i][k][j] = src[i][j][k]
+ * (NN/SpatialTransformer.cpp:131-134 with {1, C, HW}; :154-157 with {1, HW, C}). */
+int sdfl_permute3D__0_2_1(const void *src, void *dst, int64_t I, int64_t J, int64_t K, int dtype,
+                          void *stream);
+
+/* dst[i][k][j] = src[i][j][k] + residual[i][k][j]: the second permute of a SpatialTransformer
+ * block fused with the elemwise_add that follows it (NN/SpatialTransformer.cpp:154-171).
+ * residual may be dst (in-place accumulate); src may not overlap dst. */
+int sdfl_permute_add(const void *src, const void *residual, void *dst, int64_t I, int64_t J, int64_t K,
+                     int dtype, void *stream);
+
 /* K/util.cl:136-148  chunkwise_add(A, chunk, C, chunk_size) over n work-items:
  * C[i] = A[i] + chunk[i / chunk_size]; C may be A (NN/ResBlock.cpp:188-191). */
 int sdfl_chunkwise_add(const void *A, const void *chunk, void *C, int64_t n, int64_t chunk_size,

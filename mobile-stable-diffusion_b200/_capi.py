@@ -51,6 +51,10 @@ SIGNATURES = {
     "sdfl_groupnorm_forward_noalloc": (_i, [_p, _p, _p, _p, _i64, _i64, _i64, _i64, _f, _i, _i, _p]),
     "sdfl_groupnorm_bias_forward": (_i, [_p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _f, _i, _i, _p, _sz, _p]),
     "sdfl_groupnorm_bias_forward_ex": (_i, [_p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _f, _i, _i, _p, _sz, _i, _i, _p]),
+    "sdfl_groupnorm_nhwc_workspace_bytes": (_sz, [_i64, _i64, _i64, _i64, _i]),
+    "sdfl_groupnorm_nhwc_forward": (_i, [_p, _p, _p, _p, _i64, _i64, _i64, _i64, _f, _i, _i, _p, _sz, _p]),
+    "sdfl_permute3D__0_2_1": (_i, [_p, _p, _i64, _i64, _i64, _i, _p]),
+    "sdfl_permute_add": (_i, [_p, _p, _p, _i64, _i64, _i64, _i, _p]),
     "sdfl_chunkwise_add": (_i, [_p, _p, _p, _i64, _i64, _i, _p]),
     "sdfl_groupnorm_plan": (_i, [_i64, _i64, _i64, _i64, _i, _i, _i, C.POINTER(_i64)]),
     "sdfl_layernorm_forward": (_i, [_p, _p, _p, _p, _i64, _i64, _f, _i, _p]),

@@ -175,6 +175,61 @@ int sdfl_groupnorm_bias_forward_ex(const void *in, const void *channel_bias, voi
                       workspace, workspace_bytes, path, cluster_or_splits, as_stream(stream), channel_bias);
 }
 
+size_t sdfl_groupnorm_nhwc_workspace_bytes(int64_t batch, int64_t channels, int64_t hw,
+                                           int64_t num_groups, int dtype) {
+    if (!dtype_ok(dtype) || batch <= 0 || channels <= 0 || hw <= 0 || num_groups <= 0 ||
+        channels % num_groups != 0)
+        return 0;
+    // the per-chunk moments of the statistics kernel (the two-kernel form; the one-kernel form
+    // for small slabs needs none, but which one runs also depends on the pointers' alignment)
+    return sdfl_groupnorm_workspace_bytes_ex(batch, channels, hw, num_groups, dtype, SDFL_GN_SPLIT, 0);
+}
+
+int sdfl_groupnorm_nhwc_forward(const void *in, void *out, const float *gamma, const float *beta,
+                                int64_t batch, int64_t channels, int64_t hw, int64_t num_groups,
+                                float eps, int fuse_silu, int dtype, void *workspace,
+                                size_t workspace_bytes, void *stream) {
+    int rc = gn_validate(in, out, gamma, beta, batch, channels, hw, num_groups, eps, dtype);
+    if (rc != SDFL_OK) return rc;
+    if (batch == 0 || hw == 0) return SDFL_OK;
+    if (batch > 65535) return SDFL_ERR_UNSUPPORTED;
+    const int64_t bytes = batch * channels * hw * esize(dtype);
+    if (in == out || partial_overlap(in, bytes, out, bytes)) return SDFL_ERR_OVERLAP;   // a transpose cannot run in place
+    sdfl::GnShape s{batch, channels, hw, num_groups, dtype, eps,
+                    fuse_silu ? sdfl::kActSilu : sdfl::kActNone};
+    sdfl::GnPlan plan;
+    const bool fused = sdfl::gn_nhwc_fused_ok(s, in, out);
+    cudaError_t e = sdfl::gn_make_plan(s, in, out, fused ? sdfl::kGnRegister : sdfl::kGnSplit, 0, &plan);
+    if (e == cudaErrorInvalidConfiguration || e == cudaErrorInvalidValue) return SDFL_ERR_UNSUPPORTED;
+    if (e != cudaSuccess) return cuda_fail(e);
+    plan.nhwc = 1;
+    if (!fused && (workspace == nullptr || workspace_bytes < plan.workspace)) return SDFL_ERR_WORKSPACE;
+    return wrap(sdfl::gn_launch(s, plan, in, out, gamma, beta, workspace, as_stream(stream)));
+}
+
+static int permute_checked(const void *src, const void *res, void *dst, int64_t I, int64_t J, int64_t K,
+                           int dtype, void *stream) {
+    if (!dtype_ok(dtype) || I < 0 || J < 0 || K < 0) return SDFL_ERR_INVALID_VALUE;
+    if (J >= (1ll << 31) || K >= (1ll << 31)) return SDFL_ERR_UNSUPPORTED;
+    if (I == 0 || J == 0 || K == 0) return SDFL_OK;
+    if (!src || !dst) return SDFL_ERR_INVALID_POINTER;
+    const int64_t bytes = I * J * K * esize(dtype);
+    if (src == dst || partial_overlap(src, bytes, dst, bytes)) return SDFL_ERR_OVERLAP;
+    if (res && res != dst && partial_overlap(res, bytes, dst, bytes)) return SDFL_ERR_OVERLAP;
+    return wrap(sdfl::permute_021_launch(src, res, dst, I, J, K, dtype, as_stream(stream)));
+}
+
+int sdfl_permute3D__0_2_1(const void *src, void *dst, int64_t I, int64_t J, int64_t K, int dtype,
+                          void *stream) {
+    return permute_checked(src, nullptr, dst, I, J, K, dtype, stream);
+}
+
+int sdfl_permute_add(const void *src, const void *residual, void *dst, int64_t I, int64_t J, int64_t K,
+                     int dtype, void *stream) {
+    if (!residual && I > 0 && J > 0 && K > 0) return SDFL_ERR_INVALID_POINTER;
+    return permute_checked(src, residual, dst, I, J, K, dtype, stream);
+}
+
 int sdfl_chunkwise_add(const void *A, const void *chunk, void *C, int64_t n, int64_t chunk_size,
                        int dtype, void *stream) {
     if (!dtype_ok(dtype) || n < 0 || chunk_size <= 0) return SDFL_ERR_INVALID_VALUE;

@@ -723,14 +723,24 @@ struct RegArgs {
     float eps;
     FastDiv hw_div;        // element offset in the slab -> channel of the group
     FastDiv hwv_div;       // vector offset -> channel (when vec_uniform)
+    // channels-last output (NHWC template flag)
+    uint32_t hw, hw_vecs;
+    uint32_t row_bytes;    // shared-memory stride of one channel's pixels: hw * sizeof(T) rounded up to 4, plus 4
+    uint32_t pair;         // fp16 and an even number of channels per group: two channels per store
+    FastDiv out_div;       // output index within the slab -> pixel (divides by cpg, or cpg / 2 when pair)
 };
 
-template <typename T, int ACT, bool BIAS, int NVT>
+// NHWC: the result is written channels-last, out[n][p][c] (the permute3D__0_2_1 that follows the
+// norm of a SpatialTransformer block, SpatialTransformer.cpp:127-140, fused into the store).  The
+// normalised slab [cpg][hw] goes through shared memory with a 4-byte skew per channel row and
+// leaves as runs of cpg consecutive channels per pixel.
+template <typename T, int ACT, bool BIAS, int NVT, bool NHWC>
 __global__ void __launch_bounds__(kRegThreads, NVT <= 4 ? 2 : 1)
 gn_register_kernel(const RegArgs a) {
     constexpr int VEC = VecOf<T>::N;
     constexpr bool HALF = sizeof(T) == 2;
     __shared__ Moments warp_m[kRegThreads / 32];
+    extern __shared__ __align__(16) unsigned char tsm[];      // NHWC only: cpg rows of row_bytes
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     for (uint32_t unit = blockIdx.x; unit < a.units; unit += gridDim.x) {
         const uint4 *src = reinterpret_cast<const uint4 *>(a.in) + static_cast<size_t>(unit) * a.slab_vecs;
@@ -800,7 +810,14 @@ gn_register_kernel(const RegArgs a) {
                     const uint32_t cl = a.hwv_div.div(idx), c = ch0 + cl;
                     const float mc = BIAS ? mean - to_float<T>(erow[cl]) : mean;
                     const Affine<T> af = make_affine<T, ACT>(mc, rstd, __ldg(a.w + c), __ldg(a.b + c));
-                    st_stream(dst + idx, norm_vec<T, ACT>(v[k], af));
+                    const uint4 r = norm_vec<T, ACT>(v[k], af);
+                    if (NHWC) {
+                        const uint32_t p0 = (idx - cl * a.hw_vecs) * VEC;
+                        uint32_t *d = reinterpret_cast<uint32_t *>(tsm + cl * a.row_bytes + p0 * sizeof(T));
+                        d[0] = r.x; d[1] = r.y; d[2] = r.z; d[3] = r.w;
+                    } else {
+                        st_stream(dst + idx, r);
+                    }
                 } else {
                     float f[VEC];
                     unpack<T>(v[k], f);
@@ -809,12 +826,38 @@ gn_register_kernel(const RegArgs a) {
                         const uint32_t cl = a.hw_div.div(idx * VEC + l), c = ch0 + cl;
                         const float mc = BIAS ? mean - to_float<T>(erow[cl]) : mean;
                         f[l] = activate<ACT, HALF>(fmaf((f[l] - mc) * rstd, __ldg(a.w + c), __ldg(a.b + c)));
+                        if (NHWC) {
+                            const uint32_t p = idx * VEC + l - cl * a.hw;
+                            *reinterpret_cast<T *>(tsm + cl * a.row_bytes + p * sizeof(T)) = from_float<T>(f[l]);
+                        }
                     }
-                    st_stream(dst + idx, pack<T>(f));
+                    if (!NHWC) st_stream(dst + idx, pack<T>(f));
                 }
             }
         }
-        __syncthreads();       // warp_m is reused by the next slab
+        __syncthreads();       // warp_m is reused by the next slab; NHWC: the slab is in shared memory
+        if (NHWC) {
+            // out[n][p][ch0 + c]: consecutive threads take consecutive channels of a pixel
+            T *outp = static_cast<T *>(a.out) + static_cast<size_t>(unit / a.groups) * a.hw * a.channels + ch0;
+            if (HALF && a.pair) {
+                const uint32_t hp = a.cpg >> 1, total = a.hw * hp;
+                for (uint32_t o = tid; o < total; o += kRegThreads) {
+                    const uint32_t p = a.out_div.div(o), c = 2u * (o - p * hp);
+                    const unsigned short lo = *reinterpret_cast<const unsigned short *>(tsm + c * a.row_bytes + p * 2u);
+                    const unsigned short hi = *reinterpret_cast<const unsigned short *>(tsm + (c + 1u) * a.row_bytes + p * 2u);
+                    *reinterpret_cast<uint32_t *>(outp + static_cast<size_t>(p) * a.channels + c) =
+                        static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
+                }
+            } else {
+                const uint32_t total = a.hw * a.cpg;
+                for (uint32_t o = tid; o < total; o += kRegThreads) {
+                    const uint32_t p = a.out_div.div(o), c = o - p * a.cpg;
+                    outp[static_cast<size_t>(p) * a.channels + c] =
+                        *reinterpret_cast<const T *>(tsm + c * a.row_bytes + p * sizeof(T));
+                }
+            }
+            __syncthreads();   // the next slab overwrites the staging rows
+        }
     }
 }
 
@@ -954,6 +997,82 @@ __global__ void __launch_bounds__(kSplitThreads) gn_split_apply_kernel(const Spl
     }
 }
 
+// Second kernel of the split path with a channels-last store: out[n][p][c] = act(norm(in[n][c][p])).
+// A CTA takes a tile of TS channels x TS pixels (TS = 64 with two elements per access, 32 with one),
+// folds the per-chunk moments of the groups its channels belong to, applies the affine while
+// loading (rows along the pixels: coalesced) and writes through shared memory with rows along
+// the channels (coalesced again).  grid (ceil(hw / TS), ceil(C / TS), batch), block (32, 8).
+template <typename T, int ACT, bool PAIRS>
+__global__ void __launch_bounds__(256) gn_apply_nhwc_kernel(const SplitArgs a, uint32_t hw) {
+    constexpr bool HALF = sizeof(T) == 2;
+    constexpr int TS = PAIRS ? 64 : 32, E = PAIRS ? 2 : 1;
+    constexpr int PAD = PAIRS ? (HALF ? 2 : 1) : 1;
+    __shared__ __align__(8) T tile[TS][TS + PAD];
+    __shared__ float4 coef[TS];        // per channel of the tile: mean, rstd, scale, shift
+    const uint32_t tx = threadIdx.x, ty = threadIdx.y, tid = ty * 32 + tx;
+    const uint32_t p0 = blockIdx.x * TS, c0 = blockIdx.y * TS, n = blockIdx.z;
+    if (tid < TS && c0 + tid < a.channels) {
+        const uint32_t c = c0 + tid;
+        const size_t unit = static_cast<size_t>(n) * a.groups + c / a.cpg;
+        Moments m{0.f, 0.f, 0.f};
+        for (uint32_t s = 0; s < a.splits; ++s) {      // chunks in order: every CTA gets the same bits
+            const uint32_t e0 = s * a.chunk_elems, e1 = min(a.slab_elems, e0 + a.chunk_elems);
+            Moments y;
+            y.n = e1 > e0 ? static_cast<float>(e1 - e0) : 0.f;
+            y.mean = a.partial[2 * (unit * a.splits + s)];
+            y.m2 = a.partial[2 * (unit * a.splits + s) + 1];
+            m = merge(m, y);
+        }
+        const float var = m.m2 / static_cast<float>(a.slab_elems);
+        coef[tid] = make_float4(m.mean, 1.0f / sqrtf(var + a.eps), __ldg(a.w + c), __ldg(a.b + c));
+    }
+    __syncthreads();
+    const T *x = static_cast<const T *>(a.in) + static_cast<size_t>(n) * a.channels * hw;
+    T *y = static_cast<T *>(a.out) + static_cast<size_t>(n) * a.channels * hw;
+#pragma unroll
+    for (int r = ty; r < TS; r += 8) {
+        const uint32_t c = c0 + r, p = p0 + E * tx;
+        if (c < a.channels && p < hw) {
+            const float4 k = coef[r];
+            const T *src = x + static_cast<size_t>(c) * hw + p;
+            if (PAIRS) {
+                float f0, f1;
+                if (HALF) {
+                    const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(src));
+                    f0 = f.x; f1 = f.y;
+                } else {
+                    const float2 f = *reinterpret_cast<const float2 *>(src);
+                    f0 = f.x; f1 = f.y;
+                }
+                tile[r][2 * tx] = from_float<T>(activate<ACT, HALF>(fmaf((f0 - k.x) * k.y, k.z, k.w)));
+                tile[r][2 * tx + 1] = from_float<T>(activate<ACT, HALF>(fmaf((f1 - k.x) * k.y, k.z, k.w)));
+            } else {
+                tile[r][tx] = from_float<T>(activate<ACT, HALF>(fmaf((to_float<T>(*src) - k.x) * k.y, k.z, k.w)));
+            }
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int r = ty; r < TS; r += 8) {
+        const uint32_t p = p0 + r, c = c0 + E * tx;
+        if (p < hw && c < a.channels) {
+            T *dst = y + static_cast<size_t>(p) * a.channels + c;
+            if (PAIRS) {
+                const T v0 = tile[2 * tx][r], v1 = tile[2 * tx + 1][r];
+                if (HALF) {
+                    *reinterpret_cast<uint32_t *>(dst) =
+                        static_cast<uint32_t>(*reinterpret_cast<const unsigned short *>(&v0)) |
+                        (static_cast<uint32_t>(*reinterpret_cast<const unsigned short *>(&v1)) << 16);
+                } else {
+                    *reinterpret_cast<float2 *>(dst) = make_float2(to_float<T>(v0), to_float<T>(v1));
+                }
+            } else {
+                *dst = tile[tx][r];
+            }
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------------------------
 // Stand-alone kernels for the reference's three-launch sequence
 // ---------------------------------------------------------------------------------------------
@@ -1087,24 +1206,53 @@ cudaError_t launch_resident(const ResidentArgs &a, const GnPlan &plan, cudaStrea
                   : launch_resident_as<T, ACT, false>(a, plan, stream);
 }
 
+constexpr size_t kRegMaxStageBytes = 200 * 1024;   // shared-memory staging of the channels-last store
+
+template <typename T, int ACT, int NVT>
+cudaError_t launch_register_nhwc(const RegArgs &a, unsigned grid, size_t smem, cudaStream_t stream) {
+    static std::atomic<bool> done[kMaxDevices];
+    int dev = 0;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess) return err;
+    if (!(dev >= 0 && dev < kMaxDevices && done[dev].load(std::memory_order_acquire))) {
+        err = cudaFuncSetAttribute(gn_register_kernel<T, ACT, false, NVT, true>,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   static_cast<int>(kRegMaxStageBytes));
+        if (err != cudaSuccess) return err;
+        if (dev >= 0 && dev < kMaxDevices) done[dev].store(true, std::memory_order_release);
+    }
+    gn_register_kernel<T, ACT, false, NVT, true><<<grid, kRegThreads, smem, stream>>>(a);
+    return cudaGetLastError();
+}
+
 template <typename T, int ACT, bool BIAS>
-cudaError_t launch_register_as(const RegArgs &a, cudaStream_t stream) {
+cudaError_t launch_register_as(const RegArgs &a, bool nhwc, cudaStream_t stream) {
     const uint32_t per_thread = (a.slab_vecs + kRegThreads - 1) / kRegThreads;
     const unsigned grid = a.units < 148u * 64u ? a.units : 148u * 64u;
-    if (per_thread <= 4)
-        gn_register_kernel<T, ACT, BIAS, 4><<<grid, kRegThreads, 0, stream>>>(a);
-    else if (per_thread <= 12)
-        gn_register_kernel<T, ACT, BIAS, 12><<<grid, kRegThreads, 0, stream>>>(a);
-    else
-        gn_register_kernel<T, ACT, BIAS, kRegMaxVecs><<<grid, kRegThreads, 0, stream>>>(a);
-    cudaError_t err = cudaGetLastError();
+    cudaError_t err;
+    if (nhwc) {
+        if (BIAS) return cudaErrorInvalidValue;
+        const size_t smem = static_cast<size_t>(a.cpg) * a.row_bytes;
+        err = per_thread <= 4    ? launch_register_nhwc<T, ACT, 4>(a, grid, smem, stream)
+              : per_thread <= 12 ? launch_register_nhwc<T, ACT, 12>(a, grid, smem, stream)
+                                 : launch_register_nhwc<T, ACT, kRegMaxVecs>(a, grid, smem, stream);
+    } else {
+        if (per_thread <= 4)
+            gn_register_kernel<T, ACT, BIAS, 4, false><<<grid, kRegThreads, 0, stream>>>(a);
+        else if (per_thread <= 12)
+            gn_register_kernel<T, ACT, BIAS, 12, false><<<grid, kRegThreads, 0, stream>>>(a);
+        else
+            gn_register_kernel<T, ACT, BIAS, kRegMaxVecs, false><<<grid, kRegThreads, 0, stream>>>(a);
+        err = cudaGetLastError();
+    }
     if (err == cudaSuccess) g_launches.fetch_add(1);
     return err;
 }
 
 template <typename T, int ACT>
-cudaError_t launch_register(const RegArgs &a, cudaStream_t stream) {
-    return a.bias ? launch_register_as<T, ACT, true>(a, stream) : launch_register_as<T, ACT, false>(a, stream);
+cudaError_t launch_register(const RegArgs &a, bool nhwc, cudaStream_t stream) {
+    return a.bias ? launch_register_as<T, ACT, true>(a, nhwc, stream)
+                  : launch_register_as<T, ACT, false>(a, nhwc, stream);
 }
 
 // How many clusters of this size, block size and shared-memory footprint can be resident at
@@ -1165,6 +1313,29 @@ inline bool prefer_register(int64_t slab_bytes, int64_t units) {
 // ---------------------------------------------------------------------------------------------
 // Planning
 // ---------------------------------------------------------------------------------------------
+// Slabs up to this size take the one-kernel channels-last path (statistics, normalise and the
+// transposing store by the one CTA that holds the slab); beyond it the CTA's scattered
+// cpg-element runs cost more than a second kernel: statistics, then a tiled apply over all SMs.
+constexpr int64_t kNhwcFusedMaxSlabBytes = 48 * 1024;
+
+// Shared-memory row stride of the channels-last store: a channel's pixels, 4-byte aligned, plus a
+// 4-byte skew so that consecutive channels start in consecutive banks.
+int64_t gn_nhwc_row_bytes(const GnShape &s) {
+    const int64_t esz = s.dtype == kF16 ? 2 : 4;
+    return ((s.hw * esz + 3) / 4) * 4 + 4;
+}
+
+bool gn_nhwc_fused_ok(const GnShape &s, const void *in, const void *out) {
+    const int64_t esz = s.dtype == kF16 ? 2 : 4;
+    if (s.groups <= 0 || s.channels % s.groups != 0) return false;
+    const int64_t cpg = s.channels / s.groups;
+    const int64_t slab_bytes = cpg * s.hw * esz;
+    return aligned16(in) && aligned16(out) && slab_bytes % 16 == 0 && slab_bytes >= 16 &&
+           slab_bytes <= kNhwcFusedMaxSlabBytes &&
+           cpg * gn_nhwc_row_bytes(s) <= static_cast<int64_t>(kRegMaxStageBytes) &&
+           s.batch * s.groups < (1ll << 27) && s.hw * cpg < (1ll << 31);
+}
+
 cudaError_t gn_make_plan(const GnShape &s, const void *in, const void *out, int force_path,
                          int force_cluster, GnPlan *plan) {
     const int64_t esz = s.dtype == kF16 ? 2 : 4;
@@ -1302,11 +1473,17 @@ cudaError_t gn_launch(const GnShape &s, const GnPlan &plan, const void *in, void
         a.eps = s.eps;
         a.hw_div = FastDiv::make(static_cast<uint32_t>(s.hw));
         a.hwv_div = FastDiv::make(a.vec_uniform ? static_cast<uint32_t>(s.hw / vec) : 1u);
+        a.hw = static_cast<uint32_t>(s.hw);
+        a.hw_vecs = a.vec_uniform ? static_cast<uint32_t>(s.hw / vec) : 1u;
+        a.row_bytes = static_cast<uint32_t>(gn_nhwc_row_bytes(s));
+        a.pair = s.dtype == kF16 && cpg % 2 == 0;
+        a.out_div = FastDiv::make(static_cast<uint32_t>(a.pair ? cpg / 2 : cpg));
+        const bool nhwc = plan.nhwc != 0;
         if (s.dtype == kF16)
-            return s.act == kActSilu ? launch_register<__half, kActSilu>(a, stream)
-                                     : launch_register<__half, kActNone>(a, stream);
-        return s.act == kActSilu ? launch_register<float, kActSilu>(a, stream)
-                                 : launch_register<float, kActNone>(a, stream);
+            return s.act == kActSilu ? launch_register<__half, kActSilu>(a, nhwc, stream)
+                                     : launch_register<__half, kActNone>(a, nhwc, stream);
+        return s.act == kActSilu ? launch_register<float, kActSilu>(a, nhwc, stream)
+                                 : launch_register<float, kActNone>(a, nhwc, stream);
     }
 
     if (plan.path == kGnResident) {
@@ -1352,6 +1529,35 @@ cudaError_t gn_launch(const GnShape &s, const GnPlan &plan, const void *in, void
     a.eps = s.eps;
     a.hw_div = FastDiv::make(static_cast<uint32_t>(s.hw));
     const unsigned grid = static_cast<unsigned>(units * plan.splits);
+    if (plan.nhwc) {
+        // statistics as usual, then the tiled apply that writes channels-last
+        if (bias != nullptr || s.batch > 65535) return cudaErrorInvalidValue;
+        const uintptr_t pa = esz == 2 ? 3 : 7;
+        const bool pairs = s.hw % 2 == 0 && s.channels % 2 == 0 &&
+                           (reinterpret_cast<uintptr_t>(in) & pa) == 0 && (reinterpret_cast<uintptr_t>(out) & pa) == 0;
+        const int ts = pairs ? 64 : 32;
+        const dim3 tgrid(static_cast<unsigned>((s.hw + ts - 1) / ts), static_cast<unsigned>((s.channels + ts - 1) / ts),
+                         static_cast<unsigned>(s.batch));
+        if (tgrid.y > 65535) return cudaErrorInvalidValue;
+        const dim3 tblock(32, 8);
+        const uint32_t hw32 = static_cast<uint32_t>(s.hw);
+#define SDFL_NHWC_APPLY(T, ACT)                                                              \
+        do {                                                                                 \
+            if (pairs) gn_apply_nhwc_kernel<T, ACT, true><<<tgrid, tblock, 0, stream>>>(a, hw32);   \
+            else gn_apply_nhwc_kernel<T, ACT, false><<<tgrid, tblock, 0, stream>>>(a, hw32);        \
+        } while (0)
+        if (s.dtype == kF16) {
+            gn_split_stats_kernel<__half><<<grid, kSplitThreads, 0, stream>>>(a);
+            if (s.act == kActSilu) SDFL_NHWC_APPLY(__half, kActSilu); else SDFL_NHWC_APPLY(__half, kActNone);
+        } else {
+            gn_split_stats_kernel<float><<<grid, kSplitThreads, 0, stream>>>(a);
+            if (s.act == kActSilu) SDFL_NHWC_APPLY(float, kActSilu); else SDFL_NHWC_APPLY(float, kActNone);
+        }
+#undef SDFL_NHWC_APPLY
+        cudaError_t err = cudaGetLastError();
+        if (err == cudaSuccess) g_launches.fetch_add(2);
+        return err;
+    }
     if (s.dtype == kF16) {
         gn_split_stats_kernel<__half><<<grid, kSplitThreads, 0, stream>>>(a);
         if (s.act == kActSilu) gn_split_apply_kernel<__half, kActSilu><<<grid, kSplitThreads, 0, stream>>>(a);

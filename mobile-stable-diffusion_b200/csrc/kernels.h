@@ -33,6 +33,7 @@ struct GnPlan {
     int splits;        // chunks per slab (split path)
     size_t smem;       // dynamic shared memory per CTA (resident)
     size_t workspace;  // scratch bytes the split path needs
+    int nhwc;          // register path only: write the result channels-last ([batch, hw, channels])
 };
 
 struct GnShape {
@@ -46,6 +47,12 @@ struct GnShape {
 // in/out alignment matters for the resident path (16-byte bulk copies).
 cudaError_t gn_make_plan(const GnShape &s, const void *in, const void *out, int force_path,
                          int force_cluster, GnPlan *plan);
+
+// Whether GroupNorm with a channels-last store can run as one kernel (slab in one CTA's registers,
+// transposed through shared memory); otherwise the caller normalises into a scratch tensor and
+// transposes it with permute_021_launch.
+bool gn_nhwc_fused_ok(const GnShape &s, const void *in, const void *out);
+int64_t gn_nhwc_row_bytes(const GnShape &s);
 
 // bias: optional [batch, channels] addend of the storage type, applied before the statistics.
 cudaError_t gn_launch(const GnShape &s, const GnPlan &plan, const void *in, void *out,
@@ -96,6 +103,10 @@ cudaError_t act_launch(int act, const void *src, void *dst, int64_t n, int dtype
 cudaError_t add_launch(const void *a, const void *b, void *c, int64_t n, int dtype,
                        cudaStream_t stream);
 // C[i] = A[i] + chunk[i / chunk_size]   (util.cl:136-148)
+// dst[i][k][j] = src[i][j][k] (+ res[i][k][j] when res != nullptr): the reference's
+// permute3D__0_2_1, optionally fused with the residual add that follows it.
+cudaError_t permute_021_launch(const void *src, const void *res, void *dst, int64_t I, int64_t J,
+                               int64_t K, int dtype, cudaStream_t stream);
 cudaError_t chunkwise_add_launch(const void *a, const void *chunk, void *c, int64_t n,
                                  int64_t chunk_size, int dtype, cudaStream_t stream);
 

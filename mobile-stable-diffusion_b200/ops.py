@@ -18,7 +18,7 @@ __all__ = [
     "elemwise_add", "token_embedding", "timestep_embedding", "local_reduction_mean",
     "local_reduction_variance", "group_norm_apply", "layer_norm_apply", "device_status",
     "selftest_bounded_wait",
-    "launch_count", "HostPipeline", "GN_AUTO", "GN_RESIDENT", "GN_SPLIT", "GN_REGISTER",
+    "launch_count", "HostPipeline", "GN_AUTO", "GN_RESIDENT", "GN_SPLIT", "GN_REGISTER", "groupnorm_nhwc", "permute_021", "permute_add",
 ]
 
 
@@ -130,6 +130,53 @@ def groupnorm_bias(x: torch.Tensor, channel_bias: torch.Tensor, gamma: torch.Ten
             _dev(x, "x"), _dev(channel_bias, "channel_bias"), _dev(out, "out"), _f32(gamma, "gamma"),
             _f32(beta, "beta"), B, Cc, hw, num_groups, eps, int(silu), code, ws.data_ptr(), ws.numel(),
             path, cluster_or_splits, _stream(stream)), "sdfl_groupnorm_bias_forward")
+    return out
+
+
+def groupnorm_nhwc(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor, num_groups: int,
+                   eps: float = 1e-5, silu: bool = False, out: torch.Tensor | None = None,
+                   stream=None) -> torch.Tensor:
+    """act(GroupNorm(x)) of an NCHW tensor, written channels-last: out is [B, H*W, C]."""
+    _dev(x, "x")
+    B, Cc = x.shape[0], x.shape[1]
+    hw = x.numel() // (B * Cc) if B * Cc else 0
+    out = torch.empty((B, hw, Cc), dtype=x.dtype, device=x.device) if out is None else out
+    if out.numel() != x.numel() or out.dtype != x.dtype:
+        raise ValueError("out must have x's element count and dtype")
+    code = _dtype_code(x)
+    ws = _workspace(x.device, lib.sdfl_groupnorm_nhwc_workspace_bytes(B, Cc, hw, num_groups, code))
+    with torch.cuda.device(x.device):
+        check(lib.sdfl_groupnorm_nhwc_forward(
+            _dev(x, "x"), _dev(out, "out"), _f32(gamma, "gamma"), _f32(beta, "beta"), B, Cc, hw,
+            num_groups, eps, int(silu), code, ws.data_ptr(), ws.numel(),
+            _stream(stream)), "sdfl_groupnorm_nhwc_forward")
+    return out
+
+
+def permute_021(src: torch.Tensor, out: torch.Tensor | None = None, stream=None) -> torch.Tensor:
+    """[I, J, K] -> [I, K, J] (the reference's permute3D__0_2_1)."""
+    if src.dim() != 3:
+        raise ValueError("permute_021 takes a 3-D tensor")
+    I, J, K = src.shape
+    out = torch.empty((I, K, J), dtype=src.dtype, device=src.device) if out is None else out
+    with torch.cuda.device(src.device):
+        check(lib.sdfl_permute3D__0_2_1(_dev(src, "src"), _dev(out, "out"), I, J, K, _dtype_code(src),
+                                        _stream(stream)), "sdfl_permute3D__0_2_1")
+    return out
+
+
+def permute_add(src: torch.Tensor, residual: torch.Tensor, out: torch.Tensor | None = None,
+                stream=None) -> torch.Tensor:
+    """out[i, k, j] = src[i, j, k] + residual[i, k, j]."""
+    if src.dim() != 3:
+        raise ValueError("permute_add takes a 3-D tensor")
+    I, J, K = src.shape
+    if residual.numel() != src.numel() or residual.dtype != src.dtype:
+        raise ValueError("residual must have src's element count and dtype")
+    out = torch.empty((I, K, J), dtype=src.dtype, device=src.device) if out is None else out
+    with torch.cuda.device(src.device):
+        check(lib.sdfl_permute_add(_dev(src, "src"), _dev(residual, "residual"), _dev(out, "out"), I, J, K,
+                                   _dtype_code(src), _stream(stream)), "sdfl_permute_add")
     return out
 
 

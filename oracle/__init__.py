@@ -71,6 +71,7 @@ def port_lib():
             getattr(lib, name).argtypes = [_f32p, _f32p, _sz]
         lib.oracle_elemwise_add.argtypes = [_f32p, _f32p, _f32p, _sz]
         lib.oracle_chunkwise_add.argtypes = [_f32p, _f32p, _f32p, _sz, _sz]
+        lib.oracle_permute3D__0_2_1.argtypes = [_f32p, _f32p, _sz, _sz, _sz]
         lib.oracle_token_embedding.argtypes = [_i64p, _f32p, _f32p, _f32p, _sz, _sz, _sz, _sz]
         lib.oracle_token_embedding.restype = C.c_int
         lib.oracle_timestep_embedding.argtypes = [_i64p, _f32p, _sz, _sz, C.c_float]
@@ -105,6 +106,7 @@ def ref_lib():
         lib.ref_gelu.argtypes = [_f32p, _f32p, _sz]
         lib.ref_elemwise_add.argtypes = [_f32p, _f32p, _f32p, _sz]
         lib.ref_chunkwise_add.argtypes = [_f32p, _f32p, _f32p, _sz, _sz]
+        lib.ref_permute3D__0_2_1.argtypes = [_f32p, _f32p, _sz, _sz, _sz]
         _ref = lib
     return _ref
 
@@ -252,6 +254,16 @@ def elemwise_add(a, b, backend: str = "port"):
         ref_lib().ref_elemwise_add(_fp(a), _fp(b), _fp(out), a.size)
     else:
         port_lib().oracle_elemwise_add(_fp(a), _fp(b), _fp(out), a.size)
+    return out
+
+
+def permute_021(src, backend: str = "port"):
+    """[I, J, K] -> [I, K, J]: the reference's permute3D__0_2_1 with global size {I, J, K}."""
+    src = _c32(src)
+    I, J, K = src.shape
+    out = np.empty((I, K, J), np.float32)
+    fn = ref_lib().ref_permute3D__0_2_1 if backend == "ref" else port_lib().oracle_permute3D__0_2_1
+    fn(_fp(src), _fp(out), I, J, K)
     return out
 
 

@@ -208,6 +208,29 @@ static void enqueue_1d_groups(size_t global, size_t local, void (*entry)(void *)
     }
 }
 
+// clEnqueueNDRangeKernel(queue, k, 3, NULL, {gx, gy, gz}, NULL, ...) for barrier-free kernels
+// (local size 1 in every dimension, so group id == global id).
+template <class F>
+static void enqueue_3d_flat(size_t gx, size_t gy, size_t gz, F &&body) {
+#pragma omp parallel
+    {
+        tls.range = Range{{gx, gy, gz}, {1, 1, 1}, {0, 0, 0}};
+        tls.fiber = nullptr;
+#pragma omp for schedule(static) collapse(2)
+        for (long x = 0; x < static_cast<long>(gx); ++x)
+            for (long y = 0; y < static_cast<long>(gy); ++y)
+                for (size_t z = 0; z < gz; ++z) {
+                    const size_t id[3] = {static_cast<size_t>(x), static_cast<size_t>(y), z};
+                    for (int d = 0; d < 3; ++d) {
+                        tls.item.global_id[d] = id[d];
+                        tls.item.group_id[d] = id[d];
+                        tls.item.local_id[d] = 0;
+                    }
+                    body();
+                }
+    }
+}
+
 // clEnqueueNDRangeKernel(queue, k, 1, NULL, {global}, NULL, ...) for barrier-free kernels.
 template <class F>
 static void enqueue_1d_flat(size_t global, F &&body) {
@@ -250,6 +273,7 @@ static void enqueue_2d_flat(size_t g0, size_t g1, F &&body) {
 using clshim::enqueue_1d_flat;
 using clshim::enqueue_1d_groups;
 using clshim::enqueue_2d_flat;
+using clshim::enqueue_3d_flat;
 
 namespace {
 
@@ -350,6 +374,11 @@ void ref_silu(const float *src, float *dst, size_t n) {
 
 void ref_gelu(const float *src, float *dst, size_t n) {
     enqueue_1d_flat(n, [=] { ref_util::gelu(const_cast<float *>(src), dst); });
+}
+
+// permute3D__0_2_1 as launched at nn/SpatialTransformer.cpp:131-134 / :154-157: global size {I, J, K}.
+void ref_permute3D__0_2_1(const float *src, float *dst, size_t I, size_t J, size_t K) {
+    enqueue_3d_flat(I, J, K, [=] { ref_util::permute3D__0_2_1(const_cast<float *>(src), dst); });
 }
 
 void ref_chunkwise_add(const float *A, const float *chunk, float *C, size_t n, size_t chunk_size) {

@@ -219,6 +219,18 @@ void oracle_elemwise_add(const float *A, const float *B, float *C, size_t n) {
     for (long i = 0; i < (long)n; ++i) C[i] = A[i] + B[i];
 }
 
+/* util.cl:47-64 permute3D__0_2_1 with global size {I, J, K}: dst[i][k][j] = src[i][j][k]
+ * (src_idx = i*J*K + j*K + k, dst_idx = i*K*J + k*J + j).  nn/SpatialTransformer.cpp:131-134
+ * runs it with {1, C, HW} after the block's GroupNorm and :154-157 with {1, HW, C} before the
+ * residual elemwise_add. */
+void oracle_permute3D__0_2_1(const float *src, float *dst, size_t I, size_t J, size_t K) {
+#pragma omp parallel for schedule(static) collapse(2)
+    for (long i = 0; i < (long)I; ++i)
+        for (long j = 0; j < (long)J; ++j)
+            for (size_t k = 0; k < K; ++k)
+                dst[(size_t)i * K * J + k * J + (size_t)j] = src[(size_t)i * J * K + (size_t)j * K + k];
+}
+
 /* util.cl:136-148: C[i] = A[i] + chunk[i / chunk_size] (the time-embedding broadcast add of
  * nn/ResBlock.cpp:188-199, chunk_size = H*W). */
 void oracle_chunkwise_add(const float *A, const float *chunk, float *C, size_t n, size_t chunk_size) {

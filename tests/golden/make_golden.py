@@ -77,6 +77,9 @@ def main() -> None:
     chunk = rng.standard_normal(6).astype(np.float32)
     data["chunk.a"], data["chunk.chunk"] = a, chunk
     data["chunk.y"] = oracle.chunkwise_add(a, chunk, 40, backend="ref")
+    t3 = rng.standard_normal((2, 5, 7)).astype(np.float32)
+    data["permute.x"] = t3
+    data["permute.y"] = oracle.permute_021(t3, backend="ref")
     np.savez_compressed(OUT, **data)
     print(f"wrote {OUT}: {len(data)} arrays, {os.path.getsize(OUT)} bytes")
 

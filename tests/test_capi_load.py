@@ -14,7 +14,7 @@ HEADER = os.path.join(ROOT, "include", "sdfl.h")
 def declared_symbols():
     text = open(HEADER).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b(sdfl_[a-z0-9_]+)\s*\(", text)))
+    return sorted(set(re.findall(r"\b(sdfl_[A-Za-z0-9_]+)\s*\(", text)))
 
 
 def test_header_declares_the_reference_kernel_names():

@@ -54,3 +54,5 @@ def test_geglu_and_activations_match_reference_kernels(golden, oracle_mod):
     assert_bit_equal(oracle_mod.elemwise_add(x, golden["act.other"]), golden["act.add"], "add")
     assert_bit_equal(oracle_mod.chunkwise_add(golden["chunk.a"], golden["chunk.chunk"], 40),
                      golden["chunk.y"], "chunkwise_add")
+    assert_bit_equal(oracle_mod.permute_021(golden["permute.x"]), golden["permute.y"], "permute3D__0_2_1")
+    assert np.array_equal(golden["permute.y"], golden["permute.x"].transpose(0, 2, 1))
