@@ -532,6 +532,21 @@ def op_cases(torch, ops, dev):
     perm("next: permute + residual add f16 [64,4096,320] (large)", 64, 4096, 320, f16, True)
     perm("next: permute3D__0_2_1 f32 [64,1280,1024] (large)", 64, 1280, 1024, f32, False)
 
+    def smax(name, rows, keys, dtype):
+        esz = 2 if dtype == f16 else 4
+
+        def make():
+            x = rnd((rows, keys), dtype, 2.0)
+            y = torch.empty_like(x)
+            return lambda: ops.softmax(x, out=y)
+        cases.append((name, 2 * rows * keys * esz, make, ("softmax", rows, keys)))
+
+    smax("next: softmax f16 cross-attention [2*8*4096, 77]", 2 * 8 * 4096, 77, f16)
+    smax("next: softmax f32 cross-attention [8*4096, 77] (reference dtype)", 8 * 4096, 77, f32)
+    smax("next: softmax f16 self-attention [2*8*1024, 1024]", 2 * 8 * 1024, 1024, f16)
+    smax("next: softmax f16 self-attention [8*4096, 4096] (large)", 8 * 4096, 4096, f16)
+    smax("next: softmax f32 self-attention [8*4096, 4096] (large)", 8 * 4096, 4096, f32)
+
     def ln(name, rows, D, dtype):
         esz = 2 if dtype == f16 else 4
 
@@ -671,6 +686,12 @@ def cpu_reference_case(spec) -> dict:
         else:
             t = timed(lambda: oracle.permute_021(x, backend=backend))
         scale, note = I / i, f"{i} of {I} slices scaled"
+    elif kind == "softmax":
+        _, rows, keys = spec
+        r = min(rows, 4096)
+        x = (rng.standard_normal((r, keys), dtype=np.float32) * 2.0).astype(np.float32)
+        t = timed(lambda: oracle.softmax(x, backend=backend))
+        scale, note = rows / r, f"{r} rows scaled"
     elif kind == "ln":
         _, rows, D = spec
         r = min(rows, 8192)

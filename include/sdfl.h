@@ -163,6 +163,13 @@ int sdfl_permute3D__0_2_1(const void *src, void *dst, int64_t I, int64_t J, int6
 int sdfl_permute_add(const void *src, const void *residual, void *dst, int64_t I, int64_t J, int64_t K,
                      int dtype, void *stream);
 
+/* K/util.cl:150-187 softmax(input, output, __local sums, __local cache, chunkSize) launched with one
+ * work-group per row (NN/CrossAttention.cpp:365-378, NN/AttnBlock.cpp:196-207):
+ * output[r][i] = exp(input[r][i]) / sum_i exp(input[r][i]) over rows of chunk_size elements.
+ * The row maximum is subtracted before exp (same quotient; the reference overflows above 88).
+ * output == input allowed, as the reference's callers do. */
+int sdfl_softmax(const void *input, void *output, int64_t rows, int64_t chunk_size, int dtype, void *stream);
+
 /* K/util.cl:136-148  chunkwise_add(A, chunk, C, chunk_size) over n work-items:
  * C[i] = A[i] + chunk[i / chunk_size]; C may be A (NN/ResBlock.cpp:188-191). */
 int sdfl_chunkwise_add(const void *A, const void *chunk, void *C, int64_t n, int64_t chunk_size,

@@ -230,6 +230,16 @@ int sdfl_permute_add(const void *src, const void *residual, void *dst, int64_t I
     return permute_checked(src, residual, dst, I, J, K, dtype, stream);
 }
 
+int sdfl_softmax(const void *input, void *output, int64_t rows, int64_t chunk_size, int dtype, void *stream) {
+    if (!dtype_ok(dtype) || rows < 0 || chunk_size < 0) return SDFL_ERR_INVALID_VALUE;
+    if (chunk_size >= (1ll << 31)) return SDFL_ERR_UNSUPPORTED;
+    if (rows == 0 || chunk_size == 0) return SDFL_OK;
+    if (!input || !output) return SDFL_ERR_INVALID_POINTER;
+    const int64_t bytes = rows * chunk_size * esize(dtype);
+    if (partial_overlap(input, bytes, output, bytes)) return SDFL_ERR_OVERLAP;
+    return wrap(sdfl::softmax_launch(input, output, rows, chunk_size, dtype, as_stream(stream)));
+}
+
 int sdfl_chunkwise_add(const void *A, const void *chunk, void *C, int64_t n, int64_t chunk_size,
                        int dtype, void *stream) {
     if (!dtype_ok(dtype) || n < 0 || chunk_size <= 0) return SDFL_ERR_INVALID_VALUE;

@@ -103,6 +103,10 @@ cudaError_t act_launch(int act, const void *src, void *dst, int64_t n, int dtype
 cudaError_t add_launch(const void *a, const void *b, void *c, int64_t n, int dtype,
                        cudaStream_t stream);
 // C[i] = A[i] + chunk[i / chunk_size]   (util.cl:136-148)
+// Row softmax over the last dimension of [rows, dim]; out == in allowed.
+cudaError_t softmax_launch(const void *in, void *out, int64_t rows, int64_t dim, int dtype,
+                           cudaStream_t stream);
+
 // dst[i][k][j] = src[i][j][k] (+ res[i][k][j] when res != nullptr): the reference's
 // permute3D__0_2_1, optionally fused with the residual add that follows it.
 cudaError_t permute_021_launch(const void *src, const void *res, void *dst, int64_t I, int64_t J,

@@ -18,7 +18,7 @@ __all__ = [
     "elemwise_add", "token_embedding", "timestep_embedding", "local_reduction_mean",
     "local_reduction_variance", "group_norm_apply", "layer_norm_apply", "device_status",
     "selftest_bounded_wait",
-    "launch_count", "HostPipeline", "GN_AUTO", "GN_RESIDENT", "GN_SPLIT", "GN_REGISTER", "groupnorm_nhwc", "permute_021", "permute_add",
+    "launch_count", "HostPipeline", "GN_AUTO", "GN_RESIDENT", "GN_SPLIT", "GN_REGISTER", "groupnorm_nhwc", "permute_021", "permute_add", "softmax",
 ]
 
 
@@ -177,6 +177,17 @@ def permute_add(src: torch.Tensor, residual: torch.Tensor, out: torch.Tensor | N
     with torch.cuda.device(src.device):
         check(lib.sdfl_permute_add(_dev(src, "src"), _dev(residual, "residual"), _dev(out, "out"), I, J, K,
                                    _dtype_code(src), _stream(stream)), "sdfl_permute_add")
+    return out
+
+
+def softmax(x: torch.Tensor, out: torch.Tensor | None = None, stream=None) -> torch.Tensor:
+    """Softmax over the last dimension (rows = all leading dimensions); out may be x."""
+    out = torch.empty_like(x) if out is None else out
+    dim = x.shape[-1] if x.dim() else 1
+    rows = x.numel() // dim if dim else 0
+    with torch.cuda.device(x.device):
+        check(lib.sdfl_softmax(_dev(x, "x"), _dev(out, "out"), rows, dim, _dtype_code(x), _stream(stream)),
+              "sdfl_softmax")
     return out
 
 

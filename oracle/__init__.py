@@ -72,6 +72,7 @@ def port_lib():
         lib.oracle_elemwise_add.argtypes = [_f32p, _f32p, _f32p, _sz]
         lib.oracle_chunkwise_add.argtypes = [_f32p, _f32p, _f32p, _sz, _sz]
         lib.oracle_permute3D__0_2_1.argtypes = [_f32p, _f32p, _sz, _sz, _sz]
+        lib.oracle_softmax.argtypes = [_f32p, _f32p, _sz, _sz]
         lib.oracle_token_embedding.argtypes = [_i64p, _f32p, _f32p, _f32p, _sz, _sz, _sz, _sz]
         lib.oracle_token_embedding.restype = C.c_int
         lib.oracle_timestep_embedding.argtypes = [_i64p, _f32p, _sz, _sz, C.c_float]
@@ -107,6 +108,7 @@ def ref_lib():
         lib.ref_elemwise_add.argtypes = [_f32p, _f32p, _f32p, _sz]
         lib.ref_chunkwise_add.argtypes = [_f32p, _f32p, _f32p, _sz, _sz]
         lib.ref_permute3D__0_2_1.argtypes = [_f32p, _f32p, _sz, _sz, _sz]
+        lib.ref_softmax.argtypes = [_f32p, _f32p, _sz, _sz]
         _ref = lib
     return _ref
 
@@ -254,6 +256,17 @@ def elemwise_add(a, b, backend: str = "port"):
         ref_lib().ref_elemwise_add(_fp(a), _fp(b), _fp(out), a.size)
     else:
         port_lib().oracle_elemwise_add(_fp(a), _fp(b), _fp(out), a.size)
+    return out
+
+
+def softmax(x, backend: str = "port"):
+    """Row softmax over the last axis, the reference's way (no maximum subtracted)."""
+    x = _c32(x)
+    chunk = x.shape[-1]
+    rows = x.size // chunk if chunk else 0
+    out = np.empty_like(x)
+    fn = ref_lib().ref_softmax if backend == "ref" else port_lib().oracle_softmax
+    fn(_fp(x), _fp(out), rows, chunk)
     return out
 
 

@@ -293,6 +293,15 @@ void gn_var_entry(void *p) {
     auto *a = static_cast<VarArgs *>(p);
     ref_gn::local_reduction_variance(a->in, a->mean, a->out, scratch, a->reductionSize);
 }
+struct SoftmaxArgs { const float *in; float *out; size_t chunkSize; };
+// __local reductionSums[workGroupSize] and cache[chunkSize], as nn/CrossAttention.cpp:367-368 sizes them.
+void softmax_entry(void *p) {
+    static thread_local float sums[WORK_GROUP_SIZE];
+    static thread_local std::vector<float> cache;
+    auto *a = static_cast<SoftmaxArgs *>(p);
+    if (cache.size() < a->chunkSize) cache.resize(a->chunkSize);   // same for every fiber of the group
+    ref_util::softmax(a->in, a->out, sums, cache.data(), a->chunkSize);
+}
 void ln_mean_entry(void *p) {
     static thread_local float scratch[WORK_GROUP_SIZE];
     auto *a = static_cast<MeanArgs *>(p);
@@ -374,6 +383,12 @@ void ref_silu(const float *src, float *dst, size_t n) {
 
 void ref_gelu(const float *src, float *dst, size_t n) {
     enqueue_1d_flat(n, [=] { ref_util::gelu(const_cast<float *>(src), dst); });
+}
+
+// softmax as launched at nn/CrossAttention.cpp:365-378: one work-group of 64 per row of chunkSize.
+void ref_softmax(const float *in, float *out, size_t rows, size_t chunkSize) {
+    SoftmaxArgs a{in, out, chunkSize};
+    enqueue_1d_groups(rows * WORK_GROUP_SIZE, WORK_GROUP_SIZE, softmax_entry, &a);
 }
 
 // permute3D__0_2_1 as launched at nn/SpatialTransformer.cpp:131-134 / :154-157: global size {I, J, K}.

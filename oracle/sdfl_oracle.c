@@ -219,6 +219,41 @@ void oracle_elemwise_add(const float *A, const float *B, float *C, size_t n) {
     for (long i = 0; i < (long)n; ++i) C[i] = A[i] + B[i];
 }
 
+/* util.cl:150-187 softmax with one work-group of 64 items per row (nn/CrossAttention.cpp:360-378):
+ * item l adds exp(x[l]), exp(x[l+64]), ... in that order and keeps each exp in `cache` (:163-169);
+ * the partial sums are folded by the halving loop of :172-180 (for 64 items: offsets 32..1, the
+ * odd-size bookkeeping never triggers); every element is cache[i] / sums[0] (:184-186).  No
+ * maximum is subtracted, as in the reference.  out may be in. */
+void oracle_softmax(const float *in, float *out, size_t rows, size_t chunk) {
+#pragma omp parallel
+    {
+        float *cache = (float *)malloc(sizeof(float) * (chunk ? chunk : 1));
+#pragma omp for schedule(static)
+        for (long r = 0; r < (long)rows; ++r) {
+            const float *x = in + (size_t)r * chunk;
+            float sums[WORK_GROUP_SIZE];
+            for (int l = 0; l < WORK_GROUP_SIZE; ++l) {
+                float sum = 0.0f;
+                for (size_t j = (size_t)l; j < chunk; j += WORK_GROUP_SIZE) {
+                    const float e = expf(x[j]);
+                    sum += e;
+                    cache[j] = e;
+                }
+                sums[l] = sum;
+            }
+            int remainder = WORK_GROUP_SIZE % 2;
+            for (int offset = WORK_GROUP_SIZE / 2; offset > 0; offset /= 2) {
+                for (int l = 0; l < offset; ++l) sums[l + remainder] += sums[l + offset + remainder];
+                offset += remainder;
+                remainder = offset % 2;
+            }
+            float *y = out + (size_t)r * chunk;
+            for (size_t j = 0; j < chunk; ++j) y[j] = cache[j] / sums[0];
+        }
+        free(cache);
+    }
+}
+
 /* util.cl:47-64 permute3D__0_2_1 with global size {I, J, K}: dst[i][k][j] = src[i][j][k]
  * (src_idx = i*J*K + j*K + k, dst_idx = i*K*J + k*J + j).  nn/SpatialTransformer.cpp:131-134
  * runs it with {1, C, HW} after the block's GroupNorm and :154-157 with {1, HW, C} before the

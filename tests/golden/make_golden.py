@@ -80,6 +80,10 @@ def main() -> None:
     t3 = rng.standard_normal((2, 5, 7)).astype(np.float32)
     data["permute.x"] = t3
     data["permute.y"] = oracle.permute_021(t3, backend="ref")
+    for name, shape in (("softmax_r6_c77", (6, 77)), ("softmax_r3_c256", (3, 256))):
+        x = (rng.standard_normal(shape) * 2.0).astype(np.float32)
+        data[f"{name}.x"] = x
+        data[f"{name}.y"] = oracle.softmax(x, backend="ref")
     np.savez_compressed(OUT, **data)
     print(f"wrote {OUT}: {len(data)} arrays, {os.path.getsize(OUT)} bytes")
 

@@ -136,3 +136,26 @@ def test_timestep_embedding_layout_and_values():
     for row, tt in zip(got, t):
         assert np.abs(row[:160] - np.cos(tt * freq)).max() < 2e-4
         assert np.abs(row[160:] - np.sin(tt * freq)).max() < 2e-4
+
+
+@needs_ref
+def test_port_equals_compiled_reference_adjacent_kernels():
+    """chunkwise_add, permute3D__0_2_1 and softmax: the kernels either side of the norms."""
+    rng = rng_for(1, 4242)
+    a = rng.standard_normal((320, 256)).astype(np.float32)
+    e = rng.standard_normal(320).astype(np.float32)
+    assert_bit_equal(oracle.chunkwise_add(a, e, 256, backend="port"),
+                     oracle.chunkwise_add(a, e, 256, backend="ref"), "chunkwise_add")
+    t3 = rng.standard_normal((2, 320, 64)).astype(np.float32)
+    assert_bit_equal(oracle.permute_021(t3, backend="port"), oracle.permute_021(t3, backend="ref"), "permute")
+    for rows, chunk in ((64, 77), (16, 4096), (40, 64), (8, 100)):
+        x = (rng.standard_normal((rows, chunk)) * 3.0).astype(np.float32)
+        assert_bit_equal(oracle.softmax(x, backend="port"), oracle.softmax(x, backend="ref"),
+                         f"softmax {rows}x{chunk}")
+
+
+def test_softmax_against_float64():
+    rng = rng_for(1, 4243)
+    x = (rng.standard_normal((32, 77)) * 4.0).astype(np.float32)
+    e = np.exp(x.astype(np.float64))
+    assert_close(oracle.softmax(x), (e / e.sum(-1, keepdims=True)).astype(np.float32), 1e-5, "softmax vs float64")
