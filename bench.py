@@ -532,6 +532,32 @@ def op_cases(torch, ops, dev):
     perm("next: permute + residual add f16 [64,4096,320] (large)", 64, 4096, 320, f16, True)
     perm("next: permute3D__0_2_1 f32 [64,1280,1024] (large)", 64, 1280, 1024, f32, False)
 
+    def gn_cat(name, B, C1, C2, H, dtype):
+        esz = 2 if dtype == f16 else 4
+
+        def make():
+            a, c = rnd((B, C1, H, H), dtype), rnd((B, C2, H, H), dtype)
+            y = torch.empty((B, C1 + C2, H, H), device=dev, dtype=dtype)
+            g, b = 1 + 0.1 * rnd((C1 + C2,), f32), 0.1 * rnd((C1 + C2,), f32)
+            return lambda: ops.groupnorm_concat(a, c, g, b, 32, 1e-5, True, out=y)
+        cases.append((name, 2 * B * (C1 + C2) * H * H * esz + 2 * (C1 + C2) * 4, make, ("gncat", B, C1, C2, H)))
+
+    gn_cat("next: concat+GN+SiLU f16 [2,640+320,32,32]", 2, 640, 320, 32, f16)
+    gn_cat("next: concat+GN+SiLU f16 [2,320+320,64,64]", 2, 320, 320, 64, f16)
+    gn_cat("next: concat+GN+SiLU f16 [8,128+128,256,256] (large)", 8, 128, 128, 256, f16)
+
+    def ups(name, B, C, H, dtype):
+        esz = 2 if dtype == f16 else 4
+
+        def make():
+            x = rnd((B, C, H, H), dtype)
+            y = torch.empty((B, C, 2 * H, 2 * H), device=dev, dtype=dtype)
+            return lambda: ops.up_sample_nearest(x, 2, out=y)
+        cases.append((name, 5 * B * C * H * H * esz, make, ("ups", B, C, H)))
+
+    ups("next: up_sample_nearest x2 f16 [2,1280,16,16]", 2, 1280, 16, f16)
+    ups("next: up_sample_nearest x2 f16 [8,512,128,128] (large)", 8, 512, 128, f16)
+
     def smax(name, rows, keys, dtype):
         esz = 2 if dtype == f16 else 4
 
@@ -686,6 +712,18 @@ def cpu_reference_case(spec) -> dict:
         else:
             t = timed(lambda: oracle.permute_021(x, backend=backend))
         scale, note = I / i, f"{i} of {I} slices scaled"
+    elif kind == "gncat":
+        _, B, C1, C2, H = spec
+        a = rng.standard_normal((1, C1, H, H), dtype=np.float32)
+        c = rng.standard_normal((1, C2, H, H), dtype=np.float32)
+        g, b = np.ones(C1 + C2, np.float32), np.zeros(C1 + C2, np.float32)
+        t = timed(lambda: oracle.group_norm(oracle.concat_buffer(a, c), g, b, 32, 1e-5, True, backend=backend), reps=2)
+        scale, note = float(B), f"one image x {B}"
+    elif kind == "ups":
+        _, B, C, H = spec
+        x = rng.standard_normal((1, C, H, H), dtype=np.float32)
+        t = timed(lambda: oracle.up_sample_nearest(x, 2, backend=backend))
+        scale, note = float(B), f"one image x {B}"
     elif kind == "softmax":
         _, rows, keys = spec
         r = min(rows, 4096)

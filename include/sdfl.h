@@ -163,6 +163,29 @@ int sdfl_permute3D__0_2_1(const void *src, void *dst, int64_t I, int64_t J, int6
 int sdfl_permute_add(const void *src, const void *residual, void *dst, int64_t I, int64_t J, int64_t K,
                      int dtype, void *stream);
 
+/* K/up_sample.cl:1-18 up_sample_nearest(input, output, scale) with global size {channels, height,
+ * height} (NN/UpSample.cpp:93-102): output[c][i*scale+di][j*scale+dj] = input[c][i][j].  Width
+ * is a separate argument here; a batch is folded into `channels`. */
+int sdfl_up_sample_nearest(const void *input, void *output, int64_t channels, int64_t height, int64_t width,
+                           int64_t scale, int dtype, void *stream);
+
+/* M/UNetModel.cpp:1960-1990 concat_buffer(input1, input2, output): output = input1 followed by
+ * input2.  With batch > 1 each image is [n1 | n2] elements (a concatenation along the channels of
+ * NCHW tensors with n = channels * hw). */
+int sdfl_concat_buffer(const void *input1, const void *input2, void *output, int64_t batch, int64_t n1,
+                       int64_t n2, int dtype, void *stream);
+
+/* GroupNorm(+SiLU) of the channel-wise concatenation of in1 [batch, channels1, hw] and in2
+ * [batch, channels2, hw] without materialising it: concat_buffer (M/UNetModel.cpp:1960-1990) in
+ * front of the first norm of an output-block ResBlock, fused into the norm's loads.  out is
+ * [batch, channels1 + channels2, hw].  gamma/beta have channels1 + channels2 entries.  Falls back
+ * to concat + in-place norm when the tensors are not 16-byte aligned or hw * element size is not
+ * a multiple of 16.  Workspace as for sdfl_groupnorm_forward with the summed channel count. */
+int sdfl_groupnorm_concat_forward(const void *in1, int64_t channels1, const void *in2, int64_t channels2,
+                                  void *out, const float *gamma, const float *beta, int64_t batch,
+                                  int64_t hw, int64_t num_groups, float eps, int fuse_silu, int dtype,
+                                  void *workspace, size_t workspace_bytes, void *stream);
+
 /* K/util.cl:150-187 softmax(input, output, __local sums, __local cache, chunkSize) launched with one
  * work-group per row (NN/CrossAttention.cpp:365-378, NN/AttnBlock.cpp:196-207):
  * output[r][i] = exp(input[r][i]) / sum_i exp(input[r][i]) over rows of chunk_size elements.

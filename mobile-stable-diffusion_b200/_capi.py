@@ -55,6 +55,9 @@ SIGNATURES = {
     "sdfl_groupnorm_nhwc_forward": (_i, [_p, _p, _p, _p, _i64, _i64, _i64, _i64, _f, _i, _i, _p, _sz, _p]),
     "sdfl_permute3D__0_2_1": (_i, [_p, _p, _i64, _i64, _i64, _i, _p]),
     "sdfl_permute_add": (_i, [_p, _p, _p, _i64, _i64, _i64, _i, _p]),
+    "sdfl_up_sample_nearest": (_i, [_p, _p, _i64, _i64, _i64, _i64, _i, _p]),
+    "sdfl_concat_buffer": (_i, [_p, _p, _p, _i64, _i64, _i64, _i, _p]),
+    "sdfl_groupnorm_concat_forward": (_i, [_p, _i64, _p, _i64, _p, _p, _p, _i64, _i64, _i64, _f, _i, _i, _p, _sz, _p]),
     "sdfl_softmax": (_i, [_p, _p, _i64, _i64, _i, _p]),
     "sdfl_chunkwise_add": (_i, [_p, _p, _p, _i64, _i64, _i, _p]),
     "sdfl_groupnorm_plan": (_i, [_i64, _i64, _i64, _i64, _i, _i, _i, C.POINTER(_i64)]),

@@ -230,6 +230,60 @@ int sdfl_permute_add(const void *src, const void *residual, void *dst, int64_t I
     return permute_checked(src, residual, dst, I, J, K, dtype, stream);
 }
 
+int sdfl_up_sample_nearest(const void *input, void *output, int64_t channels, int64_t height, int64_t width,
+                           int64_t scale, int dtype, void *stream) {
+    if (!dtype_ok(dtype) || channels < 0 || height < 0 || width < 0 || scale < 1) return SDFL_ERR_INVALID_VALUE;
+    if (height >= (1ll << 31) / scale || width >= (1ll << 31) / scale) return SDFL_ERR_UNSUPPORTED;
+    if (channels == 0 || height == 0 || width == 0) return SDFL_OK;
+    if (!input || !output) return SDFL_ERR_INVALID_POINTER;
+    const int64_t ib = channels * height * width * esize(dtype);
+    if (input == output || partial_overlap(input, ib, output, ib * scale * scale)) return SDFL_ERR_OVERLAP;
+    return wrap(sdfl::upsample_nearest_launch(input, output, channels, height, width, scale, dtype, as_stream(stream)));
+}
+
+int sdfl_concat_buffer(const void *input1, const void *input2, void *output, int64_t batch, int64_t n1,
+                       int64_t n2, int dtype, void *stream) {
+    if (!dtype_ok(dtype) || batch < 0 || n1 < 0 || n2 < 0) return SDFL_ERR_INVALID_VALUE;
+    if (batch == 0 || n1 + n2 == 0) return SDFL_OK;
+    if ((n1 && !input1) || (n2 && !input2) || !output) return SDFL_ERR_INVALID_POINTER;
+    const int64_t ob = batch * (n1 + n2) * esize(dtype);
+    if ((n1 && partial_overlap(input1, batch * n1 * esize(dtype), output, ob)) || input1 == output ||
+        (n2 && partial_overlap(input2, batch * n2 * esize(dtype), output, ob)) || input2 == output)
+        return SDFL_ERR_OVERLAP;
+    return wrap(sdfl::concat_launch(input1, input2, output, batch, n1, n2, dtype, as_stream(stream)));
+}
+
+int sdfl_groupnorm_concat_forward(const void *in1, int64_t channels1, const void *in2, int64_t channels2,
+                                  void *out, const float *gamma, const float *beta, int64_t batch,
+                                  int64_t hw, int64_t num_groups, float eps, int fuse_silu, int dtype,
+                                  void *workspace, size_t workspace_bytes, void *stream) {
+    if (channels1 <= 0 || channels2 <= 0) return SDFL_ERR_INVALID_VALUE;
+    const int64_t channels = channels1 + channels2;
+    // shape checks on the concatenated tensor (in1 is smaller than that: its own overlap test follows)
+    int rc = gn_validate(out, out, gamma, beta, batch, channels, hw, num_groups, eps, dtype);
+    if (rc != SDFL_OK) return rc;
+    if (batch == 0 || hw == 0) return SDFL_OK;
+    if (!in1 || !in2) return SDFL_ERR_INVALID_POINTER;
+    const int64_t ob = batch * channels * hw * esize(dtype);
+    if (in1 == out || in2 == out || partial_overlap(in1, batch * channels1 * hw * esize(dtype), out, ob) ||
+        partial_overlap(in2, batch * channels2 * hw * esize(dtype), out, ob))
+        return SDFL_ERR_OVERLAP;
+    sdfl::GnShape s{batch, channels, hw, num_groups, dtype, eps,
+                    fuse_silu ? sdfl::kActSilu : sdfl::kActNone};
+    sdfl::GnPlan plan;
+    cudaError_t e = sdfl::gn_make_plan(s, in1, out, SDFL_GN_AUTO, 0, &plan);
+    if (e == cudaErrorInvalidConfiguration || e == cudaErrorInvalidValue) return SDFL_ERR_UNSUPPORTED;
+    if (e != cudaSuccess) return cuda_fail(e);
+    if (sdfl::gn_concat_fused_ok(s, plan, in1, in2, channels1))
+        return wrap(sdfl::gn_launch(s, plan, in1, out, gamma, beta, workspace, as_stream(stream), nullptr, in2,
+                                    channels1));
+    // otherwise: the reference's two copies into `out`, then the norm in place
+    rc = sdfl_concat_buffer(in1, in2, out, batch, channels1 * hw, channels2 * hw, dtype, stream);
+    if (rc != SDFL_OK) return rc;
+    return gn_forward(out, out, gamma, beta, batch, channels, hw, num_groups, eps, fuse_silu, dtype, workspace,
+                      workspace_bytes, SDFL_GN_AUTO, 0, as_stream(stream));
+}
+
 int sdfl_softmax(const void *input, void *output, int64_t rows, int64_t chunk_size, int dtype, void *stream) {
     if (!dtype_ok(dtype) || rows < 0 || chunk_size < 0) return SDFL_ERR_INVALID_VALUE;
     if (chunk_size >= (1ll << 31)) return SDFL_ERR_UNSUPPORTED;

@@ -349,6 +349,10 @@ struct ResidentArgs {
     uint32_t hw_vecs;      // hw / lanes-per-vector (when vec_uniform)
     uint32_t channels;     // C (row length of `bias`)
     const void *bias;      // [batch, C] addend of the storage type, or nullptr
+    // Input given as two tensors concatenated along the channels (in: [B, c1, hw], in2: [B, C - c1, hw]):
+    // the skip-connection concat in front of a ResBlock's first norm (UNetModel.cpp:1960-1990).
+    const void *in2;       // nullptr: `in` is the whole [B, C, hw] tensor
+    uint32_t c1;
     float eps;
     FastDiv hw_div;        // element offset -> channel
     FastDiv hwv_div;       // vector offset -> channel (when vec_uniform)
@@ -431,15 +435,37 @@ gn_resident_kernel(const ResidentArgs a) {
                                        timed_out ? kWaitCyclesAfterTimeout : kWaitCycles))
                     timed_out = true;
             }
-            const unsigned char *gsrc = static_cast<const unsigned char *>(a.in) +
-                                        (static_cast<size_t>(unit) * a.slab_vecs + v0) * 16u;
             const uint32_t lo = j * cv;
             const uint32_t bytes = (min(nv, lo + cv) - lo) * 16u;
             const uint32_t bar = smem_addr(&full[slot]);
+            const uint64_t policy = (l < P && j + H < P) ? keep : drop;
             mbar_expect_tx(bar, bytes);
             // a chunk that will be read a second time should stay in L2; a last read need not
-            bulk_load_hint(smem_addr(data + slot * chunk_bytes), gsrc + lo * 16u, bytes, bar,
-                           (l < P && j + H < P) ? keep : drop);
+            if (a.in2 == nullptr) {
+                const unsigned char *gsrc = static_cast<const unsigned char *>(a.in) +
+                                            (static_cast<size_t>(unit) * a.slab_vecs + v0) * 16u;
+                bulk_load_hint(smem_addr(data + slot * chunk_bytes), gsrc + lo * 16u, bytes, bar, policy);
+            } else {
+                // the slab's first k1 channels come from `in`, the rest from `in2`: the chunk
+                // [b0, b1) of the slab (in bytes) is one or two bulk copies
+                const uint32_t n = unit / a.groups, c_first = (unit % a.groups) * a.cpg;
+                const uint32_t k1 = c_first >= a.c1 ? 0u : min(a.cpg, a.c1 - c_first);
+                const size_t row = static_cast<size_t>(a.hw_vecs) * 16u;            // bytes of one channel
+                const size_t split = k1 * row;
+                const size_t b0 = (static_cast<size_t>(v0) + lo) * 16u, b1 = b0 + bytes;
+                const unsigned char *s1 = static_cast<const unsigned char *>(a.in) +
+                                          (static_cast<size_t>(n) * a.c1 + c_first) * row;
+                const unsigned char *s2 = static_cast<const unsigned char *>(a.in2) +
+                                          (static_cast<size_t>(n) * (a.channels - a.c1) + (max(c_first, a.c1) - a.c1)) * row;
+                const uint32_t dst = smem_addr(data + slot * chunk_bytes);
+                if (b0 < split) {
+                    const uint32_t part = static_cast<uint32_t>(min(b1, split) - b0);
+                    bulk_load_hint(dst, s1 + b0, part, bar, policy);
+                    if (b1 > split) bulk_load_hint(dst + part, s2, static_cast<uint32_t>(b1 - split), bar, policy);
+                } else {
+                    bulk_load_hint(dst, s2 + (b0 - split), bytes, bar, policy);
+                }
+            }
             if (++slot == S) { slot = 0; ++round; }
             if (++l == loads_per_slab) { l = 0; unit += nclusters; }
             return true;
@@ -728,6 +754,9 @@ struct RegArgs {
     uint32_t row_bytes;    // shared-memory stride of one channel's pixels: hw * sizeof(T) rounded up to 4, plus 4
     uint32_t pair;         // fp16 and an even number of channels per group: two channels per store
     FastDiv out_div;       // output index within the slab -> pixel (divides by cpg, or cpg / 2 when pair)
+    // input as two tensors concatenated along the channels (see ResidentArgs); needs vec_uniform
+    const void *in2;
+    uint32_t c1;
 };
 
 // NHWC: the result is written channels-last, out[n][p][c] (the permute3D__0_2_1 that follows the
@@ -748,11 +777,22 @@ gn_register_kernel(const RegArgs a) {
         const T *erow = BIAS ? static_cast<const T *>(a.bias) +
                                    static_cast<size_t>(unit / a.groups) * a.channels + (unit % a.groups) * a.cpg
                              : nullptr;
+        // two-source input: vectors [0, split) of the slab come from `in`, the rest from `in2`
+        const uint4 *src2 = src;
+        uint32_t split = 0xffffffffu;
+        if (a.in2 != nullptr) {
+            const uint32_t n = unit / a.groups, c_first = (unit % a.groups) * a.cpg;
+            const uint32_t k1 = c_first >= a.c1 ? 0u : min(a.cpg, a.c1 - c_first);
+            split = k1 * a.hw_vecs;
+            src = reinterpret_cast<const uint4 *>(a.in) + (static_cast<size_t>(n) * a.c1 + c_first) * a.hw_vecs;
+            src2 = reinterpret_cast<const uint4 *>(a.in2) +
+                   (static_cast<size_t>(n) * (a.channels - a.c1) + (max(c_first, a.c1) - a.c1)) * a.hw_vecs - split;
+        }
         uint4 v[NVT];
 #pragma unroll
         for (int k = 0; k < NVT; ++k) {
             const uint32_t idx = tid + k * kRegThreads;
-            if (idx < a.slab_vecs) v[k] = ld_stream(src + idx);
+            if (idx < a.slab_vecs) v[k] = ld_stream((idx < split ? src : src2) + idx);
         }
         // this thread's moments, shifted by its first value
         float s[2] = {0.f, 0.f}, q[2] = {0.f, 0.f};
@@ -1450,9 +1490,15 @@ cudaError_t gn_make_plan(const GnShape &s, const void *in, const void *out, int 
     return cudaSuccess;
 }
 
+bool gn_concat_fused_ok(const GnShape &s, const GnPlan &plan, const void *in1, const void *in2, int64_t c1) {
+    const int64_t esz = s.dtype == kF16 ? 2 : 4;
+    return (plan.path == kGnResident || plan.path == kGnRegister) && !plan.nhwc && aligned16(in1) &&
+           aligned16(in2) && (s.hw * esz) % 16 == 0 && c1 > 0 && c1 < s.channels;
+}
+
 cudaError_t gn_launch(const GnShape &s, const GnPlan &plan, const void *in, void *out,
                       const float *w, const float *b, void *workspace, cudaStream_t stream,
-                      const void *bias) {
+                      const void *bias, const void *in2, int64_t c1) {
     const int64_t esz = s.dtype == kF16 ? 2 : 4;
     const int64_t vec = 16 / esz;
     const int64_t cpg = s.channels / s.groups;
@@ -1478,6 +1524,9 @@ cudaError_t gn_launch(const GnShape &s, const GnPlan &plan, const void *in, void
         a.row_bytes = static_cast<uint32_t>(gn_nhwc_row_bytes(s));
         a.pair = s.dtype == kF16 && cpg % 2 == 0;
         a.out_div = FastDiv::make(static_cast<uint32_t>(a.pair ? cpg / 2 : cpg));
+        a.in2 = in2;
+        a.c1 = static_cast<uint32_t>(c1);
+        if (in2 != nullptr && !gn_concat_fused_ok(s, plan, in, in2, c1)) return cudaErrorInvalidValue;
         const bool nhwc = plan.nhwc != 0;
         if (s.dtype == kF16)
             return s.act == kActSilu ? launch_register<__half, kActSilu>(a, nhwc, stream)
@@ -1499,6 +1548,9 @@ cudaError_t gn_launch(const GnShape &s, const GnPlan &plan, const void *in, void
         a.hold = static_cast<uint32_t>(plan.hold);
         a.channels = static_cast<uint32_t>(s.channels);
         a.bias = bias;
+        a.in2 = in2;
+        a.c1 = static_cast<uint32_t>(c1);
+        if (in2 != nullptr && !gn_concat_fused_ok(s, plan, in, in2, c1)) return cudaErrorInvalidValue;
         a.vec_uniform = s.hw % vec == 0;
         a.hw_vecs = a.vec_uniform ? static_cast<uint32_t>(s.hw / vec) : 1u;
         a.eps = s.eps;
@@ -1511,7 +1563,7 @@ cudaError_t gn_launch(const GnShape &s, const GnPlan &plan, const void *in, void
                                  : launch_resident<float, kActNone>(a, plan, stream);
     }
 
-    if (workspace == nullptr) return cudaErrorInvalidValue;
+    if (workspace == nullptr || in2 != nullptr) return cudaErrorInvalidValue;
     SplitArgs a;
     a.in = in; a.out = out; a.w = w; a.b = b;
     a.partial = static_cast<float *>(workspace);

@@ -55,9 +55,18 @@ bool gn_nhwc_fused_ok(const GnShape &s, const void *in, const void *out);
 int64_t gn_nhwc_row_bytes(const GnShape &s);
 
 // bias: optional [batch, channels] addend of the storage type, applied before the statistics.
+// in2 / c1: the input is given as two tensors to be concatenated along the channels,
+// in = [batch, c1, hw] and in2 = [batch, channels - c1, hw] (only where gn_concat_fused_ok).
 cudaError_t gn_launch(const GnShape &s, const GnPlan &plan, const void *in, void *out,
                       const float *w, const float *b, void *workspace, cudaStream_t stream,
-                      const void *bias = nullptr);
+                      const void *bias = nullptr, const void *in2 = nullptr, int64_t c1 = 0);
+bool gn_concat_fused_ok(const GnShape &s, const GnPlan &plan, const void *in1, const void *in2, int64_t c1);
+
+// up_sample_nearest over `planes` images of H x W; concat of two [batch, n1] / [batch, n2] blocks.
+cudaError_t upsample_nearest_launch(const void *in, void *out, int64_t planes, int64_t H, int64_t W,
+                                    int64_t scale, int dtype, cudaStream_t stream);
+cudaError_t concat_launch(const void *in1, const void *in2, void *out, int64_t batch, int64_t n1,
+                          int64_t n2, int dtype, cudaStream_t stream);
 
 // The split path with its scratch in a fixed array inside the library (64 KiB per device: up to
 // 8192 (mean, M2) pairs, i.e. batch * groups * chunks-per-slab <= 8192).  Allocates nothing; the

@@ -18,7 +18,7 @@ __all__ = [
     "elemwise_add", "token_embedding", "timestep_embedding", "local_reduction_mean",
     "local_reduction_variance", "group_norm_apply", "layer_norm_apply", "device_status",
     "selftest_bounded_wait",
-    "launch_count", "HostPipeline", "GN_AUTO", "GN_RESIDENT", "GN_SPLIT", "GN_REGISTER", "groupnorm_nhwc", "permute_021", "permute_add", "softmax",
+    "launch_count", "HostPipeline", "GN_AUTO", "GN_RESIDENT", "GN_SPLIT", "GN_REGISTER", "groupnorm_nhwc", "permute_021", "permute_add", "softmax", "up_sample_nearest", "concat_channels", "groupnorm_concat",
 ]
 
 
@@ -177,6 +177,45 @@ def permute_add(src: torch.Tensor, residual: torch.Tensor, out: torch.Tensor | N
     with torch.cuda.device(src.device):
         check(lib.sdfl_permute_add(_dev(src, "src"), _dev(residual, "residual"), _dev(out, "out"), I, J, K,
                                    _dtype_code(src), _stream(stream)), "sdfl_permute_add")
+    return out
+
+
+def up_sample_nearest(x: torch.Tensor, scale: int = 2, out: torch.Tensor | None = None, stream=None) -> torch.Tensor:
+    """[..., H, W] -> [..., H*scale, W*scale], every element repeated scale x scale times."""
+    H, W = x.shape[-2], x.shape[-1]
+    planes = x.numel() // (H * W) if H * W else 0
+    out = torch.empty((*x.shape[:-2], H * scale, W * scale), dtype=x.dtype, device=x.device) if out is None else out
+    with torch.cuda.device(x.device):
+        check(lib.sdfl_up_sample_nearest(_dev(x, "x"), _dev(out, "out"), planes, H, W, scale, _dtype_code(x),
+                                         _stream(stream)), "sdfl_up_sample_nearest")
+    return out
+
+
+def concat_channels(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, stream=None) -> torch.Tensor:
+    """[B, C1, ...] and [B, C2, ...] -> [B, C1 + C2, ...] (the reference's concat_buffer per image)."""
+    B = a.shape[0]
+    n1, n2 = (a.numel() // B, b.numel() // B) if B else (0, 0)
+    out = torch.empty((B, a.shape[1] + b.shape[1], *a.shape[2:]), dtype=a.dtype, device=a.device) if out is None else out
+    with torch.cuda.device(a.device):
+        check(lib.sdfl_concat_buffer(_dev(a, "a"), _dev(b, "b"), _dev(out, "out"), B, n1, n2, _dtype_code(a),
+                                     _stream(stream)), "sdfl_concat_buffer")
+    return out
+
+
+def groupnorm_concat(a: torch.Tensor, b: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor,
+                     num_groups: int, eps: float = 1e-5, silu: bool = False,
+                     out: torch.Tensor | None = None, stream=None) -> torch.Tensor:
+    """act(GroupNorm(cat([a, b], dim=1))) without materialising the concatenation."""
+    B, C1, C2 = a.shape[0], a.shape[1], b.shape[1]
+    hw = a.numel() // (B * C1) if B * C1 else 0
+    out = torch.empty((B, C1 + C2, *a.shape[2:]), dtype=a.dtype, device=a.device) if out is None else out
+    code = _dtype_code(a)
+    ws = _workspace(a.device, lib.sdfl_groupnorm_workspace_bytes(B, C1 + C2, hw, num_groups, code))
+    with torch.cuda.device(a.device):
+        check(lib.sdfl_groupnorm_concat_forward(
+            _dev(a, "a"), C1, _dev(b, "b"), C2, _dev(out, "out"), _f32(gamma, "gamma"), _f32(beta, "beta"),
+            B, hw, num_groups, eps, int(silu), code, ws.data_ptr(), ws.numel(), _stream(stream)),
+            "sdfl_groupnorm_concat_forward")
     return out
 
 

@@ -73,6 +73,7 @@ def port_lib():
         lib.oracle_chunkwise_add.argtypes = [_f32p, _f32p, _f32p, _sz, _sz]
         lib.oracle_permute3D__0_2_1.argtypes = [_f32p, _f32p, _sz, _sz, _sz]
         lib.oracle_softmax.argtypes = [_f32p, _f32p, _sz, _sz]
+        lib.oracle_up_sample_nearest.argtypes = [_f32p, _f32p, _sz, _sz, _sz, _sz]
         lib.oracle_token_embedding.argtypes = [_i64p, _f32p, _f32p, _f32p, _sz, _sz, _sz, _sz]
         lib.oracle_token_embedding.restype = C.c_int
         lib.oracle_timestep_embedding.argtypes = [_i64p, _f32p, _sz, _sz, C.c_float]
@@ -109,6 +110,7 @@ def ref_lib():
         lib.ref_chunkwise_add.argtypes = [_f32p, _f32p, _f32p, _sz, _sz]
         lib.ref_permute3D__0_2_1.argtypes = [_f32p, _f32p, _sz, _sz, _sz]
         lib.ref_softmax.argtypes = [_f32p, _f32p, _sz, _sz]
+        lib.ref_up_sample_nearest.argtypes = [_f32p, _f32p, _sz, _sz, _sz]
         _ref = lib
     return _ref
 
@@ -257,6 +259,27 @@ def elemwise_add(a, b, backend: str = "port"):
     else:
         port_lib().oracle_elemwise_add(_fp(a), _fp(b), _fp(out), a.size)
     return out
+
+
+def up_sample_nearest(x, scale: int = 2, backend: str = "port"):
+    """[..., H, W] -> [..., H*scale, W*scale]; the compiled reference kernel takes square planes only."""
+    x = _c32(x)
+    H, W = x.shape[-2], x.shape[-1]
+    planes = x.size // (H * W) if H * W else 0
+    out = np.empty((*x.shape[:-2], H * scale, W * scale), np.float32)
+    if backend == "ref":
+        if H != W:
+            raise ValueError("the reference's up_sample_nearest indexes square planes (up_sample.cl:9-10)")
+        ref_lib().ref_up_sample_nearest(_fp(x), _fp(out), planes, H, scale)
+    else:
+        port_lib().oracle_up_sample_nearest(_fp(x), _fp(out), planes, H, W, scale)
+    return out
+
+
+def concat_buffer(a, b):
+    """UNetModel::concat_buffer (UNetModel.cpp:1960-1990): two buffer copies, a then b.  For a batch
+    that is the per-image concatenation along axis 1."""
+    return np.ascontiguousarray(np.concatenate([_c32(a), _c32(b)], axis=1))
 
 
 def softmax(x, backend: str = "port"):

@@ -46,6 +46,9 @@ namespace ref_geglu {
 namespace ref_util {
 #include "util.cl"
 }
+namespace ref_up {
+#include "up_sample.cl"
+}
 #pragma GCC diagnostic pop
 
 // ----------------------------------------------------------------------------------------
@@ -383,6 +386,12 @@ void ref_silu(const float *src, float *dst, size_t n) {
 
 void ref_gelu(const float *src, float *dst, size_t n) {
     enqueue_1d_flat(n, [=] { ref_util::gelu(const_cast<float *>(src), dst); });
+}
+
+// up_sample_nearest as launched at nn/UpSample.cpp:93-102: global size {channels, height, height}.
+void ref_up_sample_nearest(const float *in, float *out, size_t channels, size_t height, size_t scale) {
+    enqueue_3d_flat(channels, height, height,
+                    [=] { ref_up::up_sample_nearest(const_cast<float *>(in), out, scale); });
 }
 
 // softmax as launched at nn/CrossAttention.cpp:365-378: one work-group of 64 per row of chunkSize.

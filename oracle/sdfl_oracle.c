@@ -219,6 +219,20 @@ void oracle_elemwise_add(const float *A, const float *B, float *C, size_t n) {
     for (long i = 0; i < (long)n; ++i) C[i] = A[i] + B[i];
 }
 
+/* up_sample.cl:1-18 with global size {channels, H, H} (nn/UpSample.cpp:93-102), generalised to
+ * H x W planes: out[c][i*scale + di][j*scale + dj] = in[c][i][j] for di, dj < scale. */
+void oracle_up_sample_nearest(const float *in, float *out, size_t channels, size_t H, size_t W, size_t scale) {
+#pragma omp parallel for schedule(static) collapse(2)
+    for (long c = 0; c < (long)channels; ++c)
+        for (long i = 0; i < (long)H; ++i)
+            for (size_t j = 0; j < W; ++j) {
+                const float v = in[((size_t)c * H + (size_t)i) * W + j];
+                for (size_t di = 0; di < scale; ++di)
+                    for (size_t dj = 0; dj < scale; ++dj)
+                        out[((size_t)c * scale * H + ((size_t)i * scale + di)) * scale * W + (j * scale + dj)] = v;
+            }
+}
+
 /* util.cl:150-187 softmax with one work-group of 64 items per row (nn/CrossAttention.cpp:360-378):
  * item l adds exp(x[l]), exp(x[l+64]), ... in that order and keeps each exp in `cache` (:163-169);
  * the partial sums are folded by the halving loop of :172-180 (for 64 items: offsets 32..1, the

@@ -80,6 +80,9 @@ def main() -> None:
     t3 = rng.standard_normal((2, 5, 7)).astype(np.float32)
     data["permute.x"] = t3
     data["permute.y"] = oracle.permute_021(t3, backend="ref")
+    up = rng.standard_normal((3, 6, 6)).astype(np.float32)
+    data["upsample.x"] = up
+    data["upsample.y"] = oracle.up_sample_nearest(up, 2, backend="ref")
     for name, shape in (("softmax_r6_c77", (6, 77)), ("softmax_r3_c256", (3, 256))):
         x = (rng.standard_normal(shape) * 2.0).astype(np.float32)
         data[f"{name}.x"] = x

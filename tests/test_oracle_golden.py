@@ -56,6 +56,8 @@ def test_geglu_and_activations_match_reference_kernels(golden, oracle_mod):
                      golden["chunk.y"], "chunkwise_add")
     assert_bit_equal(oracle_mod.permute_021(golden["permute.x"]), golden["permute.y"], "permute3D__0_2_1")
     assert np.array_equal(golden["permute.y"], golden["permute.x"].transpose(0, 2, 1))
+    assert_bit_equal(oracle_mod.up_sample_nearest(golden["upsample.x"], 2), golden["upsample.y"], "up_sample_nearest")
+    assert np.array_equal(golden["upsample.y"], golden["upsample.x"].repeat(2, axis=1).repeat(2, axis=2))
     for name in ("softmax_r6_c77", "softmax_r3_c256"):
         assert_bit_equal(oracle_mod.softmax(golden[f"{name}.x"]), golden[f"{name}.y"], name)
         np.testing.assert_allclose(golden[f"{name}.y"].sum(-1), 1.0, rtol=1e-6)
