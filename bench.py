@@ -456,7 +456,7 @@ def run_ours(args) -> None:
 # per-kernel table (--ops) and single cases for profiling (--case NAME)
 # ---------------------------------------------------------------------------------------------
 def op_cases(torch, ops, dev):
-    """Every kernel of the path at the workload's named shapes (BASELINE configs 1-5).
+    """Every kernel of the path at the shapes of the five named workload configurations.
     Each case: name, algorithmic bytes, a factory and a spec for the CPU leg.  The factory
     allocates one set of buffers and returns a closure that enqueues one launch on them, so
     the caller can build a ring of buffer sets larger than L2."""

@@ -33,10 +33,12 @@ template <> struct LnVec<float> {
         q[0] = fmaf(d0, d0, q[0]); q[1] = fmaf(d1, d1, q[1]);
         q[0] = fmaf(d2, d2, q[0]); q[1] = fmaf(d3, d3, q[1]);
     }
-    static __device__ __forceinline__ uint4 norm(const uint4 &v, float mean, float rstd,
-                                                 const float *w, const float *b) {
-        const float4 ww = *reinterpret_cast<const float4 *>(w);
-        const float4 bb = *reinterpret_cast<const float4 *>(b);
+    struct WB { float4 ww, bb; };
+    static __device__ __forceinline__ WB load_wb(const float *w, const float *b) {
+        return WB{*reinterpret_cast<const float4 *>(w), *reinterpret_cast<const float4 *>(b)};
+    }
+    static __device__ __forceinline__ uint4 norm(const uint4 &v, float mean, float rstd, const WB &k) {
+        const float4 ww = k.ww, bb = k.bb;
         uint4 o;
         o.x = __float_as_uint(fmaf((__uint_as_float(v.x) - mean) * rstd, ww.x, bb.x));
         o.y = __float_as_uint(fmaf((__uint_as_float(v.y) - mean) * rstd, ww.y, bb.y));
@@ -72,12 +74,13 @@ template <> struct LnVec<__half> {
         ln_sq_half2(v.x, mean, q); ln_sq_half2(v.y, mean, q);
         ln_sq_half2(v.z, mean, q); ln_sq_half2(v.w, mean, q);
     }
-    static __device__ __forceinline__ uint4 norm(const uint4 &v, float mean, float rstd,
-                                                 const float *w, const float *b) {
-        const float4 w0 = *reinterpret_cast<const float4 *>(w);
-        const float4 w1 = *(reinterpret_cast<const float4 *>(w) + 1);
-        const float4 b0 = *reinterpret_cast<const float4 *>(b);
-        const float4 b1 = *(reinterpret_cast<const float4 *>(b) + 1);
+    struct WB { float4 w0, w1, b0, b1; };
+    static __device__ __forceinline__ WB load_wb(const float *w, const float *b) {
+        return WB{*reinterpret_cast<const float4 *>(w), *(reinterpret_cast<const float4 *>(w) + 1),
+                  *reinterpret_cast<const float4 *>(b), *(reinterpret_cast<const float4 *>(b) + 1)};
+    }
+    static __device__ __forceinline__ uint4 norm(const uint4 &v, float mean, float rstd, const WB &k) {
+        const float4 w0 = k.w0, w1 = k.w1, b0 = k.b0, b1 = k.b1;
         float d[8];
         ln_center_half2(v.x, mean, d[0], d[1]);
         ln_center_half2(v.y, mean, d[2], d[3]);
@@ -95,6 +98,13 @@ template <> struct LnVec<__half> {
 
 // Register budget: the more row vectors a lane holds, the fewer CTAs share an SM.
 constexpr int ln_min_blocks(int maxv) { return maxv <= 3 ? 6 : maxv <= 6 ? 4 : maxv <= 8 ? 3 : 2; }
+// Rows a warp takes per iteration: two while the row vectors of both still fit the registers, so
+// that every shared-memory load of scale / shift serves two rows (those loads, four times the
+// bytes of an fp16 row, made the L1 / shared-memory pipe the kernel's limit at 84 %).
+// (Used for plain LayerNorm with enough rows to fill the SMs; the add variant keeps one row.)
+constexpr int ln_min_blocks_r(int maxv, int rows_per_warp) {
+    return rows_per_warp == 2 ? (ln_min_blocks(2 * maxv) > 4 ? 4 : ln_min_blocks(2 * maxv)) : ln_min_blocks(maxv);
+}
 
 // One warp per row; lane l keeps vectors l, l+32, ... of the row in registers, so the mean,
 // the exact two-pass variance and the normalised write cost one read and one write of the row.
@@ -106,8 +116,8 @@ constexpr int ln_min_blocks(int maxv) { return maxv <= 3 ? 6 : maxv <= 6 ? 4 : m
 // Scale and shift are fp32 (2 x 4 bytes per element against 2 bytes of fp16 data): read through
 // L1 for every row they saturate the L1 data path, so each CTA first copies them to shared
 // memory (dynamic, 2 * dim floats) and every row reads them from there.
-template <typename T, int MAXV, bool ADD>
-__global__ void __launch_bounds__(kLnThreads, ln_min_blocks(MAXV))
+template <typename T, int MAXV, bool ADD, int R>
+__global__ void __launch_bounds__(kLnThreads, ln_min_blocks_r(MAXV, R))
 ln_warp_kernel(const T *in, const T *in2, T *sum_out, T *out, const float *__restrict__ gw,
                const float *__restrict__ gb, long long rows, int nvec, int dim, float eps) {
     constexpr int VEC = VecOf<T>::N;
@@ -122,41 +132,57 @@ ln_warp_kernel(const T *in, const T *in2, T *sum_out, T *out, const float *__res
     const long long warp0 = static_cast<long long>(blockIdx.x) * kLnWarps + (threadIdx.x >> 5);
     const long long nwarps = static_cast<long long>(gridDim.x) * kLnWarps;
     const float inv_d = 1.0f / static_cast<float>(dim);
-    for (long long row = warp0; row < rows; row += nwarps) {
-        const uint4 *xr = reinterpret_cast<const uint4 *>(in + row * dim);
-        uint4 *yr = reinterpret_cast<uint4 *>(out + row * dim);
-        uint4 v[MAXV];
+    for (long long row0 = warp0 * R; row0 < rows; row0 += nwarps * R) {
+        uint4 v[R][MAXV];
+        float mean[R], rstd[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const long long row = row0 + r;
+            if (row >= rows) break;
+            const uint4 *xr = reinterpret_cast<const uint4 *>(in + row * dim);
+#pragma unroll
+            for (int i = 0; i < MAXV; ++i) {
+                const int idx = lane + 32 * i;
+                if (idx < nvec) {
+                    v[r][i] = ld_stream(xr + idx);
+                    if (ADD) {
+                        float fa[VEC], fb[VEC];
+                        unpack<T>(v[r][i], fa);
+                        unpack<T>(ld_stream(reinterpret_cast<const uint4 *>(in2 + row * dim) + idx), fb);
+#pragma unroll
+                        for (int j = 0; j < VEC; ++j) fa[j] += fb[j];
+                        v[r][i] = pack<T>(fa);
+                        st_stream(reinterpret_cast<uint4 *>(sum_out + row * dim) + idx, v[r][i]);
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            if (row0 + r >= rows) break;
+            float s[2] = {0.f, 0.f};
+#pragma unroll
+            for (int i = 0; i < MAXV; ++i)
+                if (lane + 32 * i < nvec) LnVec<T>::sum(v[r][i], s);
+            mean[r] = warp_sum(s[0] + s[1]) * inv_d;
+            float q[2] = {0.f, 0.f};
+#pragma unroll
+            for (int i = 0; i < MAXV; ++i)
+                if (lane + 32 * i < nvec) LnVec<T>::sq(v[r][i], mean[r], q);
+            const float var = warp_sum(q[0] + q[1]) * inv_d;
+            rstd[r] = 1.0f / sqrtf(var + eps);
+        }
 #pragma unroll
         for (int i = 0; i < MAXV; ++i) {
             const int idx = lane + 32 * i;
             if (idx < nvec) {
-                v[i] = ld_stream(xr + idx);
-                if (ADD) {
-                    float fa[VEC], fb[VEC];
-                    unpack<T>(v[i], fa);
-                    unpack<T>(ld_stream(reinterpret_cast<const uint4 *>(in2 + row * dim) + idx), fb);
+                const typename LnVec<T>::WB k = LnVec<T>::load_wb(w + idx * VEC, b + idx * VEC);
 #pragma unroll
-                    for (int j = 0; j < VEC; ++j) fa[j] += fb[j];
-                    v[i] = pack<T>(fa);
-                    st_stream(reinterpret_cast<uint4 *>(sum_out + row * dim) + idx, v[i]);
-                }
+                for (int r = 0; r < R; ++r)
+                    if (row0 + r < rows)
+                        st_stream(reinterpret_cast<uint4 *>(out + (row0 + r) * dim) + idx,
+                                  LnVec<T>::norm(v[r][i], mean[r], rstd[r], k));
             }
-        }
-        float s[2] = {0.f, 0.f};
-#pragma unroll
-        for (int i = 0; i < MAXV; ++i)
-            if (lane + 32 * i < nvec) LnVec<T>::sum(v[i], s);
-        const float mean = warp_sum(s[0] + s[1]) * inv_d;
-        float q[2] = {0.f, 0.f};
-#pragma unroll
-        for (int i = 0; i < MAXV; ++i)
-            if (lane + 32 * i < nvec) LnVec<T>::sq(v[i], mean, q);
-        const float var = warp_sum(q[0] + q[1]) * inv_d;
-        const float rstd = 1.0f / sqrtf(var + eps);
-#pragma unroll
-        for (int i = 0; i < MAXV; ++i) {
-            const int idx = lane + 32 * i;
-            if (idx < nvec) st_stream(yr + idx, LnVec<T>::norm(v[i], mean, rstd, w + idx * VEC, b + idx * VEC));
         }
     }
 }
@@ -190,17 +216,23 @@ template <typename T, int MAXV>
 void launch_warp(const void *in, const void *in2, void *sum_out, void *out, const float *w,
                  const float *b, int64_t rows, int nvec, int dim, float eps, cudaStream_t stream) {
     // persistent grid: as many CTAs as fit the SMs at once, so the staged scale / shift are
-    // reused for many rows
-    int64_t blocks = (rows + kLnWarps - 1) / kLnWarps;
-    const int64_t cap = 148 * ln_min_blocks(MAXV);
+    // reused for many rows.  Two rows per warp when the pairs still give every SM its warps.
+    const bool two = in2 == nullptr && MAXV <= 6 && rows >= 148 * kLnWarps * 4;
+    const int64_t rows_per_cta = kLnWarps * (two ? 2 : 1);
+    int64_t blocks = (rows + rows_per_cta - 1) / rows_per_cta;
+    const int64_t cap = 148 * ln_min_blocks_r(MAXV, two ? 2 : 1);
     if (blocks > cap) blocks = cap;
     const size_t smem = 2 * static_cast<size_t>(dim) * sizeof(float);
+    const unsigned grid = static_cast<unsigned>(blocks);
     if (in2)
-        ln_warp_kernel<T, MAXV, true><<<static_cast<unsigned>(blocks), kLnThreads, smem, stream>>>(
+        ln_warp_kernel<T, MAXV, true, 1><<<grid, kLnThreads, smem, stream>>>(
             static_cast<const T *>(in), static_cast<const T *>(in2), static_cast<T *>(sum_out),
             static_cast<T *>(out), w, b, rows, nvec, dim, eps);
+    else if (two)
+        ln_warp_kernel<T, (MAXV <= 6 ? MAXV : 1), false, 2><<<grid, kLnThreads, smem, stream>>>(
+            static_cast<const T *>(in), nullptr, nullptr, static_cast<T *>(out), w, b, rows, nvec, dim, eps);
     else
-        ln_warp_kernel<T, MAXV, false><<<static_cast<unsigned>(blocks), kLnThreads, smem, stream>>>(
+        ln_warp_kernel<T, MAXV, false, 1><<<grid, kLnThreads, smem, stream>>>(
             static_cast<const T *>(in), nullptr, nullptr, static_cast<T *>(out), w, b, rows, nvec, dim, eps);
 }
 
