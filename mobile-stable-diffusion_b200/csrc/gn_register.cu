@@ -1,0 +1,271 @@
+// GroupNorm (+SiLU), register path: one CTA per (image, group) slab, the slab in the CTA's
+// registers (group_norm.cl:1-76 and util.cl:124-134 in one launch, one read and one write).
+#include "gn_device.cuh"
+
+namespace sdfl {
+
+namespace {
+
+// ---------------------------------------------------------------------------------------------
+// Register path: one CTA per slab, the whole slab in the CTA's registers
+// ---------------------------------------------------------------------------------------------
+// For the slabs of the UNet (5-240 KB) the cluster kernel's fixed costs (cluster start-up, barrier
+// set-up, the exchange) are most of its time.  Here a CTA of 512 threads loads its slab with up to
+// NVT 16-byte vectors per thread, all loads in flight at once, folds the moments through one
+// __syncthreads and normalises from registers: one HBM read, one write, no shared-memory staging.
+// Every load of a slab precedes every store to it, so out == in is safe.
+constexpr int kRegThreads = kGnRegThreads;
+constexpr int kRegMaxVecs = kGnRegMaxVecs;
+
+struct RegArgs {
+    const void *in;
+    void *out;
+    const float *w;
+    const float *b;
+    const void *bias;      // [batch, C] addend of the storage type, or nullptr
+    uint32_t units, slab_vecs, slab_elems, cpg, groups, channels;
+    uint32_t vec_uniform;  // hw % lanes-per-vector == 0
+    float eps;
+    FastDiv hw_div;        // element offset in the slab -> channel of the group
+    FastDiv hwv_div;       // vector offset -> channel (when vec_uniform)
+    // channels-last output (NHWC template flag)
+    uint32_t hw, hw_vecs;
+    uint32_t row_bytes;    // shared-memory stride of one channel's pixels: hw * sizeof(T) rounded up to 4, plus 4
+    uint32_t pair;         // fp16 and an even number of channels per group: two channels per store
+    FastDiv out_div;       // output index within the slab -> pixel (divides by cpg, or cpg / 2 when pair)
+    // input as two tensors concatenated along the channels (see ResidentArgs); needs vec_uniform
+    const void *in2;
+    uint32_t c1;
+};
+
+// NHWC: the result is written channels-last, out[n][p][c] (the permute3D__0_2_1 that follows the
+// norm of a SpatialTransformer block, SpatialTransformer.cpp:127-140, fused into the store).  The
+// normalised slab [cpg][hw] goes through shared memory with a 4-byte skew per channel row and
+// leaves as runs of cpg consecutive channels per pixel.
+template <typename T, int ACT, bool BIAS, int NVT, bool NHWC>
+__global__ void __launch_bounds__(kRegThreads, NVT <= 4 ? 2 : 1)
+gn_register_kernel(const RegArgs a) {
+    constexpr int VEC = VecOf<T>::N;
+    constexpr bool HALF = sizeof(T) == 2;
+    __shared__ Moments warp_m[kRegThreads / 32];
+    extern __shared__ __align__(16) unsigned char tsm[];      // NHWC only: cpg rows of row_bytes
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    for (uint32_t unit = blockIdx.x; unit < a.units; unit += gridDim.x) {
+        const uint4 *src = reinterpret_cast<const uint4 *>(a.in) + static_cast<size_t>(unit) * a.slab_vecs;
+        uint4 *dst = reinterpret_cast<uint4 *>(a.out) + static_cast<size_t>(unit) * a.slab_vecs;
+        const T *erow = BIAS ? static_cast<const T *>(a.bias) +
+                                   static_cast<size_t>(unit / a.groups) * a.channels + (unit % a.groups) * a.cpg
+                             : nullptr;
+        // two-source input: vectors [0, split) of the slab come from `in`, the rest from `in2`
+        const uint4 *src2 = src;
+        uint32_t split = 0xffffffffu;
+        if (a.in2 != nullptr) {
+            const uint32_t n = unit / a.groups, c_first = (unit % a.groups) * a.cpg;
+            const uint32_t k1 = c_first >= a.c1 ? 0u : min(a.cpg, a.c1 - c_first);
+            split = k1 * a.hw_vecs;
+            src = reinterpret_cast<const uint4 *>(a.in) + (static_cast<size_t>(n) * a.c1 + c_first) * a.hw_vecs;
+            src2 = reinterpret_cast<const uint4 *>(a.in2) +
+                   (static_cast<size_t>(n) * (a.channels - a.c1) + (max(c_first, a.c1) - a.c1)) * a.hw_vecs - split;
+        }
+        uint4 v[NVT];
+#pragma unroll
+        for (int k = 0; k < NVT; ++k) {
+            const uint32_t idx = tid + k * kRegThreads;
+            if (idx < a.slab_vecs) v[k] = ld_stream((idx < split ? src : src2) + idx);
+        }
+        // this thread's moments, shifted by its first value
+        float s[2] = {0.f, 0.f}, q[2] = {0.f, 0.f};
+        float shift = 0.f;
+        uint32_t mine = 0;
+        if (tid < a.slab_vecs) {
+            shift = HALF ? __half2float(__ushort_as_half(static_cast<unsigned short>(v[0].x & 0xffffu)))
+                         : __uint_as_float(v[0].x);
+            if (BIAS) shift += to_float<T>(erow[a.hw_div.div(tid * VEC)]);
+        }
+#pragma unroll
+        for (int k = 0; k < NVT; ++k) {
+            const uint32_t idx = tid + k * kRegThreads;
+            if (idx < a.slab_vecs) {
+                if (!BIAS) {
+                    stats_vec<T>(v[k], shift, s, q);
+                } else if (a.vec_uniform) {
+                    stats_vec<T>(v[k], shift - to_float<T>(erow[a.hwv_div.div(idx)]), s, q);
+                } else {
+                    float f[VEC];
+                    unpack<T>(v[k], f);
+#pragma unroll
+                    for (int l = 0; l < VEC; ++l) {
+                        const float d = f[l] + to_float<T>(erow[a.hw_div.div(idx * VEC + l)]) - shift;
+                        s[l & 1] += d;
+                        q[l & 1] = fmaf(d, d, q[l & 1]);
+                    }
+                }
+                ++mine;
+            }
+        }
+        Moments m;
+        {
+            const float cnt = static_cast<float>(mine * VEC);
+            const float ss = s[0] + s[1], qq = q[0] + q[1];
+            m.n = cnt;
+            m.mean = mine ? shift + ss / cnt : 0.f;
+            m.m2 = mine ? fmaxf(qq - ss * ss / cnt, 0.f) : 0.f;
+        }
+        m = warp_merge(m);
+        if (lane == 0) warp_m[warp] = m;
+        __syncthreads();
+        // every warp folds the 16 per-warp moments itself, in the same order
+        Moments t = lane < kRegThreads / 32 ? warp_m[lane] : Moments{0.f, 0.f, 0.f};
+        t = warp_merge(t);
+        const float mean = __shfl_sync(0xffffffffu, t.mean, 0);
+        const float var = __shfl_sync(0xffffffffu, t.m2, 0) / static_cast<float>(a.slab_elems);   // biased
+        const float rstd = 1.0f / sqrtf(var + a.eps);
+        const uint32_t ch0 = (unit % a.groups) * a.cpg;
+#pragma unroll
+        for (int k = 0; k < NVT; ++k) {
+            const uint32_t idx = tid + k * kRegThreads;
+            if (idx < a.slab_vecs) {
+                if (a.vec_uniform) {
+                    const uint32_t cl = a.hwv_div.div(idx), c = ch0 + cl;
+                    const float mc = BIAS ? mean - to_float<T>(erow[cl]) : mean;
+                    const Affine<T> af = make_affine<T, ACT>(mc, rstd, __ldg(a.w + c), __ldg(a.b + c));
+                    const uint4 r = norm_vec<T, ACT>(v[k], af);
+                    if (NHWC) {
+                        const uint32_t p0 = (idx - cl * a.hw_vecs) * VEC;
+                        uint32_t *d = reinterpret_cast<uint32_t *>(tsm + cl * a.row_bytes + p0 * sizeof(T));
+                        d[0] = r.x; d[1] = r.y; d[2] = r.z; d[3] = r.w;
+                    } else {
+                        st_stream(dst + idx, r);
+                    }
+                } else {
+                    float f[VEC];
+                    unpack<T>(v[k], f);
+#pragma unroll
+                    for (int l = 0; l < VEC; ++l) {
+                        const uint32_t cl = a.hw_div.div(idx * VEC + l), c = ch0 + cl;
+                        const float mc = BIAS ? mean - to_float<T>(erow[cl]) : mean;
+                        f[l] = activate<ACT, HALF>(fmaf((f[l] - mc) * rstd, __ldg(a.w + c), __ldg(a.b + c)));
+                        if (NHWC) {
+                            const uint32_t p = idx * VEC + l - cl * a.hw;
+                            *reinterpret_cast<T *>(tsm + cl * a.row_bytes + p * sizeof(T)) = from_float<T>(f[l]);
+                        }
+                    }
+                    if (!NHWC) st_stream(dst + idx, pack<T>(f));
+                }
+            }
+        }
+        __syncthreads();       // warp_m is reused by the next slab; NHWC: the slab is in shared memory
+        if (NHWC) {
+            // out[n][p][ch0 + c]: consecutive threads take consecutive channels of a pixel
+            T *outp = static_cast<T *>(a.out) + static_cast<size_t>(unit / a.groups) * a.hw * a.channels + ch0;
+            if (HALF && a.pair) {
+                const uint32_t hp = a.cpg >> 1, total = a.hw * hp;
+                for (uint32_t o = tid; o < total; o += kRegThreads) {
+                    const uint32_t p = a.out_div.div(o), c = 2u * (o - p * hp);
+                    const unsigned short lo = *reinterpret_cast<const unsigned short *>(tsm + c * a.row_bytes + p * 2u);
+                    const unsigned short hi = *reinterpret_cast<const unsigned short *>(tsm + (c + 1u) * a.row_bytes + p * 2u);
+                    *reinterpret_cast<uint32_t *>(outp + static_cast<size_t>(p) * a.channels + c) =
+                        static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
+                }
+            } else {
+                const uint32_t total = a.hw * a.cpg;
+                for (uint32_t o = tid; o < total; o += kRegThreads) {
+                    const uint32_t p = a.out_div.div(o), c = o - p * a.cpg;
+                    outp[static_cast<size_t>(p) * a.channels + c] =
+                        *reinterpret_cast<const T *>(tsm + c * a.row_bytes + p * sizeof(T));
+                }
+            }
+            __syncthreads();   // the next slab overwrites the staging rows
+        }
+    }
+}
+
+constexpr size_t kRegMaxStageBytes = kGnRegMaxStageBytes;
+
+template <typename T, int ACT, int NVT>
+cudaError_t launch_register_nhwc(const RegArgs &a, unsigned grid, size_t smem, cudaStream_t stream) {
+    static std::atomic<bool> done[kMaxDevices];
+    int dev = 0;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess) return err;
+    if (!(dev >= 0 && dev < kMaxDevices && done[dev].load(std::memory_order_acquire))) {
+        err = cudaFuncSetAttribute(gn_register_kernel<T, ACT, false, NVT, true>,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   static_cast<int>(kRegMaxStageBytes));
+        if (err != cudaSuccess) return err;
+        if (dev >= 0 && dev < kMaxDevices) done[dev].store(true, std::memory_order_release);
+    }
+    gn_register_kernel<T, ACT, false, NVT, true><<<grid, kRegThreads, smem, stream>>>(a);
+    return cudaGetLastError();
+}
+
+template <typename T, int ACT, bool BIAS>
+cudaError_t launch_register_as(const RegArgs &a, bool nhwc, cudaStream_t stream) {
+    const uint32_t per_thread = (a.slab_vecs + kRegThreads - 1) / kRegThreads;
+    const unsigned grid = a.units < 148u * 64u ? a.units : 148u * 64u;
+    cudaError_t err;
+    if (nhwc) {
+        if (BIAS) return cudaErrorInvalidValue;
+        const size_t smem = static_cast<size_t>(a.cpg) * a.row_bytes;
+        err = per_thread <= 4    ? launch_register_nhwc<T, ACT, 4>(a, grid, smem, stream)
+              : per_thread <= 12 ? launch_register_nhwc<T, ACT, 12>(a, grid, smem, stream)
+                                 : launch_register_nhwc<T, ACT, kRegMaxVecs>(a, grid, smem, stream);
+    } else {
+        if (per_thread <= 4)
+            gn_register_kernel<T, ACT, BIAS, 4, false><<<grid, kRegThreads, 0, stream>>>(a);
+        else if (per_thread <= 12)
+            gn_register_kernel<T, ACT, BIAS, 12, false><<<grid, kRegThreads, 0, stream>>>(a);
+        else
+            gn_register_kernel<T, ACT, BIAS, kRegMaxVecs, false><<<grid, kRegThreads, 0, stream>>>(a);
+        err = cudaGetLastError();
+    }
+    if (err == cudaSuccess) g_launches.fetch_add(1);
+    return err;
+}
+
+template <typename T, int ACT>
+cudaError_t launch_register(const RegArgs &a, bool nhwc, cudaStream_t stream) {
+    return a.bias ? launch_register_as<T, ACT, true>(a, nhwc, stream)
+                  : launch_register_as<T, ACT, false>(a, nhwc, stream);
+}
+
+}  // namespace
+
+cudaError_t gn_register_launch(const GnShape &s, const GnPlan &plan, const void *in, void *out,
+                               const float *w, const float *b, cudaStream_t stream, const void *bias,
+                               const void *in2, int64_t c1) {
+    const int64_t esz = s.dtype == kF16 ? 2 : 4;
+    const int64_t vec = 16 / esz;
+    const int64_t cpg = s.channels / s.groups;
+    const int64_t slab_elems = cpg * s.hw;
+    const int64_t units = s.batch * s.groups;
+    if (units == 0 || slab_elems == 0) return cudaSuccess;
+    RegArgs a;
+    a.in = in; a.out = out; a.w = w; a.b = b; a.bias = bias;
+    a.units = static_cast<uint32_t>(units);
+    a.slab_vecs = static_cast<uint32_t>(slab_elems * esz / 16);
+    a.slab_elems = static_cast<uint32_t>(slab_elems);
+    a.cpg = static_cast<uint32_t>(cpg);
+    a.groups = static_cast<uint32_t>(s.groups);
+    a.channels = static_cast<uint32_t>(s.channels);
+    a.vec_uniform = s.hw % vec == 0;
+    a.eps = s.eps;
+    a.hw_div = FastDiv::make(static_cast<uint32_t>(s.hw));
+    a.hwv_div = FastDiv::make(a.vec_uniform ? static_cast<uint32_t>(s.hw / vec) : 1u);
+    a.hw = static_cast<uint32_t>(s.hw);
+    a.hw_vecs = a.vec_uniform ? static_cast<uint32_t>(s.hw / vec) : 1u;
+    a.row_bytes = static_cast<uint32_t>(gn_nhwc_row_bytes(s));
+    a.pair = s.dtype == kF16 && cpg % 2 == 0;
+    a.out_div = FastDiv::make(static_cast<uint32_t>(a.pair ? cpg / 2 : cpg));
+    a.in2 = in2;
+    a.c1 = static_cast<uint32_t>(c1);
+    if (in2 != nullptr && !gn_concat_fused_ok(s, plan, in, in2, c1)) return cudaErrorInvalidValue;
+    const bool nhwc = plan.nhwc != 0;
+    if (s.dtype == kF16)
+        return s.act == kActSilu ? launch_register<__half, kActSilu>(a, nhwc, stream)
+                                 : launch_register<__half, kActNone>(a, nhwc, stream);
+    return s.act == kActSilu ? launch_register<float, kActSilu>(a, nhwc, stream)
+                             : launch_register<float, kActNone>(a, nhwc, stream);
+}
+
+}  // namespace sdfl

@@ -1,0 +1,467 @@
+// GroupNorm (+SiLU), split path and the reference's kernels by name.
+//
+// Split path: any shape and alignment.  Kernel 1 writes one (mean, M2) pair per chunk to a scratch
+// buffer; kernel 2 merges the chunk pairs of its slab in a fixed order and normalises (or, for the
+// channels-last form, normalises and transposes tile by tile).  Also the stand-alone
+// local_reduction_mean / local_reduction_variance / group_norm / layer_norm kernels that keep the
+// reference's three-launch call sequence (group_norm.cl:1-76, layer_norm.cl:58-78).
+#include "gn_device.cuh"
+
+namespace sdfl {
+
+namespace {
+
+// ---------------------------------------------------------------------------------------------
+// Split path
+// ---------------------------------------------------------------------------------------------
+constexpr int kSplitThreads = 512;
+
+struct SplitArgs {
+    const void *in;
+    void *out;
+    const float *w;
+    const float *b;
+    const void *bias;      // [batch, C] addend of the storage type, or nullptr
+    uint32_t channels;     // C
+    float *partial;        // [units * splits * 2]  (mean, M2) per chunk
+    uint32_t slab_elems;
+    uint32_t chunk_elems;  // multiple of the vector width when `vec` is set
+    uint32_t splits;
+    uint32_t cpg, groups;
+    uint32_t vec;          // 16-byte accesses allowed (alignment and divisibility hold)
+    uint32_t vec_uniform;  // and a vector never straddles a channel
+    float eps;
+    FastDiv hw_div;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(kSplitThreads) gn_split_stats_kernel(const SplitArgs a) {
+    constexpr int VEC = VecOf<T>::N;
+    __shared__ Moments warp_m[kSplitThreads / 32];
+    const uint32_t unit = blockIdx.x / a.splits, split = blockIdx.x % a.splits;
+    const uint32_t e0 = split * a.chunk_elems;
+    const uint32_t e1 = min(a.slab_elems, e0 + a.chunk_elems);
+    const T *x = static_cast<const T *>(a.in) + static_cast<size_t>(unit) * a.slab_elems;
+    const T *erow = a.bias ? static_cast<const T *>(a.bias) +
+                                 static_cast<size_t>(unit / a.groups) * a.channels + (unit % a.groups) * a.cpg
+                           : nullptr;
+    Shifted sh{0.f, 0.f, 0.f, 0.f};
+    if (a.vec) {
+        const uint4 *xv = reinterpret_cast<const uint4 *>(x);
+        for (uint32_t i = e0 / VEC + threadIdx.x; i < e1 / VEC; i += kSplitThreads) {
+            float f[VEC];
+            unpack<T>(__ldg(xv + i), f);
+            if (erow) {
+#pragma unroll
+                for (int j = 0; j < VEC; ++j) f[j] += to_float<T>(erow[a.hw_div.div(i * VEC + j)]);
+            }
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) sh.add(f[j]);
+        }
+    } else {
+        for (uint32_t i = e0 + threadIdx.x; i < e1; i += kSplitThreads)
+            sh.add(to_float<T>(x[i]) + (erow ? to_float<T>(erow[a.hw_div.div(i)]) : 0.f));
+    }
+    Moments m = warp_merge(sh.done());
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) warp_m[warp] = m;
+    __syncthreads();
+    if (warp == 0) {
+        Moments t = lane < kSplitThreads / 32 ? warp_m[lane] : Moments{0.f, 0.f, 0.f};
+        t = warp_merge(t);
+        if (lane == 0) {
+            a.partial[2 * static_cast<size_t>(blockIdx.x)] = t.mean;
+            a.partial[2 * static_cast<size_t>(blockIdx.x) + 1] = t.m2;
+        }
+    }
+}
+
+template <typename T, int ACT>
+__global__ void __launch_bounds__(kSplitThreads) gn_split_apply_kernel(const SplitArgs a) {
+    constexpr int VEC = VecOf<T>::N;
+    constexpr bool HALF = sizeof(T) == 2;
+    __shared__ float s_stats[2];
+    const uint32_t unit = blockIdx.x / a.splits, split = blockIdx.x % a.splits;
+    if (threadIdx.x < 32) {
+        // lane l folds chunks l, l+32, ... in order; lanes are then folded by shuffles.
+        Moments m{0.f, 0.f, 0.f};
+        for (uint32_t s = threadIdx.x; s < a.splits; s += 32) {
+            const uint32_t c0 = s * a.chunk_elems;
+            const uint32_t c1 = min(a.slab_elems, c0 + a.chunk_elems);
+            Moments y;
+            y.n = c1 > c0 ? static_cast<float>(c1 - c0) : 0.f;
+            const size_t p = 2 * (static_cast<size_t>(unit) * a.splits + s);
+            y.mean = a.partial[p];
+            y.m2 = a.partial[p + 1];
+            m = merge(m, y);
+        }
+        m = warp_merge(m);
+        if (threadIdx.x == 0) {
+            s_stats[0] = m.mean;
+            s_stats[1] = m.m2 / static_cast<float>(a.slab_elems);
+        }
+    }
+    __syncthreads();
+    const float mean = s_stats[0];
+    const float rstd = 1.0f / sqrtf(s_stats[1] + a.eps);
+    const uint32_t ch0 = (unit % a.groups) * a.cpg;
+    const uint32_t e0 = split * a.chunk_elems;
+    const uint32_t e1 = min(a.slab_elems, e0 + a.chunk_elems);
+    const size_t base = static_cast<size_t>(unit) * a.slab_elems;
+    const T *x = static_cast<const T *>(a.in) + base;
+    T *y = static_cast<T *>(a.out) + base;
+    const T *erow = a.bias ? static_cast<const T *>(a.bias) +
+                                 static_cast<size_t>(unit / a.groups) * a.channels + ch0
+                           : nullptr;
+    if (a.vec) {
+        const uint4 *xv = reinterpret_cast<const uint4 *>(x);
+        uint4 *yv = reinterpret_cast<uint4 *>(y);
+        for (uint32_t i = e0 / VEC + threadIdx.x; i < e1 / VEC; i += kSplitThreads) {
+            float f[VEC];
+            unpack<T>(ld_stream(xv + i), f);
+            if (a.vec_uniform) {
+                const uint32_t cl = a.hw_div.div(i * VEC), c = ch0 + cl;
+                const float wv = __ldg(a.w + c), bv = __ldg(a.b + c);
+                const float mc = erow ? mean - to_float<T>(erow[cl]) : mean;
+#pragma unroll
+                for (int j = 0; j < VEC; ++j)
+                    f[j] = activate<ACT, HALF>(fmaf((f[j] - mc) * rstd, wv, bv));
+            } else {
+#pragma unroll
+                for (int j = 0; j < VEC; ++j) {
+                    const uint32_t cl = a.hw_div.div(i * VEC + j), c = ch0 + cl;
+                    const float mc = erow ? mean - to_float<T>(erow[cl]) : mean;
+                    f[j] = activate<ACT, HALF>(
+                        fmaf((f[j] - mc) * rstd, __ldg(a.w + c), __ldg(a.b + c)));
+                }
+            }
+            st_stream(yv + i, pack<T>(f));
+        }
+    } else {
+        for (uint32_t i = e0 + threadIdx.x; i < e1; i += kSplitThreads) {
+            const uint32_t cl = a.hw_div.div(i), c = ch0 + cl;
+            const float mc = erow ? mean - to_float<T>(erow[cl]) : mean;
+            const float v = fmaf((to_float<T>(x[i]) - mc) * rstd, __ldg(a.w + c), __ldg(a.b + c));
+            y[i] = from_float<T>(activate<ACT, HALF>(v));
+        }
+    }
+}
+
+// Second kernel of the split path with a channels-last store: out[n][p][c] = act(norm(in[n][c][p])).
+// A CTA takes a tile of TS channels x TS pixels (TS = 64 with two elements per access, 32 with one),
+// folds the per-chunk moments of the groups its channels belong to, applies the affine while
+// loading (rows along the pixels: coalesced) and writes through shared memory with rows along
+// the channels (coalesced again).  grid (ceil(hw / TS), ceil(C / TS), batch), block (32, 8).
+template <typename T, int ACT, bool PAIRS>
+__global__ void __launch_bounds__(256) gn_apply_nhwc_kernel(const SplitArgs a, uint32_t hw) {
+    constexpr bool HALF = sizeof(T) == 2;
+    constexpr int TS = PAIRS ? 64 : 32, E = PAIRS ? 2 : 1;
+    constexpr int PAD = PAIRS ? (HALF ? 2 : 1) : 1;
+    __shared__ __align__(8) T tile[TS][TS + PAD];
+    __shared__ float4 coef[TS];        // per channel of the tile: mean, rstd, scale, shift
+    const uint32_t tx = threadIdx.x, ty = threadIdx.y, tid = ty * 32 + tx;
+    const uint32_t p0 = blockIdx.x * TS, c0 = blockIdx.y * TS, n = blockIdx.z;
+    if (tid < TS && c0 + tid < a.channels) {
+        const uint32_t c = c0 + tid;
+        const size_t unit = static_cast<size_t>(n) * a.groups + c / a.cpg;
+        Moments m{0.f, 0.f, 0.f};
+        for (uint32_t s = 0; s < a.splits; ++s) {      // chunks in order: every CTA gets the same bits
+            const uint32_t e0 = s * a.chunk_elems, e1 = min(a.slab_elems, e0 + a.chunk_elems);
+            Moments y;
+            y.n = e1 > e0 ? static_cast<float>(e1 - e0) : 0.f;
+            y.mean = a.partial[2 * (unit * a.splits + s)];
+            y.m2 = a.partial[2 * (unit * a.splits + s) + 1];
+            m = merge(m, y);
+        }
+        const float var = m.m2 / static_cast<float>(a.slab_elems);
+        coef[tid] = make_float4(m.mean, 1.0f / sqrtf(var + a.eps), __ldg(a.w + c), __ldg(a.b + c));
+    }
+    __syncthreads();
+    const T *x = static_cast<const T *>(a.in) + static_cast<size_t>(n) * a.channels * hw;
+    T *y = static_cast<T *>(a.out) + static_cast<size_t>(n) * a.channels * hw;
+#pragma unroll
+    for (int r = ty; r < TS; r += 8) {
+        const uint32_t c = c0 + r, p = p0 + E * tx;
+        if (c < a.channels && p < hw) {
+            const float4 k = coef[r];
+            const T *src = x + static_cast<size_t>(c) * hw + p;
+            if (PAIRS) {
+                float f0, f1;
+                if (HALF) {
+                    const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(src));
+                    f0 = f.x; f1 = f.y;
+                } else {
+                    const float2 f = *reinterpret_cast<const float2 *>(src);
+                    f0 = f.x; f1 = f.y;
+                }
+                tile[r][2 * tx] = from_float<T>(activate<ACT, HALF>(fmaf((f0 - k.x) * k.y, k.z, k.w)));
+                tile[r][2 * tx + 1] = from_float<T>(activate<ACT, HALF>(fmaf((f1 - k.x) * k.y, k.z, k.w)));
+            } else {
+                tile[r][tx] = from_float<T>(activate<ACT, HALF>(fmaf((to_float<T>(*src) - k.x) * k.y, k.z, k.w)));
+            }
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int r = ty; r < TS; r += 8) {
+        const uint32_t p = p0 + r, c = c0 + E * tx;
+        if (p < hw && c < a.channels) {
+            T *dst = y + static_cast<size_t>(p) * a.channels + c;
+            if (PAIRS) {
+                const T v0 = tile[2 * tx][r], v1 = tile[2 * tx + 1][r];
+                if (HALF) {
+                    *reinterpret_cast<uint32_t *>(dst) =
+                        static_cast<uint32_t>(*reinterpret_cast<const unsigned short *>(&v0)) |
+                        (static_cast<uint32_t>(*reinterpret_cast<const unsigned short *>(&v1)) << 16);
+                } else {
+                    *reinterpret_cast<float2 *>(dst) = make_float2(to_float<T>(v0), to_float<T>(v1));
+                }
+            } else {
+                *dst = tile[tx][r];
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Stand-alone kernels for the reference's three-launch sequence
+// ---------------------------------------------------------------------------------------------
+constexpr int kStatsThreads = 256;
+
+// out[g] = sum(in[g*n .. (g+1)*n)) / n                      (group_norm.cl:1-27)
+// out[g] = sum((in - mean[g])^2) / n  when `mean` is given   (group_norm.cl:29-57)
+template <typename T>
+__global__ void __launch_bounds__(kStatsThreads)
+stats_kernel(const T *__restrict__ in, const float *__restrict__ mean, float *__restrict__ out,
+             long long n) {
+    __shared__ float red[33];
+    const T *x = in + static_cast<size_t>(blockIdx.x) * n;
+    const float m = mean ? mean[blockIdx.x] : 0.f;
+    float acc = 0.f;
+    for (long long i = threadIdx.x; i < n; i += kStatsThreads) {
+        const float v = to_float<T>(x[i]);
+        if (mean) {
+            const float d = v - m;
+            acc = fmaf(d, d, acc);
+        } else {
+            acc += v;
+        }
+    }
+    const float t = block_sum(acc, red);
+    if (threadIdx.x == 0) out[blockIdx.x] = t / static_cast<float>(n);
+}
+
+// group_norm.cl:59-76 with the weight index wrapped per image: c = (i / channelSize) % C.
+template <typename T>
+__global__ void gn_apply_kernel(const T *__restrict__ in, const float *__restrict__ mean,
+                                const float *__restrict__ var, const float *__restrict__ w,
+                                const float *__restrict__ b, unsigned long long group_size,
+                                unsigned long long channel_size, float eps, T *__restrict__ out,
+                                unsigned long long n, unsigned long long channels) {
+    for (unsigned long long i = blockIdx.x * static_cast<unsigned long long>(blockDim.x) + threadIdx.x;
+         i < n; i += static_cast<unsigned long long>(gridDim.x) * blockDim.x) {
+        const unsigned long long g = i / group_size;
+        const unsigned long long c = (i / channel_size) % channels;
+        float t = to_float<T>(in[i]) - mean[g];
+        t /= sqrtf(var[g] + eps);
+        out[i] = from_float<T>(fmaf(t, w[c], b[c]));
+    }
+}
+
+// layer_norm.cl:63-78 (eps as an argument instead of the file-scope constant at :58).
+template <typename T>
+__global__ void ln_apply_kernel(const T *__restrict__ in, const float *__restrict__ mean,
+                                const float *__restrict__ var, const float *__restrict__ w,
+                                const float *__restrict__ b, unsigned long long dim, float eps,
+                                T *__restrict__ out, unsigned long long n) {
+    for (unsigned long long i = blockIdx.x * static_cast<unsigned long long>(blockDim.x) + threadIdx.x;
+         i < n; i += static_cast<unsigned long long>(gridDim.x) * blockDim.x) {
+        const unsigned long long k = i % dim;
+        const unsigned long long r = i / dim;
+        float t = to_float<T>(in[i]) - mean[r];
+        t /= sqrtf(var[r] + eps);
+        out[i] = from_float<T>(fmaf(t, w[k], b[k]));
+    }
+}
+
+}  // namespace
+
+cudaError_t gn_split_launch(const GnShape &s, const GnPlan &plan, const void *in, void *out, const float *w,
+                            const float *b, void *workspace, cudaStream_t stream, const void *bias) {
+    const int64_t esz = s.dtype == kF16 ? 2 : 4;
+    const int64_t vec = 16 / esz;
+    const int64_t cpg = s.channels / s.groups;
+    const int64_t slab_elems = cpg * s.hw;
+    const int64_t units = s.batch * s.groups;
+    if (units == 0 || slab_elems == 0) return cudaSuccess;
+    if (workspace == nullptr) return cudaErrorInvalidValue;
+    SplitArgs a;
+    a.in = in; a.out = out; a.w = w; a.b = b;
+    a.partial = static_cast<float *>(workspace);
+    a.bias = bias;
+    a.channels = static_cast<uint32_t>(s.channels);
+    a.slab_elems = static_cast<uint32_t>(slab_elems);
+    a.splits = static_cast<uint32_t>(plan.splits);
+    int64_t chunk = (slab_elems + plan.splits - 1) / plan.splits;
+    chunk = ((chunk + vec - 1) / vec) * vec;
+    a.chunk_elems = static_cast<uint32_t>(chunk);
+    a.cpg = static_cast<uint32_t>(cpg);
+    a.groups = static_cast<uint32_t>(s.groups);
+    a.vec = aligned16(in) && aligned16(out) && slab_elems % vec == 0;
+    a.vec_uniform = a.vec && s.hw % vec == 0;
+    a.eps = s.eps;
+    a.hw_div = FastDiv::make(static_cast<uint32_t>(s.hw));
+    const unsigned grid = static_cast<unsigned>(units * plan.splits);
+    if (plan.nhwc) {
+        // statistics as usual, then the tiled apply that writes channels-last
+        if (bias != nullptr || s.batch > 65535) return cudaErrorInvalidValue;
+        const uintptr_t pa = esz == 2 ? 3 : 7;
+        const bool pairs = s.hw % 2 == 0 && s.channels % 2 == 0 &&
+                           (reinterpret_cast<uintptr_t>(in) & pa) == 0 && (reinterpret_cast<uintptr_t>(out) & pa) == 0;
+        const int ts = pairs ? 64 : 32;
+        const dim3 tgrid(static_cast<unsigned>((s.hw + ts - 1) / ts), static_cast<unsigned>((s.channels + ts - 1) / ts),
+                         static_cast<unsigned>(s.batch));
+        if (tgrid.y > 65535) return cudaErrorInvalidValue;
+        const dim3 tblock(32, 8);
+        const uint32_t hw32 = static_cast<uint32_t>(s.hw);
+#define SDFL_NHWC_APPLY(T, ACT)                                                              \
+        do {                                                                                 \
+            if (pairs) gn_apply_nhwc_kernel<T, ACT, true><<<tgrid, tblock, 0, stream>>>(a, hw32);   \
+            else gn_apply_nhwc_kernel<T, ACT, false><<<tgrid, tblock, 0, stream>>>(a, hw32);        \
+        } while (0)
+        if (s.dtype == kF16) {
+            gn_split_stats_kernel<__half><<<grid, kSplitThreads, 0, stream>>>(a);
+            if (s.act == kActSilu) SDFL_NHWC_APPLY(__half, kActSilu); else SDFL_NHWC_APPLY(__half, kActNone);
+        } else {
+            gn_split_stats_kernel<float><<<grid, kSplitThreads, 0, stream>>>(a);
+            if (s.act == kActSilu) SDFL_NHWC_APPLY(float, kActSilu); else SDFL_NHWC_APPLY(float, kActNone);
+        }
+#undef SDFL_NHWC_APPLY
+        cudaError_t err = cudaGetLastError();
+        if (err == cudaSuccess) g_launches.fetch_add(2);
+        return err;
+    }
+    if (s.dtype == kF16) {
+        gn_split_stats_kernel<__half><<<grid, kSplitThreads, 0, stream>>>(a);
+        if (s.act == kActSilu) gn_split_apply_kernel<__half, kActSilu><<<grid, kSplitThreads, 0, stream>>>(a);
+        else gn_split_apply_kernel<__half, kActNone><<<grid, kSplitThreads, 0, stream>>>(a);
+    } else {
+        gn_split_stats_kernel<float><<<grid, kSplitThreads, 0, stream>>>(a);
+        if (s.act == kActSilu) gn_split_apply_kernel<float, kActSilu><<<grid, kSplitThreads, 0, stream>>>(a);
+        else gn_split_apply_kernel<float, kActNone><<<grid, kSplitThreads, 0, stream>>>(a);
+    }
+    cudaError_t err = cudaGetLastError();
+    if (err == cudaSuccess) g_launches.fetch_add(2);
+    return err;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Split path with its scratch inside the library image (no allocation anywhere)
+// ---------------------------------------------------------------------------------------------
+// Some callers cannot give the split path a workspace because they are not allowed to call an
+// allocator at all: a host that pre-commits every byte of device memory to its own pools at
+// start-up and treats any later cudaMalloc as a bug, a plugin loaded into such a host, or code
+// on a latency-critical thread where an allocator's implicit device synchronisation is not
+// acceptable.  For them the (mean, M2) pairs of the split path live in this fixed array, which
+// every device that loads the library carries until the process exits.
+//
+// g_static_scratch names device memory only inside device code.  On the host the symbol is a
+// stand-in; its device address has to be asked for (cudaGetSymbolAddress) with the right device
+// current, once per device, and that address is what the kernels get.
+static __device__ __align__(256) unsigned char g_static_scratch[kGnStaticScratchBytes];
+
+cudaError_t gn_launch_static_scratch(const GnShape &s, const GnPlan &plan, const void *in, void *out,
+                                     const float *w, const float *b, cudaStream_t stream) {
+    static std::mutex mu;
+    static void *address[kMaxDevices] = {};       // device address of g_static_scratch, per device
+    if (plan.path != kGnSplit || plan.workspace > kGnStaticScratchBytes) return cudaErrorInvalidValue;
+    int dev = 0;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess) return err;
+    if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+    void *ptr = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (address[dev] == nullptr) {
+            // first call on this device: resolve the symbol while this device is current
+            err = cudaGetSymbolAddress(&address[dev], g_static_scratch);
+            if (err != cudaSuccess) { address[dev] = nullptr; return err; }
+        }
+        ptr = address[dev];
+    }
+    // Nothing in the scratch has to start at zero: the statistics kernel overwrites every
+    // (mean, M2) pair the apply kernel reads, and the two run in stream order.
+    return gn_launch(s, plan, in, out, w, b, ptr, stream, nullptr);
+}
+
+cudaError_t stats_mean_launch(const void *in, float *out, int64_t groups, int64_t n, int dtype,
+                              cudaStream_t stream) {
+    if (groups == 0) return cudaSuccess;
+    if (dtype == kF16)
+        stats_kernel<__half><<<static_cast<unsigned>(groups), kStatsThreads, 0, stream>>>(
+            static_cast<const __half *>(in), nullptr, out, n);
+    else
+        stats_kernel<float><<<static_cast<unsigned>(groups), kStatsThreads, 0, stream>>>(
+            static_cast<const float *>(in), nullptr, out, n);
+    cudaError_t err = cudaGetLastError();
+    if (err == cudaSuccess) g_launches.fetch_add(1);
+    return err;
+}
+
+cudaError_t stats_var_launch(const void *in, const float *mean, float *out, int64_t groups,
+                             int64_t n, int dtype, cudaStream_t stream) {
+    if (groups == 0) return cudaSuccess;
+    if (dtype == kF16)
+        stats_kernel<__half><<<static_cast<unsigned>(groups), kStatsThreads, 0, stream>>>(
+            static_cast<const __half *>(in), mean, out, n);
+    else
+        stats_kernel<float><<<static_cast<unsigned>(groups), kStatsThreads, 0, stream>>>(
+            static_cast<const float *>(in), mean, out, n);
+    cudaError_t err = cudaGetLastError();
+    if (err == cudaSuccess) g_launches.fetch_add(1);
+    return err;
+}
+
+static unsigned flat_grid(int64_t n, int threads) {
+    int64_t blocks = (n + threads - 1) / threads;
+    const int64_t cap = 148 * 16;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    return static_cast<unsigned>(blocks);
+}
+
+cudaError_t gn_apply_launch(const void *in, const float *mean, const float *var, const float *w,
+                            const float *b, int64_t group_size, int64_t channel_size, float eps,
+                            void *out, int64_t n, int64_t channels, int dtype, cudaStream_t stream) {
+    if (n == 0) return cudaSuccess;
+    const unsigned grid = flat_grid(n, 256);
+    if (dtype == kF16)
+        gn_apply_kernel<__half><<<grid, 256, 0, stream>>>(
+            static_cast<const __half *>(in), mean, var, w, b, group_size, channel_size, eps,
+            static_cast<__half *>(out), n, channels);
+    else
+        gn_apply_kernel<float><<<grid, 256, 0, stream>>>(
+            static_cast<const float *>(in), mean, var, w, b, group_size, channel_size, eps,
+            static_cast<float *>(out), n, channels);
+    cudaError_t err = cudaGetLastError();
+    if (err == cudaSuccess) g_launches.fetch_add(1);
+    return err;
+}
+
+cudaError_t ln_apply_launch(const void *in, const float *mean, const float *var, const float *w,
+                            const float *b, int64_t dim, float eps, void *out, int64_t n, int dtype,
+                            cudaStream_t stream) {
+    if (n == 0) return cudaSuccess;
+    const unsigned grid = flat_grid(n, 256);
+    if (dtype == kF16)
+        ln_apply_kernel<__half><<<grid, 256, 0, stream>>>(
+            static_cast<const __half *>(in), mean, var, w, b, dim, eps, static_cast<__half *>(out), n);
+    else
+        ln_apply_kernel<float><<<grid, 256, 0, stream>>>(
+            static_cast<const float *>(in), mean, var, w, b, dim, eps, static_cast<float *>(out), n);
+    cudaError_t err = cudaGetLastError();
+    if (err == cudaSuccess) g_launches.fetch_add(1);
+    return err;
+}
+
+}  // namespace sdfl
