@@ -114,6 +114,31 @@ transpose_pairs_kernel(const T *__restrict__ src, const T *res, T *dst, int J, i
         const long long base = (q / tiles_j) * slice;
         T *d = dst + base;
         const int j = jt * kTile + 2 * tx;
+        if constexpr (sizeof(T) == 2) {
+            // fp16: 2 x 2 blocks.  One 32-bit word of source row 2tx and one of row 2tx+1 (two
+            // consecutive k each) give the pairs of output rows k and k+1: half as many
+            // shared-memory loads as element-wise column reads.
+#pragma unroll
+            for (int pr = ty; pr < kTile / 2; pr += 8) {
+                const int r0 = 2 * pr, k = kt * kTile + r0;
+                if (k < K && j < J) {               // K is even: row k + 1 exists too
+                    const uint32_t a = *reinterpret_cast<const uint32_t *>(&tile[buf][2 * tx][r0]);
+                    const uint32_t b = *reinterpret_cast<const uint32_t *>(&tile[buf][2 * tx + 1][r0]);
+                    uint32_t o0 = __byte_perm(a, b, 0x5410), o1 = __byte_perm(a, b, 0x7632);
+                    const long long o = static_cast<long long>(k) * J + j;
+                    if (ADD) {
+                        const uint32_t w0 = *reinterpret_cast<const uint32_t *>(&rtile[buf][r0][2 * tx]);
+                        const uint32_t w1 = *reinterpret_cast<const uint32_t *>(&rtile[buf][r0 + 1][2 * tx]);
+                        P v0 = pair_add<T>(*reinterpret_cast<const P *>(&o0), *reinterpret_cast<const P *>(&w0));
+                        P v1 = pair_add<T>(*reinterpret_cast<const P *>(&o1), *reinterpret_cast<const P *>(&w1));
+                        o0 = *reinterpret_cast<const uint32_t *>(&v0);
+                        o1 = *reinterpret_cast<const uint32_t *>(&v1);
+                    }
+                    *reinterpret_cast<uint32_t *>(d + o) = o0;
+                    *reinterpret_cast<uint32_t *>(d + o + J) = o1;
+                }
+            }
+        } else {
 #pragma unroll
         for (int r = ty; r < kTile; r += 8) {
             const int k = kt * kTile + r;
@@ -130,6 +155,7 @@ transpose_pairs_kernel(const T *__restrict__ src, const T *res, T *dst, int J, i
                 }
                 *reinterpret_cast<P *>(d + o) = v;
             }
+        }
         }
         __syncthreads();      // this buffer is the target of the copies issued next time round
     }
