@@ -223,6 +223,92 @@ __global__ void __launch_bounds__(256) gn_apply_nhwc_kernel(const SplitArgs a, u
     }
 }
 
+// The same for tensors whose extents and alignment allow two elements per access, as a persistent
+// kernel: CTAs walk over 64-channel x 64-pixel tiles (tile id = (n * tiles_c + ct) * tiles_p + pt,
+// pixels fastest, so consecutive tiles of a CTA mostly share their channels and the folded
+// moments are recomputed only when (n, ct) changes).  A tile is fetched with cp.async 4-byte
+// copies straight into shared memory while the previous one is normalised and written out
+// (double buffer): the loads in flight per SM no longer depend on registers.
+template <typename T, int ACT>
+__global__ void __launch_bounds__(256, 6)
+gn_apply_nhwc_async_kernel(const SplitArgs a, uint32_t hw, unsigned tiles_c, unsigned tiles_p,
+                           unsigned long long total_tiles) {
+    constexpr bool HALF = sizeof(T) == 2;
+    constexpr int TS = 64, PAD = HALF ? 2 : 1;
+    using Tile = T[TS][TS + PAD];
+    extern __shared__ __align__(16) unsigned char nhwc_smem[];
+    Tile *tile = reinterpret_cast<Tile *>(nhwc_smem);                       // [2]
+    float4 *coef = reinterpret_cast<float4 *>(nhwc_smem + 2 * sizeof(Tile)); // [TS]: mean, rstd, scale, shift
+    const uint32_t tx = threadIdx.x, ty = threadIdx.y, tid = ty * 32 + tx;
+    const size_t image = static_cast<size_t>(a.channels) * hw;
+
+    auto issue = [&](unsigned long long id, int buf) {
+        if (id < total_tiles) {
+            const unsigned pt = static_cast<unsigned>(id % tiles_p);
+            const unsigned long long q = id / tiles_p;
+            const unsigned ct = static_cast<unsigned>(q % tiles_c);
+            const T *x = static_cast<const T *>(a.in) + (q / tiles_c) * image;
+            const uint32_t p = pt * TS + 2 * tx;
+#pragma unroll
+            for (int r = ty; r < TS; r += 8) {
+                const uint32_t c = ct * TS + r;
+                if (c < a.channels && p < hw) {
+                    const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(&tile[buf][r][2 * tx]));
+                    const T *g = x + static_cast<size_t>(c) * hw + p;
+                    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(g) : "memory");
+                    if (!HALF) asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d + 4u), "l"(g + 1) : "memory");
+                }
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");      // one group per call, empty past the end
+    };
+
+    unsigned long long id = blockIdx.x, coef_of = ~0ull;
+    issue(id, 0);
+    for (int buf = 0; id < total_tiles; id += gridDim.x, buf ^= 1) {
+        issue(id + gridDim.x, buf ^ 1);
+        const unsigned pt = static_cast<unsigned>(id % tiles_p);
+        const unsigned long long q = id / tiles_p;              // n * tiles_c + ct
+        const unsigned ct = static_cast<unsigned>(q % tiles_c);
+        const unsigned long long n = q / tiles_c;
+        if (q != coef_of) {                                      // uniform over the CTA
+            if (tid < TS && ct * TS + tid < a.channels) {
+                const uint32_t c = ct * TS + tid;
+                const size_t unit = static_cast<size_t>(n) * a.groups + c / a.cpg;
+                Moments m{0.f, 0.f, 0.f};
+                for (uint32_t s = 0; s < a.splits; ++s) {        // chunks in order: every CTA gets the same bits
+                    const uint32_t e0 = s * a.chunk_elems, e1 = min(a.slab_elems, e0 + a.chunk_elems);
+                    Moments y;
+                    y.n = e1 > e0 ? static_cast<float>(e1 - e0) : 0.f;
+                    y.mean = a.partial[2 * (unit * a.splits + s)];
+                    y.m2 = a.partial[2 * (unit * a.splits + s) + 1];
+                    m = merge(m, y);
+                }
+                const float var = m.m2 / static_cast<float>(a.slab_elems);
+                coef[tid] = make_float4(m.mean, 1.0f / sqrtf(var + a.eps), __ldg(a.w + c), __ldg(a.b + c));
+            }
+            coef_of = q;
+        }
+        asm volatile("cp.async.wait_group 1;" ::: "memory");
+        __syncthreads();                                         // the tile has landed; coef is written
+        const uint32_t c = ct * TS + 2 * tx;
+        const float4 k0 = coef[2 * tx], k1 = coef[2 * tx + 1];   // this thread's two channels
+        T *y = static_cast<T *>(a.out) + n * image;
+#pragma unroll
+        for (int r = ty; r < TS; r += 8) {
+            const uint32_t p = pt * TS + r;
+            if (p < hw && c < a.channels) {
+                const float v0 = activate<ACT, HALF>(fmaf((to_float<T>(tile[buf][2 * tx][r]) - k0.x) * k0.y, k0.z, k0.w));
+                const float v1 = activate<ACT, HALF>(fmaf((to_float<T>(tile[buf][2 * tx + 1][r]) - k1.x) * k1.y, k1.z, k1.w));
+                T *dst = y + static_cast<size_t>(p) * a.channels + c;
+                if (HALF) *reinterpret_cast<__half2 *>(dst) = __floats2half2_rn(v0, v1);
+                else *reinterpret_cast<float2 *>(dst) = make_float2(v0, v1);
+            }
+        }
+        __syncthreads();      // tile[buf] is the target of the copies issued next time round; coef may change
+    }
+}
+
 // ---------------------------------------------------------------------------------------------
 // Stand-alone kernels for the reference's three-launch sequence
 // ---------------------------------------------------------------------------------------------
@@ -324,9 +410,13 @@ cudaError_t gn_split_launch(const GnShape &s, const GnPlan &plan, const void *in
         if (tgrid.y > 65535) return cudaErrorInvalidValue;
         const dim3 tblock(32, 8);
         const uint32_t hw32 = static_cast<uint32_t>(s.hw);
+        const unsigned tiles_c = static_cast<unsigned>((s.channels + 63) / 64), tiles_p = static_cast<unsigned>((s.hw + 63) / 64);
+        const unsigned long long total = static_cast<unsigned long long>(s.batch) * tiles_c * tiles_p;
+        const size_t asmem = 2 * esz * 64 * (64 + (esz == 2 ? 2 : 1)) + 64 * sizeof(float4);
+        const unsigned agrid = static_cast<unsigned>(total < 148ull * 6 ? total : 148ull * 6);
 #define SDFL_NHWC_APPLY(T, ACT)                                                              \
         do {                                                                                 \
-            if (pairs) gn_apply_nhwc_kernel<T, ACT, true><<<tgrid, tblock, 0, stream>>>(a, hw32);   \
+            if (pairs) gn_apply_nhwc_async_kernel<T, ACT><<<agrid, tblock, asmem, stream>>>(a, hw32, tiles_c, tiles_p, total); \
             else gn_apply_nhwc_kernel<T, ACT, false><<<tgrid, tblock, 0, stream>>>(a, hw32);        \
         } while (0)
         if (s.dtype == kF16) {
