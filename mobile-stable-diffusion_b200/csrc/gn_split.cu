@@ -46,7 +46,35 @@ __global__ void __launch_bounds__(kSplitThreads) gn_split_stats_kernel(const Spl
                                  static_cast<size_t>(unit / a.groups) * a.channels + (unit % a.groups) * a.cpg
                            : nullptr;
     Shifted sh{0.f, 0.f, 0.f, 0.f};
-    if (a.vec) {
+    Moments m{0.f, 0.f, 0.f};
+    if (a.vec && !erow) {
+        // Shifted sums with the thread's first value as pivot, four independent 16-byte loads in
+        // flight per thread, as in the cluster kernel.
+        const uint4 *xv = reinterpret_cast<const uint4 *>(x);
+        const uint32_t i1 = e1 / VEC;
+        float shift = 0.f;
+        float s[2] = {0.f, 0.f}, q[2] = {0.f, 0.f};
+        uint32_t mine = 0, i = e0 / VEC + threadIdx.x;
+        if (i < i1) shift = to_float<T>(reinterpret_cast<const T *>(xv + i)[0]);
+        for (; i + 3 * kSplitThreads < i1; i += 4 * kSplitThreads) {
+            const uint4 v0 = __ldg(xv + i), v1 = __ldg(xv + i + kSplitThreads);
+            const uint4 v2 = __ldg(xv + i + 2 * kSplitThreads), v3 = __ldg(xv + i + 3 * kSplitThreads);
+            stats_vec<T>(v0, shift, s, q);
+            stats_vec<T>(v1, shift, s, q);
+            stats_vec<T>(v2, shift, s, q);
+            stats_vec<T>(v3, shift, s, q);
+            mine += 4;
+        }
+        for (; i < i1; i += kSplitThreads) {
+            stats_vec<T>(__ldg(xv + i), shift, s, q);
+            ++mine;
+        }
+        const float cnt = static_cast<float>(mine * VEC);
+        const float ss = s[0] + s[1], qq = q[0] + q[1];
+        m.n = cnt;
+        m.mean = mine ? shift + ss / cnt : 0.f;
+        m.m2 = mine ? fmaxf(qq - ss * ss / cnt, 0.f) : 0.f;
+    } else if (a.vec) {
         const uint4 *xv = reinterpret_cast<const uint4 *>(x);
         for (uint32_t i = e0 / VEC + threadIdx.x; i < e1 / VEC; i += kSplitThreads) {
             float f[VEC];
@@ -62,7 +90,8 @@ __global__ void __launch_bounds__(kSplitThreads) gn_split_stats_kernel(const Spl
         for (uint32_t i = e0 + threadIdx.x; i < e1; i += kSplitThreads)
             sh.add(to_float<T>(x[i]) + (erow ? to_float<T>(erow[a.hw_div.div(i)]) : 0.f));
     }
-    Moments m = warp_merge(sh.done());
+    if (!(a.vec && !erow)) m = sh.done();
+    m = warp_merge(m);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     if (lane == 0) warp_m[warp] = m;
     __syncthreads();
@@ -116,6 +145,7 @@ __global__ void __launch_bounds__(kSplitThreads) gn_split_apply_kernel(const Spl
     if (a.vec) {
         const uint4 *xv = reinterpret_cast<const uint4 *>(x);
         uint4 *yv = reinterpret_cast<uint4 *>(y);
+#pragma unroll 4
         for (uint32_t i = e0 / VEC + threadIdx.x; i < e1 / VEC; i += kSplitThreads) {
             float f[VEC];
             unpack<T>(ld_stream(xv + i), f);
