@@ -63,6 +63,22 @@ def test_argument_validation_needs_no_device():
     assert lib.sdfl_timestep_embedding(A, B, 2, 320, -1.0, 0, None) == cap.ERR_INVALID_VALUE
     assert lib.sdfl_local_reduction_mean(A, B, 4, 0, 0, None) == cap.ERR_INVALID_VALUE
     assert lib.sdfl_host_pipeline_create(None, 1024, 2) == cap.ERR_INVALID_POINTER
+    # the kernels either side of the norms
+    assert lib.sdfl_groupnorm_bias_forward(A, None, B, A, A, 1, 32, 64, 32, 1e-5, 1, 0, None, 0, None) == cap.ERR_INVALID_POINTER
+    assert lib.sdfl_add_layernorm_forward(A, B, None, B, A, A, 4, 64, 1e-5, 0, None) == cap.ERR_INVALID_POINTER
+    assert lib.sdfl_chunkwise_add(A, A, B, 64, 0, 0, None) == cap.ERR_INVALID_VALUE
+    assert lib.sdfl_permute3D__0_2_1(A, A, 2, 4, 6, 0, None) == cap.ERR_OVERLAP          # a transpose cannot run in place
+    assert lib.sdfl_permute3D__0_2_1(A, B, 0, 4, 6, 0, None) == cap.OK
+    assert lib.sdfl_permute_add(A, None, B, 2, 4, 6, 0, None) == cap.ERR_INVALID_POINTER
+    assert lib.sdfl_groupnorm_nhwc_forward(A, A, A, A, 1, 32, 64, 32, 1e-5, 0, 0, None, 0, None) == cap.ERR_OVERLAP
+    assert lib.sdfl_softmax(A, B, -1, 77, 0, None) == cap.ERR_INVALID_VALUE
+    assert lib.sdfl_softmax(A, A + 4, 8, 77, 0, None) == cap.ERR_OVERLAP
+    assert lib.sdfl_softmax(A, A, 0, 77, 0, None) == cap.OK
+    assert lib.sdfl_up_sample_nearest(A, B, 4, 8, 8, 0, 0, None) == cap.ERR_INVALID_VALUE
+    assert lib.sdfl_up_sample_nearest(A, A, 4, 8, 8, 2, 0, None) == cap.ERR_OVERLAP
+    assert lib.sdfl_concat_buffer(A, None, B, 1, 4, 4, 0, None) == cap.ERR_INVALID_POINTER
+    assert lib.sdfl_groupnorm_concat_forward(A, 0, A, 32, B, A, A, 1, 64, 32, 1e-5, 1, 0, None, 0, None) == cap.ERR_INVALID_VALUE
+    assert lib.sdfl_groupnorm_concat_forward(A, 16, None, 16, B, A, A, 1, 64, 32, 1e-5, 1, 0, None, 0, None) == cap.ERR_INVALID_POINTER
 
 
 def test_workspace_query_and_plan_without_device():
