@@ -489,6 +489,18 @@ def op_cases(torch, ops, dev):
     gn("profiling size GN+SiLU f16 [4,128,512,512]", 4, 128, 512, f16, 1e-6)
     gn("GN+SiLU f32 [8,256,256,256]", 8, 256, 256, f32, 1e-6)
 
+    def gn_split(name, B, C, H, dtype, eps):
+        esz = 2 if dtype == f16 else 4
+
+        def make():
+            x = rnd((B, C, H, H), dtype)
+            y = torch.empty_like(x)
+            g, b = 1 + 0.1 * rnd((C,), f32), 0.1 * rnd((C,), f32)
+            return lambda: ops.groupnorm(x, g, b, 32, eps, True, out=y, path=ops.GN_SPLIT)
+        cases.append((name, 2 * B * C * H * H * esz + 2 * C * 4, make, ("gn", B, C, H, eps)))
+
+    gn_split("GN+SiLU f16 [4,128,512,512], split path (two kernels, three passes; any alignment)", 4, 128, 512, f16, 1e-6)
+
     def gn_bias(name, B, C, H, dtype, eps):
         esz = 2 if dtype == f16 else 4
 
@@ -502,6 +514,19 @@ def op_cases(torch, ops, dev):
     gn_bias("next: chunkwise_add+GN+SiLU f16 [2,320,64,64]", 2, 320, 64, f16, 1e-5)
     gn_bias("next: chunkwise_add+GN+SiLU f16 [2,1280,16,16]", 2, 1280, 16, f16, 1e-5)
     gn_bias("next: chunkwise_add+GN+SiLU f16 [8,256,256,256] (large)", 8, 256, 256, f16, 1e-5)
+
+    def chadd(name, B, C, H, dtype):
+        esz = 2 if dtype == f16 else 4
+
+        def make():
+            x = rnd((B, C, H, H), dtype)
+            e = rnd((B, C), dtype)
+            y = torch.empty_like(x)
+            return lambda: ops.chunkwise_add(x, e, H * H, out=y)
+        cases.append((name, 2 * B * C * H * H * esz + B * C * esz, make, ("chadd", B, C, H)))
+
+    chadd("next: chunkwise_add f16 [2,320,64,64]", 2, 320, 64, f16)
+    chadd("next: chunkwise_add f16 [8,256,256,256] (large)", 8, 256, 256, f16)
 
     def gn_nhwc(name, B, C, H, dtype):
         esz = 2 if dtype == f16 else 4
@@ -546,6 +571,18 @@ def op_cases(torch, ops, dev):
     gn_cat("next: concat+GN+SiLU f16 [2,640+320,32,32]", 2, 640, 320, 32, f16)
     gn_cat("next: concat+GN+SiLU f16 [2,320+320,64,64]", 2, 320, 320, 64, f16)
     gn_cat("next: concat+GN+SiLU f16 [8,128+128,256,256] (large)", 8, 128, 128, 256, f16)
+
+    def cat(name, B, C1, C2, H, dtype):
+        esz = 2 if dtype == f16 else 4
+
+        def make():
+            a, c = rnd((B, C1, H, H), dtype), rnd((B, C2, H, H), dtype)
+            y = torch.empty((B, C1 + C2, H, H), device=dev, dtype=dtype)
+            return lambda: ops.concat_channels(a, c, out=y)
+        cases.append((name, 2 * B * (C1 + C2) * H * H * esz, make, ("cat", B, C1, C2, H)))
+
+    cat("next: concat_buffer f16 [2,640+320,32,32]", 2, 640, 320, 32, f16)
+    cat("next: concat_buffer f16 [8,128+128,256,256] (large)", 8, 128, 128, 256, f16)
 
     def ups(name, B, C, H, dtype):
         esz = 2 if dtype == f16 else 4
@@ -719,6 +756,18 @@ def cpu_reference_case(spec) -> dict:
         c = rng.standard_normal((1, C2, H, H), dtype=np.float32)
         g, b = np.ones(C1 + C2, np.float32), np.zeros(C1 + C2, np.float32)
         t = timed(lambda: oracle.group_norm(oracle.concat_buffer(a, c), g, b, 32, 1e-5, True, backend=backend), reps=2)
+        scale, note = float(B), f"one image x {B}"
+    elif kind == "chadd":
+        _, B, C, H = spec
+        x = rng.standard_normal((C, H, H), dtype=np.float32)
+        e = rng.standard_normal(C, dtype=np.float32)
+        t = timed(lambda: oracle.chunkwise_add(x, e, H * H, backend=backend))
+        scale, note = float(B), f"one image x {B}"
+    elif kind == "cat":
+        _, B, C1, C2, H = spec
+        a = rng.standard_normal((1, C1, H, H), dtype=np.float32)
+        c = rng.standard_normal((1, C2, H, H), dtype=np.float32)
+        t = timed(lambda: oracle.concat_buffer(a, c))
         scale, note = float(B), f"one image x {B}"
     elif kind == "ups":
         _, B, C, H = spec

@@ -299,7 +299,10 @@ int sdfl_selftest_bounded_wait(long long limit_cycles, void *stream);
  * models take and return std::vector<float>, JNI boundary).  A pipeline object owns `depth`
  * device staging slots and streams, created once; forward_host copies image slabs in,
  * normalises, and copies out, overlapping the three, and returns when h_out is complete.
- * Host buffers should be page-locked (sdfl_host_alloc) for the copies to overlap. */
+ * Host buffers should be page-locked (sdfl_host_alloc) for the copies to overlap.  gamma and
+ * beta are DEVICE pointers, as everywhere else.  A pipeline belongs to the device that was
+ * current when it was created (calls made with another device current are refused with
+ * SDFL_ERR_INVALID_VALUE) and to one host thread at a time. */
 typedef struct sdfl_host_pipeline sdfl_host_pipeline;
 
 int sdfl_host_pipeline_create(sdfl_host_pipeline **pipe, size_t max_slot_bytes, int depth);

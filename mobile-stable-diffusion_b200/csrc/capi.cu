@@ -322,9 +322,10 @@ int sdfl_groupnorm_plan(int64_t batch, int64_t channels, int64_t hw, int64_t num
     cudaError_t e = sdfl::gn_make_plan(s, aligned, aligned, path, cluster_or_splits, &p);
     if (e == cudaErrorInvalidConfiguration || e == cudaErrorInvalidValue) return SDFL_ERR_UNSUPPORTED;
     if (e != cudaSuccess) return cuda_fail(e);
-    plan[0] = p.path; plan[1] = p.cluster; plan[2] = p.threads; plan[3] = p.splits;
+    plan[0] = p.path; plan[1] = p.cluster; plan[2] = p.threads;
+    plan[3] = p.path == sdfl::kGnSplit ? p.splits : p.nslots;
     plan[4] = static_cast<int64_t>(p.smem); plan[5] = static_cast<int64_t>(p.workspace);
-    plan[6] = p.nclusters; plan[7] = p.chunk_vecs; plan[3] = p.path == sdfl::kGnSplit ? p.splits : p.nslots;
+    plan[6] = p.nclusters; plan[7] = p.chunk_vecs;
     return SDFL_OK;
 }
 
@@ -482,12 +483,17 @@ int sdfl_host_pipeline_create(sdfl_host_pipeline **pipe, size_t max_slot_bytes, 
     if (!pipe) return SDFL_ERR_INVALID_POINTER;
     *pipe = nullptr;
     if (max_slot_bytes == 0 || depth < 1 || depth > 16) return SDFL_ERR_INVALID_VALUE;
-    auto *p = new (std::nothrow) sdfl_host_pipeline;
-    if (!p) return SDFL_ERR_INVALID_VALUE;
+    sdfl_host_pipeline *p = nullptr;
+    try {
+        p = new sdfl_host_pipeline;
+        p->slots.resize(static_cast<size_t>(depth));
+    } catch (...) {              // no exception crosses the C boundary
+        delete p;
+        return cuda_fail(cudaErrorMemoryAllocation);
+    }
     cudaError_t e = cudaGetDevice(&p->device);
     p->slot_bytes = (max_slot_bytes + 255) / 256 * 256;
     p->ws_bytes = 1 << 20;
-    p->slots.resize(static_cast<size_t>(depth));
     for (auto &s : p->slots) {
         if (e == cudaSuccess) e = cudaMalloc(&s.d_in, p->slot_bytes);
         if (e == cudaSuccess) e = cudaMalloc(&s.d_out, p->slot_bytes);
@@ -522,6 +528,10 @@ int sdfl_groupnorm_forward_host_async(sdfl_host_pipeline *pipe, const void *h_in
     int rc = gn_validate(h_in, h_out, gamma, beta, batch, channels, hw, num_groups, eps, dtype);
     if (rc != SDFL_OK) return rc;
     if (batch == 0 || hw == 0) return SDFL_OK;
+    int current = -1;
+    cudaError_t e = cudaGetDevice(&current);
+    if (e != cudaSuccess) return cuda_fail(e);
+    if (current != pipe->device) return SDFL_ERR_INVALID_VALUE;   // the slots live on another device
     // One pipeline step = a run of whole groups of one image, as many as fit a slot (and at
     // most ~32 MiB so that copy-in, kernel and copy-out of different steps overlap).
     const int64_t cpg = channels / num_groups;
@@ -536,7 +546,6 @@ int sdfl_groupnorm_forward_host_async(sdfl_host_pipeline *pipe, const void *h_in
     if (gps > num_groups) gps = num_groups;
     const char *src = static_cast<const char *>(h_in);
     char *dst = static_cast<char *>(h_out);
-    cudaError_t e = cudaSuccess;
     for (int64_t n = 0; n < batch && rc == SDFL_OK && e == cudaSuccess; ++n) {
         for (int64_t g0 = 0; g0 < num_groups; g0 += gps) {
             const int64_t ng = g0 + gps <= num_groups ? gps : num_groups - g0;
