@@ -16,6 +16,10 @@ namespace {
 // Every load of a slab precedes every store to it, so out == in is safe.
 constexpr int kRegThreads = kGnRegThreads;
 constexpr int kRegMaxVecs = kGnRegMaxVecs;
+// A group's scale and shift are fetched together with the slab and parked in shared memory when the
+// group has at most this many channels: fetched after the statistics instead, their DRAM round
+// trip (cold weights: every layer has its own) was 10-20 % of a small launch.
+constexpr uint32_t kRegStagedChannels = 256;
 
 struct RegArgs {
     const void *in;
@@ -48,9 +52,17 @@ gn_register_kernel(const RegArgs a) {
     constexpr int VEC = VecOf<T>::N;
     constexpr bool HALF = sizeof(T) == 2;
     __shared__ Moments warp_m[kRegThreads / 32];
+    __shared__ float s_w[kRegStagedChannels], s_b[kRegStagedChannels];
     extern __shared__ __align__(16) unsigned char tsm[];      // NHWC only: cpg rows of row_bytes
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    const bool staged = a.cpg <= kRegStagedChannels;
     for (uint32_t unit = blockIdx.x; unit < a.units; unit += gridDim.x) {
+        const uint32_t ch0 = (unit % a.groups) * a.cpg;
+        float w_mine = 0.f, b_mine = 0.f;
+        if (staged && tid < a.cpg) {             // in flight together with the slab's loads
+            w_mine = __ldg(a.w + ch0 + tid);
+            b_mine = __ldg(a.b + ch0 + tid);
+        }
         const uint4 *src = reinterpret_cast<const uint4 *>(a.in) + static_cast<size_t>(unit) * a.slab_vecs;
         uint4 *dst = reinterpret_cast<uint4 *>(a.out) + static_cast<size_t>(unit) * a.slab_vecs;
         const T *erow = BIAS ? static_cast<const T *>(a.bias) +
@@ -72,6 +84,10 @@ gn_register_kernel(const RegArgs a) {
         for (int k = 0; k < NVT; ++k) {
             const uint32_t idx = tid + k * kRegThreads;
             if (idx < a.slab_vecs) v[k] = ld_stream((idx < split ? src : src2) + idx);
+        }
+        if (staged && tid < a.cpg) {             // visible after the barrier that follows the moments
+            s_w[tid] = w_mine;
+            s_b[tid] = b_mine;
         }
         // this thread's moments, shifted by its first value
         float s[2] = {0.f, 0.f}, q[2] = {0.f, 0.f};
@@ -120,7 +136,6 @@ gn_register_kernel(const RegArgs a) {
         const float mean = __shfl_sync(0xffffffffu, t.mean, 0);
         const float var = __shfl_sync(0xffffffffu, t.m2, 0) / static_cast<float>(a.slab_elems);   // biased
         const float rstd = 1.0f / sqrtf(var + a.eps);
-        const uint32_t ch0 = (unit % a.groups) * a.cpg;
 #pragma unroll
         for (int k = 0; k < NVT; ++k) {
             const uint32_t idx = tid + k * kRegThreads;
@@ -128,7 +143,8 @@ gn_register_kernel(const RegArgs a) {
                 if (a.vec_uniform) {
                     const uint32_t cl = a.hwv_div.div(idx), c = ch0 + cl;
                     const float mc = BIAS ? mean - to_float<T>(erow[cl]) : mean;
-                    const Affine<T> af = make_affine<T, ACT>(mc, rstd, __ldg(a.w + c), __ldg(a.b + c));
+                    const Affine<T> af = make_affine<T, ACT>(mc, rstd, staged ? s_w[cl] : __ldg(a.w + c),
+                                                            staged ? s_b[cl] : __ldg(a.b + c));
                     const uint4 r = norm_vec<T, ACT>(v[k], af);
                     if (NHWC) {
                         const uint32_t p0 = (idx - cl * a.hw_vecs) * VEC;
@@ -144,7 +160,8 @@ gn_register_kernel(const RegArgs a) {
                     for (int l = 0; l < VEC; ++l) {
                         const uint32_t cl = a.hw_div.div(idx * VEC + l), c = ch0 + cl;
                         const float mc = BIAS ? mean - to_float<T>(erow[cl]) : mean;
-                        f[l] = activate<ACT, HALF>(fmaf((f[l] - mc) * rstd, __ldg(a.w + c), __ldg(a.b + c)));
+                        f[l] = activate<ACT, HALF>(fmaf((f[l] - mc) * rstd, staged ? s_w[cl] : __ldg(a.w + c),
+                                                        staged ? s_b[cl] : __ldg(a.b + c)));
                         if (NHWC) {
                             const uint32_t p = idx * VEC + l - cl * a.hw;
                             *reinterpret_cast<T *>(tsm + cl * a.row_bytes + p * sizeof(T)) = from_float<T>(f[l]);
