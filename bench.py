@@ -501,6 +501,25 @@ def op_cases(torch, ops, dev):
 
     gn_split("GN+SiLU f16 [4,128,512,512], split path (two kernels, three passes; any alignment)", 4, 128, 512, f16, 1e-6)
 
+    def gn_by_name(name, B, C, H, dtype, eps):
+        esz = 2 if dtype == f16 else 4
+
+        def make():
+            x = rnd((B, C, H, H), dtype)
+            y = torch.empty_like(x)
+            g, b = 1 + 0.1 * rnd((C,), f32), 0.1 * rnd((C,), f32)
+
+            def run():
+                mean = ops.local_reduction_mean(x, B * 32)
+                var = ops.local_reduction_variance(x, mean, B * 32)
+                ops.group_norm_apply(x, mean, var, g, b, (C // 32) * H * H, H * H, eps, C, out=y)
+                ops.silu(y, out=y)
+            return run
+        cases.append((name, 2 * B * C * H * H * esz + 2 * C * 4, make, ("gn", B, C, H, eps)))
+
+    gn_by_name("kernel by kernel (4 launches, 6 passes): mean, variance, group_norm, silu f32 [1,320,64,64]", 1, 320, 64, f32, 1e-5)
+    gn_by_name("kernel by kernel (4 launches, 6 passes): mean, variance, group_norm, silu f16 [8,256,256,256]", 8, 256, 256, f16, 1e-6)
+
     def gn_bias(name, B, C, H, dtype, eps):
         esz = 2 if dtype == f16 else 4
 

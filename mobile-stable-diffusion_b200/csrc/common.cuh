@@ -66,14 +66,6 @@ __device__ __forceinline__ uint4 ld_stream(const void *p) {
 __device__ __forceinline__ void st_stream(void *p, const uint4 &v) {
     __stcs(reinterpret_cast<uint4 *>(p), v);
 }
-// Asynchronous 16-byte copy global -> shared (both 16-byte aligned); completion through
-// cp.async.commit_group / wait_group.  No register holds the data in flight.
-__device__ __forceinline__ void cp_async16(void *smem_dst, const void *gsrc) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(
-                     static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst))),
-                 "l"(gsrc)
-                 : "memory");
-}
 
 // ---------------------------------------------------------------------------------------------
 // Activations.  exp2 / reciprocal use the SFU approximations (relative error ~2^-22), which is

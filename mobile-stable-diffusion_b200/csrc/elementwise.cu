@@ -1,6 +1,6 @@
 // Flat elementwise kernels: GEGLU gate (geglu.cl:1-25), gelu (util.cl:104-122), silu
 // (util.cl:124-134), quick_gelu (no reference kernel; silu's form with slope 1.702) and
-// elemwise_add (util.cl:1-12).  fp32 or fp16 I/O, fp32 arithmetic, 16-byte accesses when the
+// elemwise_add (util.cl:1-12), chunkwise_add (util.cl:136-148).  fp32 or fp16 I/O, fp32 arithmetic, 16-byte accesses when the
 // pointers and extents allow it, scalar otherwise.  src == dst is allowed for the unary ops.
 #include "common.cuh"
 #include "kernels.h"
@@ -173,15 +173,70 @@ cudaError_t add_dispatch(const void *a, const void *b, void *c, int64_t n, cudaS
     return err;
 }
 
-// ---- C[i] = A[i] + chunk[i / chunk_size] ------------------------------------------------------
+// ---- C[i] = A[i] + chunk[i / chunk_size]  (util.cl:136-148) -----------------------------------
+// Vector form: chunk_size is a multiple of the vector width, so a 16-byte vector lies inside one
+// chunk and its addend index is one division of the vector index (multiply-high while the vector
+// count fits 31 bits, a 64-bit division per vector beyond that).
+template <typename T, bool WIDE>
+__global__ void __launch_bounds__(kEwThreads)
+chunkwise_add_vec_kernel(const uint4 *a, const T *__restrict__ chunk, uint4 *c, long long nvec,
+                         FastDiv chunk_div, unsigned long long chunk_vecs) {
+    constexpr int VEC = VecOf<T>::N;
+    const long long stride = static_cast<long long>(gridDim.x) * kEwThreads;
+    for (long long i = static_cast<long long>(blockIdx.x) * kEwThreads + threadIdx.x; i < nvec;
+         i += stride) {
+        const unsigned long long k = WIDE ? static_cast<unsigned long long>(i) / chunk_vecs
+                                          : chunk_div.div(static_cast<uint32_t>(i));
+        const float e = to_float<T>(__ldg(chunk + k));
+        float x[VEC];
+        unpack<T>(ld_stream(a + i), x);
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) x[j] = x[j] + e;
+        st_stream(c + i, pack<T>(x));
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kEwThreads)
-chunkwise_add_kernel(const T *a, const T *__restrict__ chunk, T *c, unsigned long long n,
-                     unsigned long long chunk_size) {
+chunkwise_add_kernel(const T *a, const T *__restrict__ chunk, T *c, unsigned long long first,
+                     unsigned long long n, unsigned long long chunk_size) {
     const unsigned long long stride = static_cast<unsigned long long>(gridDim.x) * kEwThreads;
-    for (unsigned long long i = static_cast<unsigned long long>(blockIdx.x) * kEwThreads + threadIdx.x;
+    for (unsigned long long i = first + static_cast<unsigned long long>(blockIdx.x) * kEwThreads + threadIdx.x;
          i < n; i += stride)
         c[i] = from_float<T>(to_float<T>(a[i]) + to_float<T>(chunk[i / chunk_size]));
+}
+
+template <typename T>
+cudaError_t chunkwise_add_dispatch(const void *a, const void *chunk, void *c, int64_t n,
+                                   int64_t chunk_size, cudaStream_t stream) {
+    constexpr int VEC = VecOf<T>::N;
+    int launches = 0;
+    int64_t done = 0;
+    if (aligned16(a) && aligned16(c) && chunk_size % VEC == 0 && n >= VEC) {
+        const int64_t nvec = n / VEC, chunk_vecs = chunk_size / VEC;
+        const bool wide = nvec >= (1ll << 31) || chunk_vecs >= (1ll << 31);
+        const FastDiv cdiv = FastDiv::make(static_cast<uint32_t>(wide ? 1 : chunk_vecs));
+        if (wide)
+            chunkwise_add_vec_kernel<T, true><<<ew_grid(nvec), kEwThreads, 0, stream>>>(
+                static_cast<const uint4 *>(a), static_cast<const T *>(chunk), static_cast<uint4 *>(c), nvec, cdiv,
+                static_cast<unsigned long long>(chunk_vecs));
+        else
+            chunkwise_add_vec_kernel<T, false><<<ew_grid(nvec), kEwThreads, 0, stream>>>(
+                static_cast<const uint4 *>(a), static_cast<const T *>(chunk), static_cast<uint4 *>(c), nvec, cdiv,
+                static_cast<unsigned long long>(chunk_vecs));
+        done = nvec * VEC;
+        ++launches;
+    }
+    if (done < n) {
+        chunkwise_add_kernel<T><<<ew_grid(n - done), kEwThreads, 0, stream>>>(
+            static_cast<const T *>(a), static_cast<const T *>(chunk), static_cast<T *>(c),
+            static_cast<unsigned long long>(done), static_cast<unsigned long long>(n),
+            static_cast<unsigned long long>(chunk_size));
+        ++launches;
+    }
+    cudaError_t err = cudaGetLastError();
+    if (err == cudaSuccess) g_launches.fetch_add(launches);
+    return err;
 }
 
 }  // namespace
@@ -189,15 +244,8 @@ chunkwise_add_kernel(const T *a, const T *__restrict__ chunk, T *c, unsigned lon
 cudaError_t chunkwise_add_launch(const void *a, const void *chunk, void *c, int64_t n,
                                  int64_t chunk_size, int dtype, cudaStream_t stream) {
     if (n == 0) return cudaSuccess;
-    if (dtype == kF16)
-        chunkwise_add_kernel<__half><<<ew_grid(n), kEwThreads, 0, stream>>>(
-            static_cast<const __half *>(a), static_cast<const __half *>(chunk), static_cast<__half *>(c), n, chunk_size);
-    else
-        chunkwise_add_kernel<float><<<ew_grid(n), kEwThreads, 0, stream>>>(
-            static_cast<const float *>(a), static_cast<const float *>(chunk), static_cast<float *>(c), n, chunk_size);
-    cudaError_t err = cudaGetLastError();
-    if (err == cudaSuccess) g_launches.fetch_add(1);
-    return err;
+    return dtype == kF16 ? chunkwise_add_dispatch<__half>(a, chunk, c, n, chunk_size, stream)
+                         : chunkwise_add_dispatch<float>(a, chunk, c, n, chunk_size, stream);
 }
 
 cudaError_t act_launch(int act, const void *src, void *dst, int64_t n, int dtype, cudaStream_t stream) {

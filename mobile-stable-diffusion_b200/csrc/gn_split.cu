@@ -367,7 +367,107 @@ stats_kernel(const T *__restrict__ in, const float *__restrict__ mean, float *__
     if (threadIdx.x == 0) out[blockIdx.x] = t / static_cast<float>(n);
 }
 
+// The same for 16-byte aligned groups whose length is a multiple of the vector width: a thread-block
+// cluster of S CTAs per group (S = 1, 2, 4 or 8, chosen so that the grid fills the SMs even with 32
+// groups), each CTA sums its share with four 16-byte loads in flight per thread, and rank 0 folds
+// the S partial sums in rank order through distributed shared memory -- no scratch buffer, no
+// atomics, the same bits on every run.
+template <typename T>
+__global__ void __launch_bounds__(kStatsThreads)
+stats_vec_kernel(const uint4 *__restrict__ in, const float *__restrict__ mean, float *__restrict__ out,
+                 unsigned long long nvec) {
+    constexpr int VEC = VecOf<T>::N;
+    __shared__ float red[33];
+    __shared__ float cta_sum;
+    cg::cluster_group cluster = cg::this_cluster();
+    const unsigned S = cluster.num_blocks(), rank = cluster.block_rank();
+    const unsigned long long group = blockIdx.x / S;
+    const uint4 *x = in + group * nvec;
+    const unsigned long long v0 = nvec * rank / S, v1 = nvec * (rank + 1) / S;
+    const bool var = mean != nullptr;
+    const float m = var ? mean[group] : 0.f;
+    float acc[2] = {0.f, 0.f};
+    auto fold = [&](const uint4 &v) {
+        float f[VEC];
+        unpack<T>(v, f);
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) {
+            const float d = f[j] - m;              // m = 0 for the mean
+            acc[j & 1] = var ? fmaf(d, d, acc[j & 1]) : acc[j & 1] + d;
+        }
+    };
+    unsigned long long i = v0 + threadIdx.x;
+    for (; i + 3ull * kStatsThreads < v1; i += 4ull * kStatsThreads) {
+        const uint4 a0 = ld_stream(x + i), a1 = ld_stream(x + i + kStatsThreads);
+        const uint4 a2 = ld_stream(x + i + 2 * kStatsThreads), a3 = ld_stream(x + i + 3 * kStatsThreads);
+        fold(a0); fold(a1); fold(a2); fold(a3);
+    }
+    for (; i < v1; i += kStatsThreads) fold(ld_stream(x + i));
+    const float t = block_sum(acc[0] + acc[1], red);
+    if (S == 1) {
+        if (threadIdx.x == 0) out[group] = t / static_cast<float>(nvec * VEC);
+        return;
+    }
+    if (threadIdx.x == 0) cta_sum = t;
+    cluster.sync();                                  // every CTA's partial sum is in its shared memory
+    if (rank == 0 && threadIdx.x == 0) {
+        float total = 0.f;
+        for (unsigned r = 0; r < S; ++r) total += *cluster.map_shared_rank(&cta_sum, r);
+        out[group] = total / static_cast<float>(nvec * VEC);
+    }
+    cluster.sync();                                  // nobody leaves while rank 0 still reads
+}
+
 // group_norm.cl:59-76 with the weight index wrapped per image: c = (i / channelSize) % C.
+// Vector form (16-byte aligned, group and channel sizes multiples of the vector width, fewer than
+// 2^31 vectors): the group and channel of a vector by multiply-high divisions, one reciprocal
+// square root per vector.
+template <typename T>
+__global__ void __launch_bounds__(256)
+gn_apply_vec_kernel(const uint4 *__restrict__ in, const float *__restrict__ mean, const float *__restrict__ var,
+                    const float *__restrict__ w, const float *__restrict__ b, FastDiv group_div, FastDiv chan_div,
+                    FastDiv wrap_div, float eps, uint4 *__restrict__ out, uint32_t nvec) {
+    constexpr int VEC = VecOf<T>::N;
+    for (uint32_t i = blockIdx.x * 256u + threadIdx.x; i < nvec; i += gridDim.x * 256u) {
+        const uint32_t g = group_div.div(i);
+        const uint32_t q = chan_div.div(i);
+        const uint32_t c = q - wrap_div.div(q) * wrap_div.d;
+        const float mu = __ldg(mean + g), inv = 1.0f / sqrtf(__ldg(var + g) + eps);
+        const float wc = __ldg(w + c), bc = __ldg(b + c);
+        float f[VEC];
+        unpack<T>(ld_stream(in + i), f);
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) f[j] = fmaf((f[j] - mu) * inv, wc, bc);
+        st_stream(out + i, pack<T>(f));
+    }
+}
+
+// layer_norm.cl:63-78, vector form: dim a multiple of the vector width, everything 16-byte aligned.
+template <typename T>
+__global__ void __launch_bounds__(256)
+ln_apply_vec_kernel(const uint4 *__restrict__ in, const float *__restrict__ mean, const float *__restrict__ var,
+                    const float *__restrict__ w, const float *__restrict__ b, FastDiv row_div, float eps,
+                    uint4 *__restrict__ out, uint32_t nvec) {
+    constexpr int VEC = VecOf<T>::N;
+    for (uint32_t i = blockIdx.x * 256u + threadIdx.x; i < nvec; i += gridDim.x * 256u) {
+        const uint32_t r = row_div.div(i);
+        const uint32_t k = (i - r * row_div.d) * VEC;
+        const float mu = __ldg(mean + r), inv = 1.0f / sqrtf(__ldg(var + r) + eps);
+        float f[VEC], wk[VEC], bk[VEC];
+        unpack<T>(ld_stream(in + i), f);
+#pragma unroll
+        for (int j = 0; j < VEC; j += 4) {
+            const float4 w4 = __ldg(reinterpret_cast<const float4 *>(w + k + j));
+            const float4 b4 = __ldg(reinterpret_cast<const float4 *>(b + k + j));
+            wk[j] = w4.x; wk[j + 1] = w4.y; wk[j + 2] = w4.z; wk[j + 3] = w4.w;
+            bk[j] = b4.x; bk[j + 1] = b4.y; bk[j + 2] = b4.z; bk[j + 3] = b4.w;
+        }
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) f[j] = fmaf((f[j] - mu) * inv, wk[j], bk[j]);
+        st_stream(out + i, pack<T>(f));
+    }
+}
+
 template <typename T>
 __global__ void gn_apply_kernel(const T *__restrict__ in, const float *__restrict__ mean,
                                 const float *__restrict__ var, const float *__restrict__ w,
@@ -514,32 +614,44 @@ cudaError_t gn_launch_static_scratch(const GnShape &s, const GnPlan &plan, const
     return gn_launch(s, plan, in, out, w, b, ptr, stream, nullptr);
 }
 
+namespace {
+// mean (mean == nullptr) or variance of `groups` runs of n elements.
+template <typename T>
+cudaError_t stats_launch(const void *in, const float *mean, float *out, int64_t groups, int64_t n,
+                         cudaStream_t stream) {
+    constexpr int VEC = VecOf<T>::N;
+    cudaError_t err;
+    if (gn_aligned16(in) && n % VEC == 0 && n >= VEC) {
+        // cluster size: up to eight CTAs of 256 threads per SM, at least 8 vectors per thread
+        int S = 1;
+        while (S < 8 && groups * S * 2 <= 8 * 148 && n / VEC / (S * 2) >= 8 * kStatsThreads) S *= 2;
+        cudaLaunchConfig_t cfg;
+        cudaLaunchAttribute attr[1];
+        cluster_config(&cfg, attr, static_cast<unsigned>(groups * S), S, kStatsThreads, 0, stream);
+        err = cudaLaunchKernelEx(&cfg, stats_vec_kernel<T>, static_cast<const uint4 *>(in), mean, out,
+                                 static_cast<unsigned long long>(n / VEC));
+    } else {
+        stats_kernel<T><<<static_cast<unsigned>(groups), kStatsThreads, 0, stream>>>(
+            static_cast<const T *>(in), mean, out, n);
+        err = cudaGetLastError();
+    }
+    if (err == cudaSuccess) g_launches.fetch_add(1);
+    return err;
+}
+}  // namespace
+
 cudaError_t stats_mean_launch(const void *in, float *out, int64_t groups, int64_t n, int dtype,
                               cudaStream_t stream) {
     if (groups == 0) return cudaSuccess;
-    if (dtype == kF16)
-        stats_kernel<__half><<<static_cast<unsigned>(groups), kStatsThreads, 0, stream>>>(
-            static_cast<const __half *>(in), nullptr, out, n);
-    else
-        stats_kernel<float><<<static_cast<unsigned>(groups), kStatsThreads, 0, stream>>>(
-            static_cast<const float *>(in), nullptr, out, n);
-    cudaError_t err = cudaGetLastError();
-    if (err == cudaSuccess) g_launches.fetch_add(1);
-    return err;
+    return dtype == kF16 ? stats_launch<__half>(in, nullptr, out, groups, n, stream)
+                         : stats_launch<float>(in, nullptr, out, groups, n, stream);
 }
 
 cudaError_t stats_var_launch(const void *in, const float *mean, float *out, int64_t groups,
                              int64_t n, int dtype, cudaStream_t stream) {
     if (groups == 0) return cudaSuccess;
-    if (dtype == kF16)
-        stats_kernel<__half><<<static_cast<unsigned>(groups), kStatsThreads, 0, stream>>>(
-            static_cast<const __half *>(in), mean, out, n);
-    else
-        stats_kernel<float><<<static_cast<unsigned>(groups), kStatsThreads, 0, stream>>>(
-            static_cast<const float *>(in), mean, out, n);
-    cudaError_t err = cudaGetLastError();
-    if (err == cudaSuccess) g_launches.fetch_add(1);
-    return err;
+    return dtype == kF16 ? stats_launch<__half>(in, mean, out, groups, n, stream)
+                         : stats_launch<float>(in, mean, out, groups, n, stream);
 }
 
 static unsigned flat_grid(int64_t n, int threads) {
@@ -554,6 +666,24 @@ cudaError_t gn_apply_launch(const void *in, const float *mean, const float *var,
                             const float *b, int64_t group_size, int64_t channel_size, float eps,
                             void *out, int64_t n, int64_t channels, int dtype, cudaStream_t stream) {
     if (n == 0) return cudaSuccess;
+    const int64_t vec = dtype == kF16 ? 8 : 4;
+    if (gn_aligned16(in) && gn_aligned16(out) && n % vec == 0 && group_size % vec == 0 &&
+        channel_size % vec == 0 && n / vec < (1ll << 31) && channels < (1ll << 31)) {
+        const uint32_t nvec = static_cast<uint32_t>(n / vec);
+        const FastDiv gd = FastDiv::make(static_cast<uint32_t>(group_size / vec));
+        const FastDiv cd = FastDiv::make(static_cast<uint32_t>(channel_size / vec));
+        const FastDiv wd = FastDiv::make(static_cast<uint32_t>(channels));
+        const unsigned vgrid = flat_grid(nvec, 256);
+        if (dtype == kF16)
+            gn_apply_vec_kernel<__half><<<vgrid, 256, 0, stream>>>(static_cast<const uint4 *>(in), mean, var, w, b, gd,
+                                                                  cd, wd, eps, static_cast<uint4 *>(out), nvec);
+        else
+            gn_apply_vec_kernel<float><<<vgrid, 256, 0, stream>>>(static_cast<const uint4 *>(in), mean, var, w, b, gd,
+                                                                 cd, wd, eps, static_cast<uint4 *>(out), nvec);
+        cudaError_t verr = cudaGetLastError();
+        if (verr == cudaSuccess) g_launches.fetch_add(1);
+        return verr;
+    }
     const unsigned grid = flat_grid(n, 256);
     if (dtype == kF16)
         gn_apply_kernel<__half><<<grid, 256, 0, stream>>>(
@@ -572,6 +702,22 @@ cudaError_t ln_apply_launch(const void *in, const float *mean, const float *var,
                             const float *b, int64_t dim, float eps, void *out, int64_t n, int dtype,
                             cudaStream_t stream) {
     if (n == 0) return cudaSuccess;
+    const int64_t vec = dtype == kF16 ? 8 : 4;
+    if (gn_aligned16(in) && gn_aligned16(out) && gn_aligned16(w) && gn_aligned16(b) && n % vec == 0 &&
+        dim % vec == 0 && n / vec < (1ll << 31)) {
+        const uint32_t nvec = static_cast<uint32_t>(n / vec);
+        const FastDiv rd = FastDiv::make(static_cast<uint32_t>(dim / vec));
+        const unsigned vgrid = flat_grid(nvec, 256);
+        if (dtype == kF16)
+            ln_apply_vec_kernel<__half><<<vgrid, 256, 0, stream>>>(static_cast<const uint4 *>(in), mean, var, w, b, rd,
+                                                                  eps, static_cast<uint4 *>(out), nvec);
+        else
+            ln_apply_vec_kernel<float><<<vgrid, 256, 0, stream>>>(static_cast<const uint4 *>(in), mean, var, w, b, rd,
+                                                                 eps, static_cast<uint4 *>(out), nvec);
+        cudaError_t verr = cudaGetLastError();
+        if (verr == cudaSuccess) g_launches.fetch_add(1);
+        return verr;
+    }
     const unsigned grid = flat_grid(n, 256);
     if (dtype == kF16)
         ln_apply_kernel<__half><<<grid, 256, 0, stream>>>(

@@ -115,10 +115,10 @@ constexpr int ln_min_blocks_r(int maxv, int rows_per_warp) {
 // reference's two steps (elemwise_add, then layer_norm on what was stored).
 // Scale and shift are fp32 (2 x 4 bytes per element against 2 bytes of fp16 data): read through
 // L1 for every row they saturate the L1 data path, so each CTA first copies them to shared
-// memory (dynamic, 2 * dim floats) and every row reads them from there.  The copy is a cp.async
-// that is waited for only in front of a warp's first normalise step: the first rows' loads and
-// statistics run beside it instead of behind it (a cold DRAM round trip, 10-20 % of a small
-// launch).  Every warp passes the named barrier exactly once, wherever its row loop stands.
+// memory (dynamic, 2 * dim floats) and every row reads them from there.  (Tried: the copy as a
+// cp.async waited for, with a CTA barrier, only in front of each warp's first normalise step, so
+// that the first rows load beside it.  With the weights in L2 it was 1-6 % slower, same GPU, same
+// session: the barrier then sits behind the row loads and every warp waits for the slowest.)
 template <typename T, int MAXV, bool ADD, int R>
 __global__ void __launch_bounds__(kLnThreads, ln_min_blocks_r(MAXV, R))
 ln_warp_kernel(const T *in, const T *in2, T *sum_out, T *out, const float *__restrict__ gw,
@@ -127,16 +127,10 @@ ln_warp_kernel(const T *in, const T *in2, T *sum_out, T *out, const float *__res
     extern __shared__ __align__(16) float s_wb[];
     float *w = s_wb, *b = s_wb + dim;
     for (int i = threadIdx.x; i < dim / 4; i += kLnThreads) {
-        cp_async16(w + 4 * i, gw + 4 * i);
-        cp_async16(b + 4 * i, gb + 4 * i);
+        reinterpret_cast<float4 *>(w)[i] = __ldg(reinterpret_cast<const float4 *>(gw) + i);
+        reinterpret_cast<float4 *>(b)[i] = __ldg(reinterpret_cast<const float4 *>(gb) + i);
     }
-    asm volatile("cp.async.commit_group;" ::: "memory");
-    bool staged = false;                      // warp-uniform
-    auto wait_staged = [&]() {
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
-        asm volatile("bar.sync 1, %0;" ::"n"(kLnThreads) : "memory");
-        staged = true;
-    };
+    __syncthreads();
     const int lane = threadIdx.x & 31;
     const long long warp0 = static_cast<long long>(blockIdx.x) * kLnWarps + (threadIdx.x >> 5);
     const long long nwarps = static_cast<long long>(gridDim.x) * kLnWarps;
@@ -181,7 +175,6 @@ ln_warp_kernel(const T *in, const T *in2, T *sum_out, T *out, const float *__res
             const float var = warp_sum(q[0] + q[1]) * inv_d;
             rstd[r] = 1.0f / sqrtf(var + eps);
         }
-        if (!staged) wait_staged();
 #pragma unroll
         for (int i = 0; i < MAXV; ++i) {
             const int idx = lane + 32 * i;
@@ -195,7 +188,6 @@ ln_warp_kernel(const T *in, const T *in2, T *sum_out, T *out, const float *__res
             }
         }
     }
-    if (!staged) wait_staged();               // a warp without rows still owes the barrier its arrival
 }
 
 // Any D, any alignment: one CTA per row (grid-stride), three reads of the row.

@@ -99,3 +99,31 @@ def test_full_size_geglu_fp16_properties(sdfl):
     assert float((diff - 2e-3 * want.abs()).max()) <= 2e-3
     rows = oracle.gelu_multiply(ab[0, :16].cpu().numpy().astype(np.float32))
     assert_close(to_np(y[0, :16]), rows, TOL["float16"], "first rows vs oracle")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "float16"])
+@pytest.mark.parametrize("n,chunk_size,misalign", [
+    (320 * 4096, 4096, 0),        # the time-embedding add of a ResBlock: [320, 64, 64] + [320]
+    (1280 * 64, 64, 0),
+    (40 * 72, 72, 0),             # chunk a multiple of the vector width, vector kernel
+    (40 * 72 + 5, 72, 0),         # ... with a scalar tail (the last chunk is ragged)
+    (33 * 77, 77, 0),             # chunk not a multiple of the vector width: scalar kernel
+    (40 * 72, 72, 1),             # unaligned buffers: scalar kernel
+    (7, 3, 0), (1, 1, 0),
+])
+def test_chunkwise_add_is_bit_exact(sdfl, n, chunk_size, misalign, dtype):
+    """chunkwise_add (util.cl:136-148): C[i] = A[i] + chunk[i / chunk_size], one rounding."""
+    rng = rng_for(2, 4000 + n % 991 + chunk_size)
+    nchunks = -(-n // chunk_size)
+    a = rng.standard_normal(n).astype(np.float32).astype(NP_DTYPE[dtype])
+    e = rng.standard_normal(nchunks).astype(np.float32).astype(NP_DTYPE[dtype])
+    want = oracle.chunkwise_add(a.astype(np.float32), e.astype(np.float32), chunk_size).astype(NP_DTYPE[dtype])
+    src = Guarded((n,), getattr(torch, dtype), misalign=misalign)
+    src.tensor.copy_(to_dev(a))
+    out = Guarded((n,), getattr(torch, dtype), misalign=misalign)
+    sdfl.ops.chunkwise_add(src.tensor, to_dev(e), chunk_size, out=out.tensor)
+    out.check()
+    assert_bit_equal(to_np(out.tensor), want, f"chunkwise_add n={n} chunk={chunk_size} {dtype}")
+    sdfl.ops.chunkwise_add(src.tensor, to_dev(e), chunk_size, out=src.tensor)     # in place, as the reference does
+    src.check()
+    assert_bit_equal(to_np(src.tensor), want, "chunkwise_add in place")

@@ -133,3 +133,51 @@ def test_add_layernorm_rejects_out_overlapping_the_sum(sdfl):
     with pytest.raises(sdfl.SdflError) as e:
         sdfl.ops.add_layernorm(a, torch.zeros_like(a), g, g, sum_out=a, out=a)
     assert e.value.status == sdfl._capi.ERR_OVERLAP
+
+
+@pytest.mark.parametrize("dtype", ["float32", "float16"])
+@pytest.mark.parametrize("shape,groups,misalign", [
+    ((1, 320, 64, 64), 32, 0),      # 32 groups: a cluster of CTAs per group
+    ((2, 64, 16, 16), 32, 0),       # one CTA per group, vector loads
+    ((2, 64, 5, 7), 32, 0),         # 35-pixel channels: element-wise kernels
+    ((2, 64, 16, 16), 32, 1),       # unaligned buffers: element-wise kernels
+])
+def test_groupnorm_kernel_by_kernel_all_layouts(sdfl, shape, groups, misalign, dtype):
+    """local_reduction_mean -> local_reduction_variance -> group_norm (group_norm.cl:1-76) at
+    shapes that reach the clustered, the vector and the element-wise forms of the kernels."""
+    rng = rng_for(1, 60 + sum(shape) + misalign)
+    B, C = shape[:2]
+    hw = int(np.prod(shape[2:]))
+    x = (rng.standard_normal(shape) * 1.5 + 0.3).astype(np.float32).astype(NP_DTYPE[dtype])
+    g = (1 + 0.1 * rng.standard_normal(C)).astype(np.float32)
+    b = (0.1 * rng.standard_normal(C)).astype(np.float32)
+    want, wmean, wvar = oracle.group_norm(x.astype(np.float32), g, b, groups, 1e-5, False, return_stats=True)
+    src = Guarded(shape, getattr(torch, dtype), misalign=misalign)
+    src.tensor.copy_(to_dev(x))
+    mean = sdfl.ops.local_reduction_mean(src.tensor, B * groups)
+    var = sdfl.ops.local_reduction_variance(src.tensor, mean, B * groups)
+    assert_close(to_np(mean), wmean.reshape(-1), 1e-5, "group means")
+    assert_close(to_np(var), wvar.reshape(-1), 1e-5, "group variances")
+    out = Guarded(shape, getattr(torch, dtype), misalign=misalign)
+    sdfl.ops.group_norm_apply(src.tensor, mean, var, to_dev(g), to_dev(b), group_size=(C // groups) * hw,
+                              channel_size=hw, eps=1e-5, num_channels=C, out=out.tensor)
+    out.check()
+    assert_close(to_np(out.tensor), want, TOL[dtype], f"group_norm kernel {shape} {dtype}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "float16"])
+@pytest.mark.parametrize("rows,D,misalign", [(8192, 320, 0), (154, 768, 0), (33, 77, 0), (64, 320, 1)])
+def test_layernorm_kernel_by_kernel_all_layouts(sdfl, rows, D, misalign, dtype):
+    """local_reduction_mean -> local_reduction_variance -> layer_norm (layer_norm.cl:1-78)."""
+    x, gamma, beta = ln_inputs(rng_for(2, 90 + rows + D + misalign), rows, D, dtype, mean=0.2, std=1.3)
+    want, wmean, wvar = oracle.layer_norm(x.astype(np.float32), gamma, beta, 1e-5, return_stats=True)
+    src = Guarded((rows, D), getattr(torch, dtype), misalign=misalign)
+    src.tensor.copy_(to_dev(x))
+    mean = sdfl.ops.local_reduction_mean(src.tensor, rows)
+    var = sdfl.ops.local_reduction_variance(src.tensor, mean, rows)
+    assert_close(to_np(mean), wmean.reshape(-1), 1e-5, "row means")
+    assert_close(to_np(var), wvar.reshape(-1), 1e-5, "row variances")
+    out = Guarded((rows, D), getattr(torch, dtype), misalign=misalign)
+    sdfl.ops.layer_norm_apply(src.tensor, mean, var, to_dev(gamma), to_dev(beta), D, 1e-5, out=out.tensor)
+    out.check()
+    assert_close(to_np(out.tensor), want, TOL[dtype], f"layer_norm kernel [{rows},{D}] {dtype}")
