@@ -326,6 +326,11 @@ gn_resident_kernel(const ResidentArgs a) {
                 mbar_arrive_peer(map_to_rank(smem_addr(&stat_bar[par]), lane));
             }
         }
+        // Scale and shift of the first chunk of the normalise pass: fetched now, so that their L2
+        // round trip runs beside the exchange instead of behind it.
+        const uint32_t ch0 = (unit % a.groups) * a.cpg;
+        const uint32_t c_first = a.vec_uniform ? a.hwv_div.div(v0 + (P - H) % P * cv) : 0u;
+        const float w_first = __ldg(a.w + ch0 + c_first), b_first = __ldg(a.b + ch0 + c_first);
         // All csize CTAs have written their pair once the barrier's phase completes.  Every
         // warp folds the pairs itself (same order everywhere -> same bits everywhere).
         if (!mbar_wait_cluster_bounded(smem_addr(&stat_bar[par]), (it >> 1) & 1u,
@@ -350,7 +355,6 @@ gn_resident_kernel(const ResidentArgs a) {
         // pass 2: normalise + affine (+ activation) from shared memory to global; each slot is
         // handed back to the producer as soon as this warp is done with it.  Held chunks
         // (P-H .. P-1, already in their slots) first, then chunks 0 .. P-H-1 as they come back.
-        const uint32_t ch0 = (unit % a.groups) * a.cpg;
         uint4 *gv = reinterpret_cast<uint4 *>(static_cast<unsigned char *>(a.out) +
                                               (static_cast<size_t>(unit) * a.slab_vecs + v0) * 16u);
         for (uint32_t k = 0; k < P; ++k) {
@@ -372,8 +376,9 @@ gn_resident_kernel(const ResidentArgs a) {
                 if (c == a.hwv_div.div(v0 + hi - 1u)) {
                     fast = true;
                     const float mc = BIAS ? mean - to_float<T>(erow[c]) : mean;
-                    const Affine<T> af = make_affine<T, ACT>(mc, rstd, __ldg(a.w + ch0 + c),
-                                                            __ldg(a.b + ch0 + c));
+                    const bool first = k == 0 && c == c_first;
+                    const Affine<T> af = make_affine<T, ACT>(mc, rstd, first ? w_first : __ldg(a.w + ch0 + c),
+                                                            first ? b_first : __ldg(a.b + ch0 + c));
                     uint4 v[NV > 0 ? NV : 1];
 #pragma unroll
                     for (int k = 0; k < NV; ++k) v[k] = sv[tid + k * 256];
