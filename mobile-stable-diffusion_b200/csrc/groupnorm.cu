@@ -52,9 +52,10 @@ inline bool aligned16(const void *p) { return gn_aligned16(p); }
 // When the register path beats the cluster path (launches timed back to back on B200, fp16 and
 // fp32, 32-256 slabs of 5-240 KB): always for slabs up to 48 KB (3.5-6 us against 5.5-7); for
 // larger ones once there are at least 64 slabs, i.e. enough CTAs to pull on HBM from many SMs
-// (with 32 slabs of 60-160 KB a cluster of 8 per slab is 0.3-1 us faster).
+// (with 32 slabs a cluster of 8 per slab is 0.6-1.4 us faster from 120 KB on, and 0.3-0.6 us
+// slower up to 80 KB).
 inline bool prefer_register(int64_t slab_bytes, int64_t units) {
-    return slab_bytes <= 48 * 1024 || units >= 64;
+    return slab_bytes <= 48 * 1024 || units >= 64 || (units >= 32 && slab_bytes <= 96 * 1024);
 }
 
 }  // namespace
