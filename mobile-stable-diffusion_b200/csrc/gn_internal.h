@@ -9,8 +9,8 @@ namespace sdfl {
 
 // ---- cluster ring kernel (gn_ring.cu) ----------------------------------------------------------
 constexpr int kGnMaxSlots = 16;
-constexpr uint32_t kGnHeaderBytes = 1536;            // mbarriers, merge scratch, published moments
-constexpr uint32_t kGnMaxPartBytes = 225 * 1024;     // per-CTA ring (227 KB less the header)
+constexpr uint32_t kGnHeaderBytes = 1024;            // mbarriers, merge scratch, published moments
+constexpr uint32_t kGnMaxPartBytes = 226 * 1024;     // per-CTA ring (227 KB less the header)
 
 // The unrolled kernel variants need 256 consumer threads and chunks of 256 * NV vectors.
 inline int gn_ring_unroll(int threads, int chunk_vecs) {

@@ -55,7 +55,6 @@ struct ResidentArgs {
     // the skip-connection concat in front of a ResBlock's first norm (UNetModel.cpp:1960-1990).
     const void *in2;       // nullptr: `in` is the whole [B, C, hw] tensor
     uint32_t c1;
-    uint32_t pipelined;    // moments pass of the next slab ahead of the normalise pass of this one
     float eps;
     FastDiv hw_div;        // element offset -> channel
     FastDiv hwv_div;       // vector offset -> channel (when vec_uniform)
@@ -100,33 +99,27 @@ gn_resident_kernel(const ResidentArgs a) {
     extern __shared__ __align__(128) unsigned char smem[];
     uint64_t *full = reinterpret_cast<uint64_t *>(smem);                  // [kMaxSlots]
     uint64_t *empty = reinterpret_cast<uint64_t *>(smem + 128);           // [kMaxSlots]
-    Moments *warp_m = reinterpret_cast<Moments *>(smem + 256);            // [2][16], by slab parity
-    uint64_t *stat_bar = reinterpret_cast<uint64_t *>(smem + 640);        // [4] peers arrive here
-    float *peer_stats = reinterpret_cast<float *>(smem + 704);            // [4][16][2] written by peers
+    Moments *warp_m = reinterpret_cast<Moments *>(smem + 256);            // [31]
+    uint64_t *stat_bar = reinterpret_cast<uint64_t *>(smem + 640);        // [2] peers arrive here
+    float *peer_stats = reinterpret_cast<float *>(smem + 704);            // [2][16][2] written by peers
     unsigned char *data = smem + kHeaderBytes;
 
     // This CTA's share of every slab: vectors [v0, v0 + nv), cut into P chunks that move through
     // a ring of S slots.  Loads are numbered 0, 1, 2, ... over the whole kernel ("positions");
-    // position p uses slot p % S, phase (p / S) & 1 of that slot's barriers.  A slab is read in
-    // two segments: the moments pass (chunks 0 .. P-1) and the normalise pass.
-    //   in order (pipelined == 0), per slab:
-    //     positions p0 .. p0+P-1        first read of chunks 0 .. P-1
-    //     positions p0+P .. p0+2P-H-1   second read of chunks 0 .. P-H-1
-    //     The last H = min(S-1, P) chunks of the first read are not released after the moments
-    //     pass: they are still in their slots when the normalise pass starts, which therefore
-    //     begins without waiting and reads P-H instead of P chunks again.  P <= S means H = P:
-    //     the share is resident and nothing is read twice.
-    //   pipelined: moments(slab 0), then per slab i: moments(slab i+1), normalise(slab i); every
-    //     segment is P positions (H = 0).  The cluster exchange of slab i+1 and the skew between
-    //     the CTAs of the cluster then hide behind the normalise pass of slab i; the price is two
-    //     slabs per cluster waiting in L2 instead of one.
+    // position p uses slot p % S, phase (p / S) & 1 of that slot's barriers.  Per slab:
+    //   positions p0 .. p0+P-1        first read of chunks 0 .. P-1        (moments pass)
+    //   positions p0+P .. p0+2P-H-1   second read of chunks 0 .. P-H-1     (normalise pass)
+    // The last H = min(S-1, P) chunks of the first read are not released after the moments
+    // pass: they are still in their slots when the normalise pass starts, which therefore
+    // begins without waiting and reads P-H instead of P chunks again.  P <= S means H = P:
+    // the share is resident and nothing is read twice.
     const uint32_t v0 = static_cast<uint32_t>((static_cast<uint64_t>(a.slab_vecs) * rank) / csize);
     const uint32_t v1 = static_cast<uint32_t>((static_cast<uint64_t>(a.slab_vecs) * (rank + 1)) / csize);
     const uint32_t nv = v1 - v0;
     const uint32_t cv = a.chunk_vecs;
     const uint32_t P = (nv + cv - 1) / cv;
     const uint32_t S = a.nslots;
-    const uint32_t H = a.pipelined ? 0u : (P <= S ? P : min(a.hold, S - 1u));
+    const uint32_t H = P <= S ? P : min(a.hold, S - 1u);
     const uint32_t loads_per_slab = 2u * P - H;
     const uint32_t chunk_bytes = cv * 16u;
 
@@ -134,9 +127,11 @@ gn_resident_kernel(const ResidentArgs a) {
         // ---------------- producer warp ----------------------------------------------------------
         bool timed_out = false;
         const uint64_t keep = policy_evict_last(), drop = policy_evict_first();
-        uint32_t slot = 0, round = 0;
-        // chunk j of this CTA's share of slab `unit` -> the next slot of the ring
-        auto issue_chunk = [&](uint32_t unit, uint32_t j, bool keep_in_l2) {
+        uint32_t unit = cluster_id, l = 0, slot = 0, round = 0;
+        // Issue the next load of the sequence; false when all slabs are done.
+        auto issue_next = [&]() -> bool {
+            if (unit >= a.units) return false;
+            const uint32_t j = l < P ? l : l - P;
             if (round > 0) {       // the slot's previous occupant must have been released
                 if (!mbar_wait_bounded(smem_addr(&empty[slot]), (round - 1) & 1u,
                                        timed_out ? kWaitCyclesAfterTimeout : kWaitCycles))
@@ -145,9 +140,9 @@ gn_resident_kernel(const ResidentArgs a) {
             const uint32_t lo = j * cv;
             const uint32_t bytes = (min(nv, lo + cv) - lo) * 16u;
             const uint32_t bar = smem_addr(&full[slot]);
-            // a chunk that will be read a second time should stay in L2; a last read need not
-            const uint64_t policy = keep_in_l2 ? keep : drop;
+            const uint64_t policy = (l < P && j + H < P) ? keep : drop;
             mbar_expect_tx(bar, bytes);
+            // a chunk that will be read a second time should stay in L2; a last read need not
             if (a.in2 == nullptr) {
                 const unsigned char *gsrc = static_cast<const unsigned char *>(a.in) +
                                             (static_cast<size_t>(unit) * a.slab_vecs + v0) * 16u;
@@ -174,35 +169,7 @@ gn_resident_kernel(const ResidentArgs a) {
                 }
             }
             if (++slot == S) { slot = 0; ++round; }
-        };
-        // The load sequence.  `unit`: the slab being read (in order) / the slab whose normalise pass
-        // is pending (pipelined); stage 0: moments of the first slab, 1: moments of the slab after
-        // `unit`, 2: normalise pass of `unit`.
-        uint32_t unit = cluster_id, l = 0, stage = 0;
-        auto issue_next = [&]() -> bool {
-            if (unit >= a.units) return false;
-            if (!a.pipelined) {
-                const bool first_pass = l < P;
-                const uint32_t j = first_pass ? l : l - P;
-                issue_chunk(unit, j, first_pass && j + H < P);
-                if (++l == loads_per_slab) { l = 0; unit += nclusters; }
-                return true;
-            }
-            const bool more = unit + nclusters < a.units;
-            if (stage == 0) {
-                issue_chunk(unit, l, true);
-                if (++l == P) { l = 0; stage = more ? 1u : 2u; }
-            } else if (stage == 1) {
-                issue_chunk(unit + nclusters, l, true);
-                if (++l == P) { l = 0; stage = 2; }
-            } else {
-                issue_chunk(unit, l, false);
-                if (++l == P) {
-                    l = 0;
-                    unit += nclusters;
-                    stage = unit + nclusters < a.units ? 1u : 2u;
-                }
-            }
+            if (++l == loads_per_slab) { l = 0; unit += nclusters; }
             return true;
         };
         if (lane == 0) {
@@ -210,7 +177,8 @@ gn_resident_kernel(const ResidentArgs a) {
                 mbar_init(smem_addr(&full[k]), 1);
                 mbar_init(smem_addr(&empty[k]), cwarps);
             }
-            for (uint32_t k = 0; k < 4; ++k) mbar_init(smem_addr(&stat_bar[k]), csize);
+            mbar_init(smem_addr(&stat_bar[0]), csize);
+            mbar_init(smem_addr(&stat_bar[1]), csize);
             asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // inits before the copy engine's arrivals
             // The first S loads need no release: start them before the barrier below, so the
@@ -243,16 +211,16 @@ gn_resident_kernel(const ResidentArgs a) {
     cluster.sync();
 
     bool timed_out = false;
-
-    // Moments pass of slab `unit` (the `it`-th slab of this cluster), whose chunks are at ring
-    // positions p0 .. p0+P-1: shifted sums chunk by chunk as the copies land, then this CTA's
-    // (mean, M2) goes to slot [it % 4][rank] of every CTA of the cluster.  Four published sets:
-    // a CTA can be at most two slabs ahead of a peer that has not yet read a set (pipelined
-    // order), and the set it then writes is a different one.
-    auto moments_pass = [&](uint32_t unit, uint32_t p0, uint32_t it) {
+    uint32_t pos = 0, it = 0;                // position of the slab's first load
+    for (uint32_t unit = cluster_id; unit < a.units; unit += nclusters, ++it) {
+        const uint32_t par = it & 1u;
+        const uint32_t p0 = pos;
+        // this slab's addends: bias[image, group's first channel ...]
         const T *erow = BIAS ? static_cast<const T *>(a.bias) +
                                    static_cast<size_t>(unit / a.groups) * a.channels + (unit % a.groups) * a.cpg
                              : nullptr;
+
+        // pass 1: shifted sums, chunk by chunk as the copies land
         float s[2] = {0.f, 0.f}, q[2] = {0.f, 0.f};
         float shift = 0.f;
         uint32_t nvec_mine = 0;
@@ -329,7 +297,7 @@ gn_resident_kernel(const ResidentArgs a) {
                     ++nvec_mine;
                 }
             }
-            if (j + H < P) {       // not one of the chunks held for the normalise pass
+            if (j + H < P) {       // not one of the chunks held for pass 2
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_addr(&empty[slot]));
             }
@@ -343,38 +311,21 @@ gn_resident_kernel(const ResidentArgs a) {
             m.m2 = nvec_mine ? fmaxf(qq - ss * ss / cnt, 0.f) : 0.f;
         }
         m = warp_merge(m);
-        // Two sets of per-warp moments by slab parity: a warp reaches the next slab's write of the
-        // same set only through the barrier of the slab in between, which warp 0 joins after it
-        // has read this one.
-        Moments *wm = warp_m + (it & 1u) * 16u;
-        if (lane == 0) wm[warp] = m;
+        if (lane == 0) warp_m[warp] = m;
         consumer_sync(consumers);
         if (warp == 0) {
-            // This CTA's moments -> slot [it % 4][rank] of every CTA of the cluster (itself
+            // This CTA's moments -> slot [par][rank] of every CTA of the cluster (itself
             // included), one lane per destination, then one arrival on that CTA's barrier.
-            const uint32_t set = it & 3u;
-            Moments t = lane < cwarps ? wm[lane] : Moments{0.f, 0.f, 0.f};
+            Moments t = lane < cwarps ? warp_m[lane] : Moments{0.f, 0.f, 0.f};
             t = warp_merge(t);
             const float cta_mean = __shfl_sync(0xffffffffu, t.mean, 0);
             const float cta_m2 = __shfl_sync(0xffffffffu, t.m2, 0);
             if (lane < csize) {
-                st_peer_f32x2(map_to_rank(smem_addr(&peer_stats[(set * 16u + rank) * 2u]), lane),
+                st_peer_f32x2(map_to_rank(smem_addr(&peer_stats[(par * 16u + rank) * 2u]), lane),
                               cta_mean, cta_m2);
-                mbar_arrive_peer(map_to_rank(smem_addr(&stat_bar[set]), lane));
+                mbar_arrive_peer(map_to_rank(smem_addr(&stat_bar[par]), lane));
             }
         }
-    };
-
-    // Normalise pass of the same slab: wait for the csize published pairs, fold them, then
-    // normalise + affine (+ activation) from shared memory to global.  Chunks held since the
-    // moments pass (at p1 + P-H .. p1 + P-1) first, then chunks 0 .. P-H-1 as they come back at
-    // positions p2, p2 + 1, ...; each slot is handed back to the producer as soon as this warp is
-    // done with it.
-    auto normalise_pass = [&](uint32_t unit, uint32_t p1, uint32_t p2, uint32_t it) {
-        const T *erow = BIAS ? static_cast<const T *>(a.bias) +
-                                   static_cast<size_t>(unit / a.groups) * a.channels + (unit % a.groups) * a.cpg
-                             : nullptr;
-        const uint32_t set = it & 3u;
         // Scale and shift of the first chunk of the normalise pass: fetched now, so that their L2
         // round trip runs beside the exchange instead of behind it (1-2 % on every shape; fetching
         // every chunk's pair one chunk ahead as well was 1-4 % slower than this, same GPU, same session).
@@ -383,7 +334,7 @@ gn_resident_kernel(const ResidentArgs a) {
         const float w_first = __ldg(a.w + ch0 + c_first), b_first = __ldg(a.b + ch0 + c_first);
         // All csize CTAs have written their pair once the barrier's phase completes.  Every
         // warp folds the pairs itself (same order everywhere -> same bits everywhere).
-        if (!mbar_wait_cluster_bounded(smem_addr(&stat_bar[set]), (it >> 2) & 1u,
+        if (!mbar_wait_cluster_bounded(smem_addr(&stat_bar[par]), (it >> 1) & 1u,
                                        timed_out ? kWaitCyclesAfterTimeout : kWaitCycles))
             timed_out = true;
         float mean, rstd;
@@ -393,20 +344,24 @@ gn_resident_kernel(const ResidentArgs a) {
                 const uint32_t q0 = static_cast<uint32_t>((static_cast<uint64_t>(a.slab_vecs) * lane) / csize);
                 const uint32_t q1 = static_cast<uint32_t>((static_cast<uint64_t>(a.slab_vecs) * (lane + 1)) / csize);
                 t.n = static_cast<float>(q1 - q0) * VEC;
-                t.mean = peer_stats[(set * 16u + lane) * 2u];
-                t.m2 = peer_stats[(set * 16u + lane) * 2u + 1u];
+                t.mean = peer_stats[(par * 16u + lane) * 2u];
+                t.m2 = peer_stats[(par * 16u + lane) * 2u + 1u];
             }
             t = warp_merge(t);
             const float var = __shfl_sync(0xffffffffu, t.m2, 0) / static_cast<float>(a.slab_elems);   // biased: group_norm.cl:53-55
             mean = __shfl_sync(0xffffffffu, t.mean, 0);
             rstd = 1.0f / sqrtf(var + a.eps);
         }
+
+        // pass 2: normalise + affine (+ activation) from shared memory to global; each slot is
+        // handed back to the producer as soon as this warp is done with it.  Held chunks
+        // (P-H .. P-1, already in their slots) first, then chunks 0 .. P-H-1 as they come back.
         uint4 *gv = reinterpret_cast<uint4 *>(static_cast<unsigned char *>(a.out) +
                                               (static_cast<size_t>(unit) * a.slab_vecs + v0) * 16u);
         for (uint32_t k = 0; k < P; ++k) {
             const bool held = k < H;
             const uint32_t j = held ? P - H + k : k - H;          // chunk of the share
-            const uint32_t p = held ? p1 + j : p2 + j;            // its position in the ring
+            const uint32_t p = held ? p0 + j : p0 + P + j;        // its position in the ring
             const uint32_t slot = p % S, round = p / S;
             if (!held) {
                 if (!mbar_wait_bounded(smem_addr(&full[slot]), round & 1u,
@@ -427,10 +382,10 @@ gn_resident_kernel(const ResidentArgs a) {
                                                             first ? b_first : __ldg(a.b + ch0 + c));
                     uint4 v[NV > 0 ? NV : 1];
 #pragma unroll
-                    for (int kk = 0; kk < NV; ++kk) v[kk] = sv[tid + kk * 256];
+                    for (int k = 0; k < NV; ++k) v[k] = sv[tid + k * 256];
 #pragma unroll
-                    for (int kk = 0; kk < NV; ++kk)
-                        st_stream(&gv[lo + tid + kk * 256], norm_vec<T, ACT>(v[kk], af));
+                    for (int k = 0; k < NV; ++k)
+                        st_stream(&gv[lo + tid + k * 256], norm_vec<T, ACT>(v[k], af));
                 }
             }
             if (fast) {
@@ -473,29 +428,7 @@ gn_resident_kernel(const ResidentArgs a) {
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_addr(&empty[slot]));
         }
-    };
-
-    uint32_t pos = 0, it = 0;                // ring position of the next segment; slabs done
-    if (!a.pipelined) {
-        for (uint32_t unit = cluster_id; unit < a.units; unit += nclusters, ++it) {
-            moments_pass(unit, pos, it);
-            normalise_pass(unit, pos, pos + P, it);
-            pos += loads_per_slab;
-        }
-    } else {
-        uint32_t unit = cluster_id;
-        if (unit < a.units) {
-            moments_pass(unit, pos, 0u);
-            pos += P;
-        }
-        for (; unit < a.units; unit += nclusters, ++it) {
-            if (unit + nclusters < a.units) {
-                moments_pass(unit + nclusters, pos, it + 1u);
-                pos += P;
-            }
-            normalise_pass(unit, 0u, pos, it);
-            pos += P;
-        }
+        pos = p0 + loads_per_slab;
     }
     if (timed_out && lane == 0) atomicOr(&g_gn_status, 1u);
     // No barrier at exit: nobody reads a peer's shared memory; a CTA's own slots are written
@@ -620,7 +553,6 @@ cudaError_t gn_ring_launch(const GnShape &s, const GnPlan &plan, const void *in,
     a.chunk_vecs = static_cast<uint32_t>(plan.chunk_vecs);
     a.nslots = static_cast<uint32_t>(plan.nslots);
     a.hold = static_cast<uint32_t>(plan.hold);
-    a.pipelined = plan.pipelined ? 1u : 0u;
     a.channels = static_cast<uint32_t>(s.channels);
     a.bias = bias;
     a.in2 = in2;

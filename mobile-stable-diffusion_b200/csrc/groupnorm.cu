@@ -170,7 +170,6 @@ cudaError_t gn_make_plan(const GnShape &s, const void *in, const void *out, int 
             plan->chunk_vecs = static_cast<int>(chunk_vecs);
             plan->nslots = static_cast<int>(nslots);
             plan->hold = (force_cluster >> 28) & 3 ? ((force_cluster >> 28) & 3) - 1 : static_cast<int>(nslots) - 1;
-            plan->pipelined = ((force_cluster >> 30) & 1) && chunks > nslots && units > plan->nclusters;
             return cudaSuccess;
         }
         if (force_path == kGnResident) return cudaErrorInvalidConfiguration;

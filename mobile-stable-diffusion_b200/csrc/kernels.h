@@ -30,7 +30,6 @@ struct GnPlan {
     int chunk_vecs;    // 16-byte vectors per shared-memory ring chunk (resident)
     int nslots;        // chunk slots in the ring (resident); fewer than a part's chunks = re-read mode
     int hold;          // chunks kept in their slots between the two passes in re-read mode
-    int pipelined;     // resident: the next slab's moments pass runs ahead of this slab's normalise pass
     int splits;        // chunks per slab (split path)
     size_t smem;       // dynamic shared memory per CTA (resident)
     size_t workspace;  // scratch bytes the split path needs

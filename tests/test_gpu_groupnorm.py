@@ -282,48 +282,6 @@ def test_unrolled_chunks_with_256_consumer_threads(sdfl, shape, G, cluster, chun
     assert sdfl.ops.device_status() == 0
 
 
-PIPELINED = 1 << 30      # knob bit: next slab's moments pass ahead of this slab's normalise pass
-
-
-@pytest.mark.parametrize("dtype", ["float32", "float16"])
-@pytest.mark.parametrize("shape,G,cluster,chunk_kb", [
-    ((40, 64, 64, 64), 32, 1, 4),       # one CTA per slab, small chunks, the general loops
-    ((32, 128, 64, 64), 32, 2, 4),
-    ((12, 512, 64, 64), 32, 2, 16),     # the unrolled chunk variants
-    ((6, 256, 128, 128), 32, 8, 8),     # clusters of 8
-    ((40, 96, 40, 40), 8, 4, 2),        # chunks straddle channel ends, ragged shares
-])
-def test_pipelined_slab_order(sdfl, shape, G, cluster, chunk_kb, dtype):
-    """Clusters that take several slabs each, with the moments pass of slab i+1 ahead of the
-    normalise pass of slab i: same results as the in-order kernel's oracle, also with the fused
-    per-channel addend and in place."""
-    rng = rng_for(5, 1300 + sum(shape) + cluster)
-    x, gamma, beta = gn_inputs(rng, shape, dtype)
-    e = (rng.standard_normal(shape[:2]) * 0.8).astype(np.float32).astype(x.dtype)
-    knob = ring_knob(cluster, 3, chunk_kb, 8) | PIPELINED
-    kw = dict(path=sdfl.ops.GN_RESIDENT, cluster_or_splits=knob)
-    hw = shape[2] * shape[3]
-    plan = sdfl.ops.groupnorm_plan(shape[0], shape[1], hw, G, getattr(torch, dtype), sdfl.ops.GN_RESIDENT, knob)
-    esz = 2 if dtype == "float16" else 4
-    part_vecs = -(-(shape[1] // G * hw * esz // 16) // cluster)
-    assert plan["cluster"] == cluster and shape[0] * G > plan["nclusters"]       # several slabs per cluster
-    assert -(-part_vecs // plan["chunk_vecs"]) > 3                               # shares longer than the ring
-    want = oracle_group_norm(x, gamma, beta, G, 1e-5, True)
-    out = Guarded(shape, getattr(torch, dtype))
-    sdfl.ops.groupnorm(to_dev(x), to_dev(gamma), to_dev(beta), G, 1e-5, True, out=out.tensor, **kw)
-    out.check()
-    assert_close(to_np(out.tensor), want, TOL[dtype], f"pipelined {shape} c={cluster}")
-    inplace = to_dev(x)
-    sdfl.ops.groupnorm(inplace, to_dev(gamma), to_dev(beta), G, 1e-5, True, out=inplace, **kw)
-    assert torch.equal(inplace, out.tensor), "in place differs"
-    want = oracle_bias_group_norm(x, e, gamma, beta, G, 1e-5, False)
-    out = Guarded(shape, getattr(torch, dtype))
-    sdfl.ops.groupnorm_bias(to_dev(x), to_dev(e), to_dev(gamma), to_dev(beta), G, 1e-5, False, out=out.tensor, **kw)
-    out.check()
-    assert_close(to_np(out.tensor), want, TOL[dtype], f"pipelined+bias {shape} c={cluster}")
-    assert sdfl.ops.device_status() == 0
-
-
 @pytest.mark.parametrize("dtype", ["float32", "float16"])
 @pytest.mark.parametrize("shape,G", [
     ((2, 320, 64, 64), 32), ((2, 1280, 8, 8), 32), ((2, 640, 32, 32), 32), ((2, 1920, 16, 16), 32),
