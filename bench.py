@@ -574,6 +574,7 @@ def op_cases(torch, ops, dev):
 
     perm("next: permute3D__0_2_1 f16 [2,320,4096]->[2,4096,320]", 2, 320, 4096, f16, False)
     perm("next: permute + residual add f16 [2,4096,320]->[2,320,4096]", 2, 4096, 320, f16, True)
+    perm("next: permute3D__0_2_1 f16 [64,320,4096] (large)", 64, 320, 4096, f16, False)
     perm("next: permute + residual add f16 [64,4096,320] (large)", 64, 4096, 320, f16, True)
     perm("next: permute3D__0_2_1 f32 [64,1280,1024] (large)", 64, 1280, 1024, f32, False)
 

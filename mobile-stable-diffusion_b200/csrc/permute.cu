@@ -6,7 +6,9 @@
 // The reference moves one element per work-item with one side of the copy strided by a whole
 // row.  Here a CTA moves a 64 x 64 tile through shared memory: both the global reads (along k)
 // and the global writes (along j) are pairs of elements in consecutive lanes, i.e. full 128- or
-// 256-byte segments per warp.  Odd extents or unaligned pointers take the scalar 32 x 32 tiles.
+// 256-byte segments per warp (fp16 with extents that are multiples of 8: 16-byte accesses and an
+// ldmatrix.trans write-out, transpose_h8_kernel).  Odd extents or unaligned pointers take the
+// scalar 32 x 32 tiles.
 #include "common.cuh"
 #include "kernels.h"
 
@@ -161,6 +163,120 @@ transpose_pairs_kernel(const T *__restrict__ src, const T *res, T *dst, int J, i
     }
 }
 
+// fp16 with J and K multiples of 8 and 16-byte aligned pointers: the same persistent double-buffered
+// walk over tiles, but every access is 16 bytes wide.  A tile arrives by 16-byte cp.async into rows
+// padded by 16 bytes (eight consecutive rows start in eight different groups of four banks).  It
+// leaves through ldmatrix.trans: one x4 instruction hands a warp four transposed 8 x 8 blocks
+// (source rows j0 .. j0+31, columns k0 .. k0+7), lane (r, q) holding the pairs (j0 + 8m + 2q, +1)
+// of output row k0 + r for m = 0 .. 3; a 4 x 4 exchange inside each quad of lanes turns that into
+// the eight consecutive j of block q, one 16-byte store per lane.  The 2-byte column reads that
+// capped the pair kernel at 4.5 TB/s are gone.
+__device__ __forceinline__ uint32_t quad_pick(const uint32_t (&v)[4], uint32_t i) {
+    return i == 0 ? v[0] : i == 1 ? v[1] : i == 2 ? v[2] : v[3];
+}
+
+// TJ x TK: tile extents along the source's rows (j) and columns (k), multiples of 32 and 8.
+template <bool ADD, int TJ, int TK>
+__global__ void __launch_bounds__(256)
+transpose_h8_kernel(const __half *__restrict__ src, const __half *res, __half *dst, int J, int K, unsigned tiles_j,
+                    unsigned tiles_k, unsigned long long total_tiles) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    constexpr int kSrcRow = TK * 2 + 16, kResRow = TJ * 2 + 16;       // bytes; 16 mod 128 either way
+    constexpr int kSrcTile = TJ * kSrcRow, kResTile = TK * kResRow;
+    unsigned char *tile = smem_raw;                       // [2] source tiles, rows along k
+    unsigned char *rtile = smem_raw + 2 * kSrcTile;       // [2] residual tiles, rows along j (ADD only)
+    const int tid = threadIdx.y * 32 + threadIdx.x, lane = threadIdx.x, warp = threadIdx.y;
+    const long long slice = static_cast<long long>(J) * K;
+
+    auto issue = [&](unsigned long long id, int buf) {
+        if (id < total_tiles) {
+            const unsigned kt = static_cast<unsigned>(id % tiles_k);
+            const unsigned long long q = id / tiles_k;
+            const unsigned jt = static_cast<unsigned>(q % tiles_j);
+            const __half *s = src + (q / tiles_j) * slice;
+#pragma unroll
+            for (int t = tid; t < TJ * (TK / 8); t += 256) {          // TJ rows x TK/8 segments of 16 bytes
+                const int r = t / (TK / 8), seg = t % (TK / 8);
+                const int j = jt * TJ + r, k = kt * TK + seg * 8;
+                if (j < J && k < K) {
+                    const uint32_t d = static_cast<uint32_t>(
+                        __cvta_generic_to_shared(tile + buf * kSrcTile + r * kSrcRow + seg * 16));
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(s + static_cast<long long>(j) * K + k) : "memory");
+                }
+            }
+            if (ADD) {
+                const __half *a = res + (q / tiles_j) * slice;
+#pragma unroll
+                for (int t = tid; t < TK * (TJ / 8); t += 256) {
+                    const int r = t / (TJ / 8), seg = t % (TJ / 8);
+                    const int kk = kt * TK + r, jj = jt * TJ + seg * 8;
+                    if (kk < K && jj < J) {
+                        const uint32_t d = static_cast<uint32_t>(
+                            __cvta_generic_to_shared(rtile + buf * kResTile + r * kResRow + seg * 16));
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(a + static_cast<long long>(kk) * J + jj) : "memory");
+                    }
+                }
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");      // one group per call, empty past the end
+    };
+
+    unsigned long long id = blockIdx.x;
+    issue(id, 0);
+    for (int buf = 0; id < total_tiles; id += gridDim.x, buf ^= 1) {
+        issue(id + gridDim.x, buf ^ 1);
+        asm volatile("cp.async.wait_group 1;" ::: "memory");
+        __syncthreads();
+        const unsigned kt = static_cast<unsigned>(id % tiles_k);
+        const unsigned long long q = id / tiles_k;
+        const unsigned jt = static_cast<unsigned>(q % tiles_j);
+        __half *d = dst + (q / tiles_j) * slice;
+        const uint32_t rr = lane >> 2, qq = lane & 3;
+#pragma unroll
+        for (int kb = warp; kb < TK / 8; kb += 8) {
+            const int k = kt * TK + kb * 8 + rr;                  // this lane's output row
+#pragma unroll
+            for (int jg = 0; jg < TJ / 32; ++jg) {
+                // four 8 x 8 blocks: source rows jg*32 + 8m .. +7 (lane l gives the address of row
+                // jg*32 + l), columns kb*8 .. +7
+                const uint32_t addr = static_cast<uint32_t>(__cvta_generic_to_shared(
+                    tile + buf * kSrcTile + (jg * 32 + lane) * kSrcRow + kb * 16));
+                uint32_t in[4];
+                asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                             : "=r"(in[0]), "=r"(in[1]), "=r"(in[2]), "=r"(in[3]) : "r"(addr));
+                // exchange inside the quad: lane q ends up with word q of lanes 0 .. 3
+                uint32_t out[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+                for (uint32_t s = 0; s < 4; ++s) {
+                    const uint32_t send = quad_pick(in, (qq - s) & 3u);
+                    const uint32_t got = __shfl_sync(0xffffffffu, send, (lane & ~3u) | ((qq + s) & 3u));
+                    const uint32_t slot = (qq + s) & 3u;
+                    out[0] = slot == 0 ? got : out[0];
+                    out[1] = slot == 1 ? got : out[1];
+                    out[2] = slot == 2 ? got : out[2];
+                    out[3] = slot == 3 ? got : out[3];
+                }
+                const int j = jt * TJ + jg * 32 + qq * 8;
+                if (k < K && j < J) {
+                    uint4 v = make_uint4(out[0], out[1], out[2], out[3]);
+                    if (ADD) {
+                        const uint4 w = *reinterpret_cast<const uint4 *>(
+                            rtile + buf * kResTile + (kb * 8 + rr) * kResRow + (jg * 32 + qq * 8) * 2);
+                        float x[8], y[8];
+                        unpack<__half>(v, x);
+                        unpack<__half>(w, y);
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) x[e] += y[e];       // fp32 add, one rounding, as the reference
+                        v = pack<__half>(x);
+                    }
+                    st_stream(d + static_cast<long long>(k) * J + j, v);
+                }
+            }
+        }
+        __syncthreads();      // this buffer is the target of the copies issued next time round
+    }
+}
+
 // Any extents and alignment: 32 x 32 tiles, one element per access.
 template <typename T, bool ADD>
 __global__ void __launch_bounds__(256)
@@ -191,6 +307,24 @@ transpose_scalar_kernel(const T *__restrict__ src, const T *res, T *dst, long lo
     }
 }
 
+template <bool ADD, int TJ, int TK>
+cudaError_t launch_h8(const __half *s, const __half *r, __half *d, int64_t I, int64_t J, int64_t K, cudaStream_t stream) {
+    constexpr size_t smem = 2 * (TJ * (TK * 2 + 16) + (ADD ? TK * (TJ * 2 + 16) : 0));
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(transpose_h8_kernel<ADD, TJ, TK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             static_cast<int>(smem));
+        if (e != cudaSuccess) return e;
+    }
+    const unsigned tiles_j = static_cast<unsigned>((J + TJ - 1) / TJ), tiles_k = static_cast<unsigned>((K + TK - 1) / TK);
+    const unsigned long long total = static_cast<unsigned long long>(I) * tiles_j * tiles_k;
+    const unsigned long long per_sm = 220 * 1024 / (smem + 1024) < 6 ? 220 * 1024 / (smem + 1024) : 6;
+    const unsigned long long ctas = 148ull * per_sm;
+    const unsigned grid = static_cast<unsigned>(total < ctas ? total : ctas);
+    transpose_h8_kernel<ADD, TJ, TK><<<grid, dim3(32, 8), smem, stream>>>(s, r, d, static_cast<int>(J), static_cast<int>(K),
+                                                                         tiles_j, tiles_k, total);
+    return cudaGetLastError();
+}
+
 template <typename T, bool ADD>
 constexpr size_t transpose_smem_bytes() {
     return (ADD ? 2 : 1) * Stages<T>::N * sizeof(T) * kTile * (kTile + (sizeof(T) == 2 ? 2 : 1));
@@ -205,6 +339,24 @@ cudaError_t transpose_dispatch(const void *src, const void *res, void *dst, int6
                        (!ADD || (reinterpret_cast<uintptr_t>(res) & align) == 0);
     const T *s = static_cast<const T *>(src), *r = static_cast<const T *>(res);
     T *d = static_cast<T *>(dst);
+    if constexpr (sizeof(T) == 2) {
+        const bool wide = J % 8 == 0 && K % 8 == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0 &&
+                          (reinterpret_cast<uintptr_t>(dst) & 15) == 0 &&
+                          (!ADD || (reinterpret_cast<uintptr_t>(res) & 15) == 0);
+        if (wide) {
+            // 64 x 128 tiles, the long side (256-byte row segments) along a dimension that is a
+            // multiple of 128, the longer one if both are: on [64,320,4096] 80 % of the HBM peak
+            // against 71 % with 64 x 64 tiles, on [64,4096,320] with the residual 86 % against 82 %
+            // (128 x 128 tiles: 71 % and 40 %).
+            const bool k_wide = K % 128 == 0 && (J % 128 != 0 || K >= J);
+            const bool j_wide = !k_wide && J % 128 == 0;
+            cudaError_t err = k_wide   ? launch_h8<ADD, 64, 128>(s, r, d, I, J, K, stream)
+                              : j_wide ? launch_h8<ADD, 128, 64>(s, r, d, I, J, K, stream)
+                                       : launch_h8<ADD, 64, 64>(s, r, d, I, J, K, stream);
+            if (err == cudaSuccess) g_launches.fetch_add(1);
+            return err;
+        }
+    }
     if (pairs) {
         const unsigned tiles_j = static_cast<unsigned>((J + kTile - 1) / kTile);
         const unsigned tiles_k = static_cast<unsigned>((K + kTile - 1) / kTile);

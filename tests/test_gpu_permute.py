@@ -10,7 +10,9 @@ from gpu_util import Guarded, gn_inputs, oracle_group_norm, to_dev, to_np
 
 pytestmark = pytest.mark.gpu
 
-SHAPES_3D = [(1, 320, 4096), (2, 4096, 320), (2, 64, 64), (3, 5, 7), (1, 1, 9), (2, 33, 64), (1, 130, 66),
+SHAPES_3D = [(1, 320, 4096), (2, 4096, 320), (2, 64, 64),
+             (3, 72, 200), (2, 8, 8), (1, 136, 264),        # multiples of 8 but not of the 64 x 64 tile
+             (3, 5, 7), (1, 1, 9), (2, 33, 64), (1, 130, 66),
              (70000, 2, 2)]
 
 
@@ -27,7 +29,7 @@ def test_permute_is_a_bit_exact_copy(sdfl, shape, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "float16"])
-@pytest.mark.parametrize("shape", SHAPES_3D[:7])
+@pytest.mark.parametrize("shape", SHAPES_3D[:10])
 def test_permute_fused_with_the_residual_add(sdfl, shape, dtype):
     """permute3D__0_2_1 then elemwise_add (SpatialTransformer.cpp:154-171): one rounded add per element."""
     rng = rng_for(7, 50 + sum(shape))
