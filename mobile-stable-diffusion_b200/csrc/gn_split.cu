@@ -339,6 +339,128 @@ gn_apply_nhwc_async_kernel(const SplitArgs a, uint32_t hw, unsigned tiles_c, uns
     }
 }
 
+// fp16 with hw and C multiples of 8 and 16-byte aligned tensors: the same persistent walk with
+// 16-byte accesses on both sides.  A TJ-channel x TK-pixel tile arrives by 16-byte cp.async into rows
+// padded by 16 bytes; ldmatrix.trans hands each lane the pairs (channel c, c+1) of one pixel, the
+// affine (+ SiLU) is applied there, and a 4 x 4 exchange inside each quad of lanes gives every lane
+// eight consecutive channels of its pixel: one 16-byte store.
+__device__ __forceinline__ uint32_t nhwc_quad_pick(const uint32_t (&v)[4], uint32_t i) {
+    return i == 0 ? v[0] : i == 1 ? v[1] : i == 2 ? v[2] : v[3];
+}
+
+template <int ACT, int TJ, int TK>
+__global__ void __launch_bounds__(256)
+gn_apply_nhwc_h8_kernel(const SplitArgs a, uint32_t hw, unsigned tiles_c, unsigned tiles_p,
+                        unsigned long long total_tiles) {
+    extern __shared__ __align__(16) unsigned char nhwc_smem[];
+    constexpr int kRow = TK * 2 + 16, kTileBytes = TJ * kRow;
+    unsigned char *tile = nhwc_smem;                                          // [2]
+    float2 *coef = reinterpret_cast<float2 *>(nhwc_smem + 2 * kTileBytes);    // [TJ]: folded scale, shift
+    const int tid = threadIdx.y * 32 + threadIdx.x, lane = threadIdx.x, warp = threadIdx.y;
+    const size_t image = static_cast<size_t>(a.channels) * hw;
+    const __half *in = static_cast<const __half *>(a.in);
+    __half *out = static_cast<__half *>(a.out);
+
+    auto issue = [&](unsigned long long id, int buf) {
+        if (id < total_tiles) {
+            const unsigned pt = static_cast<unsigned>(id % tiles_p);
+            const unsigned long long q = id / tiles_p;
+            const unsigned ct = static_cast<unsigned>(q % tiles_c);
+            const __half *x = in + (q / tiles_c) * image;
+#pragma unroll
+            for (int t = tid; t < TJ * (TK / 8); t += 256) {
+                const int r = t / (TK / 8), seg = t % (TK / 8);
+                const uint32_t c = ct * TJ + r, p = pt * TK + seg * 8;
+                if (c < a.channels && p < hw) {
+                    const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(tile + buf * kTileBytes + r * kRow + seg * 16));
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(x + static_cast<size_t>(c) * hw + p) : "memory");
+                }
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");      // one group per call, empty past the end
+    };
+
+    unsigned long long id = blockIdx.x, coef_of = ~0ull;
+    issue(id, 0);
+    for (int buf = 0; id < total_tiles; id += gridDim.x, buf ^= 1) {
+        issue(id + gridDim.x, buf ^ 1);
+        const unsigned pt = static_cast<unsigned>(id % tiles_p);
+        const unsigned long long q = id / tiles_p;              // n * tiles_c + ct
+        const unsigned ct = static_cast<unsigned>(q % tiles_c);
+        const unsigned long long n = q / tiles_c;
+        if (q != coef_of) {                                      // uniform over the CTA
+            if (tid < TJ && ct * TJ + tid < a.channels) {
+                const uint32_t c = ct * TJ + tid;
+                const size_t unit = static_cast<size_t>(n) * a.groups + c / a.cpg;
+                Moments m{0.f, 0.f, 0.f};
+                for (uint32_t s = 0; s < a.splits; ++s) {        // chunks in order: every CTA gets the same bits
+                    const uint32_t e0 = s * a.chunk_elems, e1 = min(a.slab_elems, e0 + a.chunk_elems);
+                    Moments y;
+                    y.n = e1 > e0 ? static_cast<float>(e1 - e0) : 0.f;
+                    y.mean = a.partial[2 * (unit * a.splits + s)];
+                    y.m2 = a.partial[2 * (unit * a.splits + s) + 1];
+                    m = merge(m, y);
+                }
+                const float var = m.m2 / static_cast<float>(a.slab_elems);
+                const Affine<__half> af = make_affine<__half, ACT>(m.mean, 1.0f / sqrtf(var + a.eps), __ldg(a.w + c), __ldg(a.b + c));
+                coef[tid] = make_float2(af.p0, af.p1);
+            }
+            coef_of = q;
+        }
+        asm volatile("cp.async.wait_group 1;" ::: "memory");
+        __syncthreads();                                         // the tile has landed; coef is written
+        __half *y = out + n * image;
+        const uint32_t rr = lane >> 2, qq = lane & 3;
+#pragma unroll
+        for (int kb = warp; kb < TK / 8; kb += 8) {
+            const uint32_t p = pt * TK + kb * 8 + rr;            // this lane's pixel
+#pragma unroll
+            for (int jg = 0; jg < TJ / 32; ++jg) {
+                const uint32_t addr = static_cast<uint32_t>(__cvta_generic_to_shared(
+                    tile + buf * kTileBytes + (jg * 32 + lane) * kRow + kb * 16));
+                uint32_t v[4];
+                asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                             : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]) : "r"(addr));
+#pragma unroll
+                for (int m = 0; m < 4; ++m) {                    // channels jg*32 + 8m + 2q, +1 of pixel p
+                    const float2 k0 = coef[jg * 32 + 8 * m + 2 * qq], k1 = coef[jg * 32 + 8 * m + 2 * qq + 1];
+                    const float2 x = __half22float2(*reinterpret_cast<const __half2 *>(&v[m]));
+                    const float h0 = fmaf(x.x, k0.x, k0.y), h1 = fmaf(x.y, k1.x, k1.y);
+                    const __half2 r = __floats2half2_rn(ACT == kActSilu ? fmaf(h0, tanh_approx(h0), h0) : h0,
+                                                        ACT == kActSilu ? fmaf(h1, tanh_approx(h1), h1) : h1);
+                    v[m] = *reinterpret_cast<const uint32_t *>(&r);
+                }
+                uint32_t o[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+                for (uint32_t s = 0; s < 4; ++s) {               // lane q ends up with word q of lanes 0 .. 3
+                    const uint32_t send = nhwc_quad_pick(v, (qq - s) & 3u);
+                    const uint32_t got = __shfl_sync(0xffffffffu, send, (lane & ~3u) | ((qq + s) & 3u));
+                    const uint32_t slot = (qq + s) & 3u;
+                    o[0] = slot == 0 ? got : o[0];
+                    o[1] = slot == 1 ? got : o[1];
+                    o[2] = slot == 2 ? got : o[2];
+                    o[3] = slot == 3 ? got : o[3];
+                }
+                const uint32_t c = ct * TJ + jg * 32 + qq * 8;
+                if (p < hw && c < a.channels)
+                    st_stream(y + static_cast<size_t>(p) * a.channels + c, make_uint4(o[0], o[1], o[2], o[3]));
+            }
+        }
+        __syncthreads();      // tile[buf] is the target of the copies issued next time round; coef may change
+    }
+}
+
+template <int ACT, int TJ, int TK>
+cudaError_t launch_nhwc_h8(const SplitArgs &a, const GnShape &s, cudaStream_t stream) {
+    constexpr size_t smem = 2 * TJ * (TK * 2 + 16) + TJ * sizeof(float2);
+    const unsigned tiles_c = static_cast<unsigned>((s.channels + TJ - 1) / TJ), tiles_p = static_cast<unsigned>((s.hw + TK - 1) / TK);
+    const unsigned long long total = static_cast<unsigned long long>(s.batch) * tiles_c * tiles_p;
+    const unsigned long long ctas = 148ull * 6;
+    const unsigned grid = static_cast<unsigned>(total < ctas ? total : ctas);
+    gn_apply_nhwc_h8_kernel<ACT, TJ, TK><<<grid, dim3(32, 8), smem, stream>>>(a, static_cast<uint32_t>(s.hw), tiles_c, tiles_p, total);
+    return cudaGetLastError();
+}
+
 // ---------------------------------------------------------------------------------------------
 // Stand-alone kernels for the reference's three-launch sequence
 // ---------------------------------------------------------------------------------------------
@@ -549,6 +671,24 @@ cudaError_t gn_split_launch(const GnShape &s, const GnPlan &plan, const void *in
             if (pairs) gn_apply_nhwc_async_kernel<T, ACT><<<agrid, tblock, asmem, stream>>>(a, hw32, tiles_c, tiles_p, total); \
             else gn_apply_nhwc_kernel<T, ACT, false><<<tgrid, tblock, 0, stream>>>(a, hw32);        \
         } while (0)
+        const bool wide = s.dtype == kF16 && s.hw % 8 == 0 && s.channels % 8 == 0 && aligned16(in) && aligned16(out);
+        if (wide) {
+            // tile shape as in the fp16 transpose: the long side along a dimension that is a multiple of 128
+            gn_split_stats_kernel<__half><<<grid, kSplitThreads, 0, stream>>>(a);
+            const bool p_wide = s.hw % 128 == 0 && (s.channels % 128 != 0 || s.hw >= s.channels);
+            const bool c_wide = !p_wide && s.channels % 128 == 0;
+            cudaError_t herr;
+            if (s.act == kActSilu)
+                herr = p_wide ? launch_nhwc_h8<kActSilu, 64, 128>(a, s, stream)
+                       : c_wide ? launch_nhwc_h8<kActSilu, 128, 64>(a, s, stream)
+                                : launch_nhwc_h8<kActSilu, 64, 64>(a, s, stream);
+            else
+                herr = p_wide ? launch_nhwc_h8<kActNone, 64, 128>(a, s, stream)
+                       : c_wide ? launch_nhwc_h8<kActNone, 128, 64>(a, s, stream)
+                                : launch_nhwc_h8<kActNone, 64, 64>(a, s, stream);
+            if (herr == cudaSuccess) g_launches.fetch_add(2);
+            return herr;
+        }
         if (s.dtype == kF16) {
             gn_split_stats_kernel<__half><<<grid, kSplitThreads, 0, stream>>>(a);
             if (s.act == kActSilu) SDFL_NHWC_APPLY(__half, kActSilu); else SDFL_NHWC_APPLY(__half, kActNone);

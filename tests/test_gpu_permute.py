@@ -68,6 +68,8 @@ def test_permute_errors(sdfl):
     ((2, 6, 5, 8), 2),           # odd channels per group: scalar channels-last stores
     ((1, 64, 128, 128), 32),     # fp32 slabs of 128 KB; still one CTA per slab
     ((1, 128, 256, 256), 32),    # slabs too large for one CTA: norm into the scratch, then the transpose
+    ((1, 512, 40, 40), 32),      # ... with tiles that are long along the channels (C a multiple of 128, H*W not)
+    ((1, 320, 40, 40), 8),       # ... and with neither a multiple of 128: square tiles, ragged edges
 ])
 def test_groupnorm_with_channels_last_store(sdfl, shape, G, dtype):
     """GroupNorm::forward + permute3D__0_2_1{1, C, HW} (SpatialTransformer.cpp:127-140) as one call."""
