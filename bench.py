@@ -561,6 +561,7 @@ def op_cases(torch, ops, dev):
     gn_nhwc("next: GN + channels-last store f16 [2,1280,16,16]", 2, 1280, 16, f16)
     gn_nhwc("next: GN + channels-last store f32 [1,320,64,64]", 1, 320, 64, f32)
     gn_nhwc("next: GN + channels-last store f16 [8,512,128,128] (large)", 8, 512, 128, f16)
+    gn_nhwc("next: GN + channels-last store f32 [4,512,128,128] (large)", 4, 512, 128, f32)
 
     def perm(name, I, J, K, dtype, add):
         esz = 2 if dtype == f16 else 4
