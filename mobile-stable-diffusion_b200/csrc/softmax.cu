@@ -94,7 +94,8 @@ softmax_warp_kernel(const T *__restrict__ in, T *out, long long rows, int dim) {
 // Short rows of any length and alignment (the 77 keys of cross-attention: 154- or 308-byte rows):
 // one warp per row, lane l holds elements l, l+32, ... (up to MAXE), element-wise accesses that
 // are consecutive across the lanes.  (Four rows per warp iteration, all loads issued first, was
-// slower: 15.2 against 9.4 us on 65536 fp16 rows of 77.)
+// slower: 15.2 against 9.4 us on 65536 fp16 rows of 77; blocks of 64 rows staged in shared memory
+// with 16-byte global accesses on both sides: 11.8 us.)
 template <typename T, int MAXE>
 __global__ void __launch_bounds__(kSmThreads)
 softmax_warp_scalar_kernel(const T *__restrict__ in, T *out, long long rows, int dim) {

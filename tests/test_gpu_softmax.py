@@ -11,7 +11,8 @@ pytestmark = pytest.mark.gpu
 
 # (rows, keys): cross-attention rows of 77, self-attention rows of 64 .. 4096, ragged and long rows
 SHAPES = [(8 * 64, 77), (8 * 64, 64), (8 * 32, 256), (64, 1024), (48, 4096), (5, 100), (3, 1), (7, 333),
-          (4, 8192), (2, 20000)]
+          (4, 8192), (2, 20000),
+          (130, 77), (257, 33), (300, 255), (129, 3)]      # short odd rows, a few more than a multiple of 64
 
 
 @pytest.mark.parametrize("dtype", ["float32", "float16"])
