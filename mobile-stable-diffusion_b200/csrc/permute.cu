@@ -348,8 +348,11 @@ cudaError_t transpose_dispatch(const void *src, const void *res, void *dst, int6
             // multiple of 128, the longer one if both are: on [64,320,4096] 80 % of the HBM peak
             // against 71 % with 64 x 64 tiles, on [64,4096,320] with the residual 86 % against 82 %
             // (128 x 128 tiles: 71 % and 40 %).
-            const bool k_wide = K % 128 == 0 && (J % 128 != 0 || K >= J);
-            const bool j_wide = !k_wide && J % 128 == 0;
+            // Small tensors keep 64 x 64 tiles: with fewer tiles than two rounds of the persistent
+            // grid the larger tiles leave SMs idle ([2,320,4096]: 5.5 against 5.0 us).
+            const bool enough = I * ((J + 63) / 64) * ((K + 63) / 64) >= 4 * 148 * 6;
+            const bool k_wide = enough && K % 128 == 0 && (J % 128 != 0 || K >= J);
+            const bool j_wide = enough && !k_wide && J % 128 == 0;
             cudaError_t err = k_wide   ? launch_h8<ADD, 64, 128>(s, r, d, I, J, K, stream)
                               : j_wide ? launch_h8<ADD, 128, 64>(s, r, d, I, J, K, stream)
                                        : launch_h8<ADD, 64, 64>(s, r, d, I, J, K, stream);
