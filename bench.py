@@ -42,13 +42,13 @@ GROUPS = 32
 EPS = 1e-6
 L2_BYTES = 126 * 1024 * 1024
 PEAK_FALLBACK_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel divided by
-# its algorithmic bytes, from the ncu capture of [4,128,512,512] fp16 summarised in
-# profiles/gn_resident_kernel_half_silu_4x128x512x512.md: 287.2 MB read + 211.3 MB written for
-# 536.9 MB algorithmic (reads 1.07x the input; part of the output is still dirty in L2 when
-# the kernel ends).  Traffic grows in proportion to the slabs processed, so the per-launch
-# figure reported is this ratio times the launch's algorithmic bytes.
-NCU_TRAFFIC_RATIO = 0.929
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the step's kernel divided by its
+# algorithmic bytes, from an ncu capture of the same kernel on a smaller batch of the same four
+# shapes (inputs larger than L2, within the size an ncu capture may have).  Traffic grows in
+# proportion to the slabs processed, so the per-launch figure reported is this ratio times the
+# launch's algorithmic bytes; None until a capture exists.
+NCU_TRAFFIC_RATIO_MULTI = None
+NCU_TRAFFIC_SOURCE = None
 
 
 def algorithmic_bytes(batch: int, C: int, H: int, esz: int = 2) -> int:
@@ -171,6 +171,8 @@ def time_cpu_reference(steps: int, warmup: int, budget_s: float, exact_steps: bo
     import oracle
     backend = "ref" if oracle.have_ref() else "port"
     kind = "reference" if backend == "ref" else "port"
+    # all the cores this process may run on, whatever OMP_NUM_THREADS says (torchrun exports 1)
+    oracle.set_num_threads(len(os.sched_getaffinity(0)))
     cores = oracle.num_threads(backend)
     groups_used = GROUPS
     data = cpu_reference_data(np, groups_used)
@@ -245,7 +247,34 @@ def run_reference(args) -> None:
 # ---------------------------------------------------------------------------------------------
 # our arm
 # ---------------------------------------------------------------------------------------------
+def bind_to_gpu_numa_node(torch, local_rank: int) -> dict:
+    """Pin this process to the CPUs of the NUMA node its GPU hangs off, so that the page-locked
+    host buffers allocated afterwards (first touch) are local to the GPU's PCIe root.  Returns
+    what was found; leaves the affinity alone when the topology cannot be read."""
+    info = {"numa_node": None, "cpus": len(os.sched_getaffinity(0))}
+    try:
+        bus = torch.cuda.get_device_properties(local_rank).pci_bus_id
+        dom = torch.cuda.get_device_properties(local_rank).pci_domain_id
+        dev = torch.cuda.get_device_properties(local_rank).pci_device_id
+        path = f"/sys/bus/pci/devices/{dom:04x}:{bus:02x}:{dev:02x}.0/numa_node"
+        node = int(open(path).read().strip())
+        if node < 0:
+            return info
+        cpus = set()
+        for part in open(f"/sys/devices/system/node/node{node}/cpulist").read().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        cpus &= os.sched_getaffinity(0)
+        if cpus:
+            os.sched_setaffinity(0, cpus)
+            info.update({"numa_node": node, "cpus": len(cpus)})
+    except Exception as e:                      # no sysfs / no permission: report and carry on
+        info["error"] = f"{type(e).__name__}: {e}"
+    return info
+
+
 def run_ours(args) -> None:
+    import numpy as np
     import torch
     import torch.distributed as dist
 
@@ -273,6 +302,7 @@ def run_ours(args) -> None:
     lo, hi = sharding.partition(BATCH, world, rank)          # images of this rank
     b_local = hi - lo
     K, W = args.steps, max(args.warmup, 3)
+    R = max(args.blocks, 1)
 
     # ring of buffer sets so that a buffer is reused only after > 4x L2 of other traffic
     step_bytes = sum(algorithmic_bytes(b_local, C, H) for C, H in SHAPES)
@@ -288,71 +318,110 @@ def run_ours(args) -> None:
             tensors.append((x, gamma, beta, torch.empty_like(x)))
         sets.append(tensors)
 
-    def step(tensors):
+    multi_plan: list = []
+
+    def step_multi(tensors):         # the step as ONE launch over its four tensors
+        ops.groupnorm_multi([t[0] for t in tensors], [t[1] for t in tensors], [t[2] for t in tensors],
+                            GROUPS, EPS, True, outs=[t[3] for t in tensors], plan=multi_plan)
+
+    def step_chain(tensors):         # the step as four launches, one per tensor
         for x, gamma, beta, y in tensors:
             ops.groupnorm(x, gamma, beta, GROUPS, EPS, True, out=y)
 
+    step = step_chain if args.chain else step_multi
+    launches_per_step = len(SHAPES) if args.chain else 1
     stream = torch.cuda.Stream(device=dev)
-    with torch.cuda.stream(stream):
-        for s in sets:                      # first calls: attribute set-up, plan cache, workspace
-            step(s)
-        stream.synchronize()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    def capture(fn):
         graphs = []
-        for s in sets:                      # one CUDA graph per buffer set (4 launches)
+        for s in sets:                      # first calls: attribute set-up, plan cache, workspace
+            fn(s)
+        stream.synchronize()
+        for s in sets:                      # one CUDA graph per buffer set
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g, stream=stream):
-                step(s)
+                fn(s)
             graphs.append(g)
+        return graphs
+
+    def timed_blocks(graphs, blocks):
+        """`blocks` blocks of K graph replays each, every block between its own pair of events;
+        returns the per-block device times in ms (this rank)."""
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(blocks)]
+        i = 0
+        for a, b in evs:
+            a.record(stream)
+            for _ in range(K):
+                graphs[i % ring].replay()
+                i += 1
+            b.record(stream)
+        return evs
+
+    with torch.cuda.stream(stream):
+        graphs = capture(step)
         for i in range(W):
             graphs[i % ring].replay()
         stream.synchronize()
 
-        def barrier():
-            if world > 1:
-                dist.barrier()
-            torch.cuda.synchronize(dev)
-
-        sampler = ClockSampler(local_rank)
+        sampler = ClockSampler(local_rank, period=0.005)
         sampler.start()
-        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        n0 = ops.launch_count()
         barrier()
         t_begin = time.perf_counter()
-        ev0.record(stream)
-        for i in range(K):
-            graphs[i % ring].replay()
-        ev1.record(stream)
+        evs = timed_blocks(graphs, R)
         barrier()
         t_end = time.perf_counter()
-        ms = ev0.elapsed_time(ev1)
-        launches_per_step = len(SHAPES)
-        clocks = sampler.summary(t_begin, t_end, "timed region")
-        if clocks.get("sm_mhz") is None and clocks.get("sm_max_mhz") is not None:
-            # the timed region was shorter than the sampling period: hold the same load for
-            # ~1.5 s and take the clocks there (not part of any reported time)
-            t2 = time.perf_counter()
-            i = 0
-            while time.perf_counter() - t2 < 1.5:
-                graphs[i % ring].replay()
-                i += 1
-                if i % 64 == 0:
-                    stream.synchronize()
-            stream.synchronize()
-            clocks = sampler.summary(t2, time.perf_counter(), "same load held 1.5 s after the timed region")
-        _ = n0
+        block_ms = [a.elapsed_time(b) for a, b in evs]
+        clocks = sampler.summary(t_begin, t_end, f"timed region ({R} blocks of {K} steps)")
 
-    t = torch.tensor([ms], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_max = float(t.item())
+        # the other way of launching the step, same buffers, outside the headline region
+        other = step_multi if args.chain else step_chain
+        other_graphs = capture(other)
+        for i in range(W):
+            other_graphs[i % ring].replay()
+        barrier()
+        other_ms = [a.elapsed_time(b) for a, b in timed_blocks(other_graphs, min(R, 7))]
+        del other_graphs
+
+    def max_over_ranks(values):
+        t = torch.tensor(values, device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return [float(v) for v in t.tolist()]
+
+    block_ms = max_over_ranks(block_ms)              # a block is as slow as its slowest rank
+    other_ms = max_over_ranks(other_ms)
+    ms_med = statistics.median(block_ms)
     total_bytes = sum(algorithmic_bytes(BATCH, C, H) for C, H in SHAPES) if BATCH % world == 0 else None
     if total_bytes is None:
         tb = torch.tensor([step_bytes], device=dev, dtype=torch.float64)
         dist.all_reduce(tb)
         total_bytes = float(tb.item())
-    value = total_bytes * K / (ms_max * 1e-3) / 1e9
+    to_gbs = lambda ms: total_bytes * K / (ms * 1e-3) / 1e9
+    value = to_gbs(ms_med)
 
-    # ---- per-shape device times (L2 flushed between launches; outside the headline region) ----
+    # ---- parity of what was just timed: one image per shape of the step's own output vs the oracle ----
+    parity = None
+    if rank == 0 and not args.no_parity_check:
+        import oracle
+        with torch.cuda.stream(stream):
+            graphs[0].replay()
+            stream.synchronize()
+        worst = 0.0
+        for (C, H), (x, gamma, beta, y) in zip(SHAPES, sets[0]):
+            want = oracle.group_norm(x[:1].float().cpu().numpy(), gamma.cpu().numpy(), beta.cpu().numpy(),
+                                     GROUPS, EPS, True)
+            got = y[:1].float().cpu().numpy().astype(np.float64)
+            worst = max(worst, float((np.abs(got - want) / (2e-3 + 2e-3 * np.abs(want))).max()))
+        parity = {"max_err_over_tol": round(worst, 4), "tolerance": 2e-3, "images": len(SHAPES),
+                  "what": "image 0 of each of the four tensors as written by the timed step, against the "
+                          "CPU oracle (the reference's kernels restated in C)"}
+
+    # ---- per-shape device times of single launches (L2 flushed between launches; not the headline) ----
     per_shape = []
     with torch.cuda.stream(stream):
         flush = torch.empty(2 * L2_BYTES, dtype=torch.uint8, device=dev)
@@ -377,6 +446,7 @@ def run_ours(args) -> None:
         del flush
 
     # ---- end to end through the host-buffer C-ABI call ------------------------------------------
+    numa = bind_to_gpu_numa_node(torch, local_rank)      # before the page-locked buffers are allocated
     e2e_steps = max(2, min(K, 5))
     pipe = ops.HostPipeline(max_slot_bytes=16 << 20, depth=6, device=local_rank)
     host = []
@@ -392,20 +462,37 @@ def run_ours(args) -> None:
         return float(host[-1][1][-1, -1, -1, -1])        # the step's result is read on the host
 
     e2e_step()
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize(dev)
+    barrier()
     t0 = time.perf_counter()
     for _ in range(e2e_steps):
         e2e_step()
     torch.cuda.synchronize(dev)
     e2e_s = time.perf_counter() - t0
-    te = torch.tensor([e2e_s], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(te, op=dist.ReduceOp.MAX)
-    e2e_value = total_bytes * e2e_steps / float(te.item()) / 1e9
-    # the host path runs groups in smaller calls (other cluster sizes): same values within fp16 tolerance
-    ok = bool((host[0][1].to(dev).float() - sets[0][0][3].float()).abs().max() <= 4e-3)
+    # copies alone (same buffers, same slots' worth of bytes, both directions at once): what PCIe and
+    # the host memory give this rank while all ranks copy together
+    copy_streams = [torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)]
+    d_stage = [torch.empty_like(sets[0][k][0]) for k in range(len(SHAPES))]
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(2):
+        with torch.cuda.stream(copy_streams[0]):
+            for k, (h_in, _, _, _) in enumerate(host):
+                d_stage[k].copy_(h_in, non_blocking=True)
+        with torch.cuda.stream(copy_streams[1]):
+            for k, (_, h_out, _, _) in enumerate(host):
+                h_out.copy_(sets[0][k][3], non_blocking=True)
+        torch.cuda.synchronize(dev)
+    copy_s = (time.perf_counter() - t0) / 2
+    del d_stage
+    te = max_over_ranks([e2e_s, copy_s])
+    e2e_value = total_bytes * e2e_steps / te[0] / 1e9
+    # the host path runs groups in smaller calls (other plans): same values within fp16 tolerance
+    with torch.cuda.stream(stream):
+        step(sets[0])
+        stream.synchronize()
+    e2e_step()
+    ok = all(bool(((h_out.to(dev).float() - t[3].float()).abs() - 2e-3 * t[3].float().abs()).max() <= 2e-3)
+             for (_, h_out, _, _), t in zip(host, sets[0]))
     pipe.close()
     half_bytes = sum(b_local * C * H * H * 2 for C, H in SHAPES)
     hb = torch.tensor([half_bytes], device=dev, dtype=torch.float64)
@@ -416,9 +503,21 @@ def run_ours(args) -> None:
     if rank == 0:
         peak, peak_kind = measured_peak()
         per_gpu = value / world
+        if args.chain:
+            kernel = ("gn_resident_kernel<__half, silu> / gn_register_kernel (one launch per tensor): " +
+                      ", ".join(f"[{p['shape'][0]},{p['shape'][1]},{p['shape'][2]},{p['shape'][3]}] {p['path']}"
+                                + (f" cluster {p['cluster']} x {p['nclusters']}" if p["path"] == "cluster ring" else "")
+                                for p in per_shape))
+        else:
+            teams = [(multi_plan[2] >> (8 * k)) & 0xff for k in range(len(SHAPES))] if multi_plan else []
+            kernel = (f"gn_multi_kernel<__half, silu, 8 vectors/thread> (the step's one launch): {multi_plan[1]} CTAs "
+                      f"in gangs of {multi_plan[0]}, CTAs per slab {teams} for the four tensors")
+        # DRAM traffic per launch: from the ncu capture of the same kernel on the 4-image shard
+        # (profiles/), scaled by the algorithmic bytes; only the plan of that capture is measured
+        traffic_ratio = None if args.chain else NCU_TRAFFIC_RATIO_MULTI
         line = {
             "metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world, "steps": K,
-            "warmup": W, "ms_per_step": round(ms_max / K, 5), "higher_is_better": True,
+            "warmup": W, "ms_per_step": round(ms_med / K, 5), "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32 arithmetic on f16 storage",
             "data": "synthetic",
             "config": {"workload": "SD VAE decoder GroupNorm(32, eps 1e-6)+SiLU fp16, batch 8: "
@@ -426,21 +525,34 @@ def run_ours(args) -> None:
                        "sharding": f"{BATCH // world if BATCH % world == 0 else 'ragged'} images per GPU, no collective",
                        "l2": f"in+out per step per GPU {step_bytes / 1e6:.0f} MB, ring of {ring} buffer "
                              f"set(s): a buffer is reused after >= {ring * step_bytes / 1e6:.0f} MB of other traffic (L2 126 MB)",
-                       "launch": "one CUDA graph per step (4 kernel nodes)"},
+                       "launch": f"one CUDA graph per step ({launches_per_step} kernel node(s))"},
+            "timing": {"blocks": R, "steps_per_block": K,
+                       "block_ms": {"min": round(min(block_ms), 4), "median": round(ms_med, 4), "max": round(max(block_ms), 4)},
+                       "how": "every block of K graph replays between its own CUDA events on the launching stream, "
+                              "max over ranks per block, median over blocks; value and ms_per_step are the median block's"},
             "elements_per_s": round(value * 1e9 / 4, 0),
             "e2e": {"value": round(e2e_value, 2), "unit": UNIT, "steps": e2e_steps,
                     "h2d_bytes_per_step": int(hb.item()), "d2h_bytes_per_step": int(hb.item()),
-                    "matches_device_path": bool(ok)},
-            "gpu_launches": K * launches_per_step * world,
+                    "matches_device_path": bool(ok), "host_numa": numa,
+                    "copies_alone": {"gbs_both_directions": round(2 * hb.item() / te[1] / 1e9, 2),
+                                     "what": "the same bytes copied in and out at once with no kernel, all ranks "
+                                             "together (max over ranks): the ceiling PCIe and host memory set"}},
+            "gpu_launches": K * R * launches_per_step * world,
             "clocks": clocks,
-            "roofline": {"bound": "hbm", "kernel": "gn_resident_kernel<__half, silu, 8 vectors/thread> (three of the four launches of a step, 95 % of its time)",
+            "roofline": {"bound": "hbm", "kernel": kernel,
                          "achieved": round(per_gpu, 1), "peak": peak, "unit": UNIT,
                          "frac": round(per_gpu / peak, 4), "peak_source": f"of {peak_kind}",
-                         "traffic": (None if NCU_TRAFFIC_RATIO is None
-                                     else round(NCU_TRAFFIC_RATIO * step_bytes / launches_per_step)),
+                         "traffic": None if traffic_ratio is None else round(traffic_ratio * step_bytes / launches_per_step),
+                         "traffic_source": None if traffic_ratio is None else NCU_TRAFFIC_SOURCE,
                          "per_gpu": True},
-            "per_shape": per_shape,
+            "other_launch_form": {"what": "one launch per step (gn_multi_kernel)" if args.chain else
+                                          "four launches per step, one per tensor (cluster ring / register kernels)",
+                                  "value": round(to_gbs(statistics.median(other_ms)), 2), "unit": UNIT,
+                                  "ms_per_step": round(statistics.median(other_ms) / K, 5)},
+            "per_shape_single_launch": per_shape,
         }
+        if parity is not None:
+            line["parity_check"] = parity
         if world == 1 and not args.no_cpu_baseline:
             r = time_cpu_reference(steps=1000, warmup=1, budget_s=12.0, exact_steps=False)
             line["cpu_baseline"] = {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")}
@@ -449,7 +561,6 @@ def run_ours(args) -> None:
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
-
 
 
 # ---------------------------------------------------------------------------------------------
@@ -932,9 +1043,12 @@ def run_ops(args) -> None:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--blocks", type=int, default=25, help="timed blocks of --steps steps each (the median block is reported)")
+    ap.add_argument("--chain", action="store_true", help="launch the step as four kernels, one per tensor, instead of one")
+    ap.add_argument("--no-parity-check", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--ops", action="store_true", help="per-kernel table over all named shapes")
     ap.add_argument("--case", default="", help="with --ops: only cases whose name contains this")

@@ -96,6 +96,57 @@ size_t sdfl_groupnorm_workspace_bytes_ex(int64_t batch, int64_t channels, int64_
 int sdfl_groupnorm_plan(int64_t batch, int64_t channels, int64_t hw, int64_t num_groups, int dtype,
                         int path, int cluster_or_splits, int64_t plan[8]);
 
+/* GroupNorm(+SiLU) of a list of independent tensors in ONE launch.  The reference normalises one
+ * tensor per GroupNorm::forward call (NN/GroupNorm.cpp:68-170) and runs its call sites one after
+ * another on one queue (NN/ResBlock.cpp:125-142, M/Decoder.cpp:523-536); tensors that do not depend
+ * on each other -- the images of a batch shard held as separate buffers, the conditional and
+ * unconditional halves of a guidance pair, the layers of a benchmark step -- can be handed over
+ * together here.  Every (image, group) slab of every tensor becomes one item of a work list that a
+ * single grid of resident CTAs walks (largest slabs first), so the launch, first-data and drain
+ * latencies are paid once and small tensors fill the SMs that large ones leave idle.  Results per
+ * tensor are those of sdfl_groupnorm_forward within the rounding of a different summation order.
+ * All tensors share dtype and fuse_silu; each has its own shape, eps and weights.
+ * Requirements per tensor: 16-byte aligned in/out, hw * element size a multiple of 16, slabs
+ * (channels / num_groups * hw elements) of at least 512 bytes; at most SDFL_GN_MULTI_MAX non-empty
+ * tensors.  Otherwise SDFL_ERR_UNSUPPORTED is returned and nothing is launched (call
+ * sdfl_groupnorm_forward per tensor).  out == in is allowed per tensor; different tensors must not
+ * overlap (SDFL_ERR_OVERLAP).
+ * workspace: NULL, or sdfl_groupnorm_multi_workspace_bytes() bytes of device memory that were
+ * zero-filled once before their first use (the kernel leaves them ready for the next launch).
+ * The CTAs that share a slab exchange their partial moments through it and the work list's
+ * counter lives there.  With NULL a buffer inside the library is used, shared by all such calls
+ * on the device: pass an own workspace per stream when two of these launches could overlap on the
+ * GPU.  The grid is sized to be resident as a whole (its CTAs wait for each other, every wait
+ * bounded): run it on a device that is not oversubscribed by other long-running kernels. */
+enum { SDFL_GN_MULTI_MAX = 8 };
+typedef struct sdfl_gn_tensor {
+    const void *in;
+    void *out;
+    const float *gamma;
+    const float *beta;
+    int64_t batch, channels, hw, num_groups;
+    float eps;
+} sdfl_gn_tensor;
+size_t sdfl_groupnorm_multi_workspace_bytes(void);
+int sdfl_groupnorm_forward_multi(const sdfl_gn_tensor *tensors, int count, int fuse_silu, int dtype,
+                                 void *workspace, size_t workspace_bytes, void *stream);
+/* The same with tuning knobs (tests, sweeps, profiling); knobs = 0 is the automatic plan.
+ * knobs: bits 0-7 CTAs per gang (a gang works on one large slab, or on several small ones at once);
+ * 8-9 team size per tensor (1 = the whole gang on every slab, 2 = by slab size); bit 10 cooperative
+ * launch; bit 11 / bit 30 force / forbid that half of the gangs start at the small end of the list;
+ * 12-13 the share of a slab per CTA that team sizes aim at, in units of 128 KB; 14-15 item order
+ * (1 = static, 2 = drawn from a counter); 16-23 ring chunk in KB (16 or 32); 24-27 ring slots; 28-29
+ * chunks held between the passes + 1.
+ * d_trace: NULL, or device memory of grid * 16 64-bit words that receives, per CTA, nanosecond time
+ * stamps (start, barriers set up, first chunk landed, first slab's moments done, its statistics
+ * known, its stores issued, all slabs done, first copy issued), the SM number, the number of
+ * slabs handled and the time one thread spent waiting for statistics / for chunks in either pass.
+ * plan (optional, host): {CTAs per gang, grid size, team sizes of the first four tensors (8 bits
+ * each), shared memory per CTA}. */
+int sdfl_groupnorm_forward_multi_ex(const sdfl_gn_tensor *tensors, int count, int fuse_silu, int dtype,
+                                    void *workspace, size_t workspace_bytes, int knobs,
+                                    unsigned long long *d_trace, int plan[4], void *stream);
+
 /* GroupNorm(+SiLU) for callers that may not allocate device memory and therefore cannot supply
  * the workspace sdfl_groupnorm_forward may ask for.  (No counterpart in the reference: it
  * creates and releases its mean/variance buffers inside every forward call,

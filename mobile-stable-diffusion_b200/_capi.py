@@ -31,6 +31,15 @@ class SdflError(RuntimeError):
 
 
 _p = C.c_void_p
+
+
+class GnTensor(C.Structure):
+    """sdfl_gn_tensor of include/sdfl.h."""
+    _fields_ = [("in_", C.c_void_p), ("out", C.c_void_p), ("gamma", C.c_void_p), ("beta", C.c_void_p),
+                ("batch", C.c_int64), ("channels", C.c_int64), ("hw", C.c_int64),
+                ("num_groups", C.c_int64), ("eps", C.c_float)]
+
+
 _i64 = C.c_int64
 _f = C.c_float
 _i = C.c_int
@@ -48,6 +57,9 @@ SIGNATURES = {
     "sdfl_groupnorm_forward_ex": (_i, [_p, _p, _p, _p, _i64, _i64, _i64, _i64, _f, _i, _i, _p, _sz,
                                        _i, _i, _p]),
     "sdfl_groupnorm_workspace_bytes_ex": (_sz, [_i64, _i64, _i64, _i64, _i, _i, _i]),
+    "sdfl_groupnorm_multi_workspace_bytes": (_sz, []),
+    "sdfl_groupnorm_forward_multi": (_i, [_p, _i, _i, _i, _p, _sz, _p]),
+    "sdfl_groupnorm_forward_multi_ex": (_i, [_p, _i, _i, _i, _p, _sz, _i, _p, C.POINTER(_i), _p]),
     "sdfl_groupnorm_forward_noalloc": (_i, [_p, _p, _p, _p, _i64, _i64, _i64, _i64, _f, _i, _i, _p]),
     "sdfl_groupnorm_bias_forward": (_i, [_p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _f, _i, _i, _p, _sz, _p]),
     "sdfl_groupnorm_bias_forward_ex": (_i, [_p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _f, _i, _i, _p, _sz, _i, _i, _p]),

@@ -20,7 +20,7 @@ BUILD = os.path.join(PKG, "build")
 LIBDIR = os.path.join(PKG, "lib")
 LIB = os.path.join(LIBDIR, "libsdfl.so")
 
-SOURCES = ["groupnorm.cu", "gn_ring.cu", "gn_register.cu", "gn_split.cu", "layernorm.cu", "elementwise.cu", "embedding.cu", "permute.cu", "softmax.cu", "resample.cu", "capi.cu"]
+SOURCES = ["groupnorm.cu", "gn_ring.cu", "gn_multi.cu", "gn_register.cu", "gn_split.cu", "layernorm.cu", "elementwise.cu", "embedding.cu", "permute.cu", "softmax.cu", "resample.cu", "capi.cu"]
 HEADERS = [os.path.join(CSRC, "common.cuh"), os.path.join(CSRC, "kernels.h"),
            os.path.join(CSRC, "gn_internal.h"), os.path.join(CSRC, "gn_device.cuh"),
            os.path.join(ROOT, "include", "sdfl.h")]

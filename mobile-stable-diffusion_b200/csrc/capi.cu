@@ -137,6 +137,50 @@ int sdfl_groupnorm_forward_ex(const void *in, void *out, const float *gamma, con
                       workspace, workspace_bytes, path, cluster_or_splits, as_stream(stream));
 }
 
+size_t sdfl_groupnorm_multi_workspace_bytes(void) { return sdfl::kGnMultiScratchBytes; }
+
+// GroupNorm(+SiLU) of up to SDFL_GN_MULTI_MAX tensors in one persistent launch; see sdfl.h.
+int sdfl_groupnorm_forward_multi_ex(const sdfl_gn_tensor *tensors, int count, int fuse_silu, int dtype,
+                                    void *workspace, size_t workspace_bytes, int knobs,
+                                    unsigned long long *d_trace, int plan[4], void *stream) {
+    if (plan) plan[0] = plan[1] = plan[2] = plan[3] = 0;
+    if (count < 0 || !dtype_ok(dtype) || knobs < 0) return SDFL_ERR_INVALID_VALUE;
+    if (count == 0) return SDFL_OK;
+    if (!tensors) return SDFL_ERR_INVALID_POINTER;
+    if (workspace != nullptr && workspace_bytes < sdfl::kGnMultiScratchBytes) return SDFL_ERR_WORKSPACE;
+    sdfl::GnMultiTensor ts[SDFL_GN_MULTI_MAX];
+    int n = 0;
+    for (int k = 0; k < count; ++k) {
+        const sdfl_gn_tensor &t = tensors[k];
+        int rc = gn_validate(t.in, t.out, t.gamma, t.beta, t.batch, t.channels, t.hw, t.num_groups, t.eps, dtype);
+        if (rc != SDFL_OK) return rc;
+        if (t.batch == 0 || t.hw == 0) continue;            // an empty tensor is no work
+        if (n == SDFL_GN_MULTI_MAX) return SDFL_ERR_UNSUPPORTED;
+        ts[n++] = sdfl::GnMultiTensor{t.in, t.out, t.gamma, t.beta, t.batch, t.channels, t.hw, t.num_groups, t.eps};
+    }
+    // outputs must not overlap one another or another tensor's input
+    for (int i = 0; i < n; ++i)
+        for (int j = 0; j < n; ++j) {
+            if (i == j) continue;
+            const int64_t bi = ts[i].batch * ts[i].channels * ts[i].hw * esize(dtype);
+            const int64_t bj = ts[j].batch * ts[j].channels * ts[j].hw * esize(dtype);
+            if (any_overlap(ts[i].out, bi, ts[j].out, bj) || any_overlap(ts[i].out, bi, ts[j].in, bj))
+                return SDFL_ERR_OVERLAP;
+        }
+    if (n == 0) return SDFL_OK;
+    if (sdfl::gn_multi_check(ts, n, dtype) != 0) return SDFL_ERR_UNSUPPORTED;
+    cudaError_t e = sdfl::gn_multi_launch(ts, n, dtype, fuse_silu ? sdfl::kActSilu : sdfl::kActNone, knobs,
+                                          workspace, d_trace, plan, as_stream(stream));
+    if (e == cudaErrorInvalidConfiguration || e == cudaErrorInvalidValue) return SDFL_ERR_UNSUPPORTED;
+    return wrap(e);
+}
+
+int sdfl_groupnorm_forward_multi(const sdfl_gn_tensor *tensors, int count, int fuse_silu, int dtype,
+                                 void *workspace, size_t workspace_bytes, void *stream) {
+    return sdfl_groupnorm_forward_multi_ex(tensors, count, fuse_silu, dtype, workspace, workspace_bytes, 0,
+                                           nullptr, nullptr, stream);
+}
+
 // GroupNorm(+SiLU) through the split path with the scratch in the library's own fixed device
 // array: for callers that are not allowed to allocate (see sdfl.h).  No allocation is made
 // here or below; shapes whose scratch would exceed the array are refused before any launch.
@@ -470,7 +514,11 @@ int sdfl_elemwise_add(const void *A, const void *B, void *C, int64_t n, int dtyp
 
 int sdfl_device_status(unsigned int *value, int clear, void *stream) {
     if (!value) return SDFL_ERR_INVALID_POINTER;
-    return wrap(sdfl::gn_read_status(value, clear != 0, as_stream(stream)));
+    unsigned int ring = 0, multi = 0;
+    cudaError_t e = sdfl::gn_read_status(&ring, clear != 0, as_stream(stream));
+    if (e == cudaSuccess) e = sdfl::gn_multi_read_status(&multi, clear != 0, as_stream(stream));
+    *value = ring | multi;
+    return wrap(e);
 }
 
 int sdfl_selftest_bounded_wait(long long limit_cycles, void *stream) {

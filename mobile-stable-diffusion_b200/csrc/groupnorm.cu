@@ -190,6 +190,7 @@ cudaError_t gn_make_plan(const GnShape &s, const void *in, const void *out, int 
     if (splits < 1) splits = 1;
     if (splits > 1024) splits = 1024;
     if (force_cluster > 0) splits = force_cluster & 0xffff;
+    if (splits < 1) splits = 1;          // a forced count whose low 16 bits are zero
     int64_t chunk = (slab_elems + splits - 1) / splits;
     chunk = ((chunk + vec - 1) / vec) * vec;
     splits = (slab_elems + chunk - 1) / chunk;

@@ -68,6 +68,35 @@ cudaError_t upsample_nearest_launch(const void *in, void *out, int64_t planes, i
 cudaError_t concat_launch(const void *in1, const void *in2, void *out, int64_t batch, int64_t n1,
                           int64_t n2, int dtype, cudaStream_t stream);
 
+// GroupNorm (+SiLU) over a list of tensors in one persistent launch (gn_multi.cu).  All tensors
+// share dtype and activation; each needs 16-byte aligned buffers, hw * element size a multiple
+// of 16 and slabs of at least 512 bytes (gn_multi_check returns 0).
+constexpr int kGnMultiMaxTensors = 8;
+constexpr int kGnMultiMaxCtas = 512;
+constexpr int kGnMultiMaxGangs = 512;
+constexpr size_t kGnMultiScratchBytes = 16 + static_cast<size_t>(kGnMultiMaxGangs) * 8 * 8 +
+                                        static_cast<size_t>(kGnMultiMaxCtas) * (4 + 8 * 16);
+struct GnMultiTensor {
+    const void *in;
+    void *out;
+    const float *w;
+    const float *b;
+    int64_t batch, channels, hw, groups;
+    float eps;
+};
+int gn_multi_check(const GnMultiTensor *ts, int n, int dtype);
+// knobs (0 = automatic): bits 0-7 CTAs per gang; 8-9 teams (1: the whole gang on every slab, 2: a team
+// size per tensor); 10 cooperative launch; 11 upper half of the gangs starts at the small end of the
+// list (30: never); 12-13 share of a slab per CTA the team sizes aim at, in units of 128 KB; 14-15
+// order of the items (1 static, 2 drawn from a counter); 16-23 ring chunk in KB (16 or 32); 24-27
+// ring slots; 28-29 held chunks + 1.
+// scratch: kGnMultiScratchBytes of device memory, zero before its first use, or nullptr for the
+// library's own.  trace: nullptr, or [grid][16] device words for the time stamps of one launch.
+// plan_out (optional): {CTAs per gang, grid, split, shared memory bytes}.
+cudaError_t gn_multi_launch(const GnMultiTensor *ts, int n, int dtype, int act, int knobs, void *scratch,
+                            unsigned long long *trace, int *plan_out, cudaStream_t stream);
+cudaError_t gn_multi_read_status(unsigned int *value, bool clear, cudaStream_t stream);
+
 // The split path with its scratch in a fixed array inside the library (64 KiB per device: up to
 // 8192 (mean, M2) pairs, i.e. batch * groups * chunks-per-slab <= 8192).  Allocates nothing; the
 // first call on a device resolves the array's device address.

@@ -14,7 +14,7 @@ from . import _capi
 from ._capi import F16, F32, GN_AUTO, GN_REGISTER, GN_RESIDENT, GN_SPLIT, SdflError, check, lib
 
 __all__ = [
-    "groupnorm", "groupnorm_bias", "chunkwise_add", "groupnorm_noalloc", "groupnorm_plan", "layernorm", "add_layernorm", "gelu_multiply", "silu", "gelu", "quick_gelu",
+    "groupnorm", "groupnorm_multi", "groupnorm_bias", "chunkwise_add", "groupnorm_noalloc", "groupnorm_plan", "layernorm", "add_layernorm", "gelu_multiply", "silu", "gelu", "quick_gelu",
     "elemwise_add", "token_embedding", "timestep_embedding", "local_reduction_mean",
     "local_reduction_variance", "group_norm_apply", "layer_norm_apply", "device_status",
     "selftest_bounded_wait",
@@ -109,6 +109,60 @@ def groupnorm(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor, num_grou
             num_groups, eps, int(silu), code, ws.data_ptr(), ws.numel(), path, cluster_or_splits,
             _stream(stream)), "sdfl_groupnorm_forward")
     return out
+
+
+_multi_workspaces: dict[tuple[int, int], torch.Tensor] = {}
+
+
+def _multi_workspace(device: torch.device, stream_handle: int) -> torch.Tensor:
+    """Zero-filled exchange scratch of the multi-tensor GroupNorm, one per (device, stream):
+    launches on different streams may overlap on the GPU and must not share it."""
+    key = (device.index if device.index is not None else torch.cuda.current_device(), stream_handle)
+    ws = _multi_workspaces.get(key)
+    if ws is None:
+        ws = torch.zeros(int(lib.sdfl_groupnorm_multi_workspace_bytes()), dtype=torch.uint8, device=device)
+        _multi_workspaces[key] = ws
+    return ws
+
+
+def groupnorm_multi(xs, gammas, betas, num_groups, eps=1e-5, silu: bool = False, outs=None,
+                    knobs: int = 0, trace: torch.Tensor | None = None, stream=None, plan: list | None = None):
+    """GroupNorm(+SiLU) of a list of independent NCHW tensors in one launch
+    (sdfl_groupnorm_forward_multi).  `num_groups` and `eps` may be scalars or per-tensor lists.
+    Raises SdflError(ERR_UNSUPPORTED) when a tensor does not meet the call's requirements
+    (alignment, hw * element size a multiple of 16, more than 8 tensors)."""
+    n = len(xs)
+    if len(gammas) != n or len(betas) != n:
+        raise ValueError("xs, gammas and betas must have the same length")
+    groups = list(num_groups) if isinstance(num_groups, (list, tuple)) else [num_groups] * n
+    epss = list(eps) if isinstance(eps, (list, tuple)) else [eps] * n
+    outs = [torch.empty_like(x) for x in xs] if outs is None else list(outs)
+    if n == 0:
+        return outs
+    code = _dtype_code(xs[0])
+    arr = (_capi.GnTensor * n)()
+    for k, (x, g, b, o) in enumerate(zip(xs, gammas, betas, outs)):
+        if x.dim() < 2 or _dtype_code(x) != code or o.shape != x.shape or o.dtype != x.dtype:
+            raise ValueError("tensors must be [batch, channels, ...] of one dtype; outs must match")
+        B, Cc = x.shape[0], x.shape[1]
+        arr[k].in_ = _dev(x, "x")
+        arr[k].out = _dev(o, "out")
+        arr[k].gamma = _f32(g, "gamma")
+        arr[k].beta = _f32(b, "beta")
+        arr[k].batch, arr[k].channels = B, Cc
+        arr[k].hw = x.numel() // (B * Cc) if B * Cc else 0
+        arr[k].num_groups = groups[k]
+        arr[k].eps = epss[k]
+    sh = _stream(stream)
+    ws = _multi_workspace(xs[0].device, sh)
+    pl = (C.c_int * 4)()
+    with torch.cuda.device(xs[0].device):
+        check(lib.sdfl_groupnorm_forward_multi_ex(
+            arr, n, int(silu), code, ws.data_ptr(), ws.numel(), knobs,
+            0 if trace is None else trace.data_ptr(), pl, sh), "sdfl_groupnorm_forward_multi")
+    if plan is not None:
+        plan[:] = [int(v) for v in pl]
+    return outs
 
 
 def groupnorm_bias(x: torch.Tensor, channel_bias: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor,

@@ -91,6 +91,42 @@ def test_workspace_query_and_plan_without_device():
     assert lib.sdfl_groupnorm_plan(2, 30, 64, 32, 0, 0, 0, plan) == cap.ERR_INVALID_VALUE
 
 
+def test_forced_split_count_with_zero_low_bits_is_clamped():
+    """cluster_or_splits = 65536 has no chunk count in its low 16 bits: one chunk, not a division by zero."""
+    cap = load_package()._capi
+    lib = cap.lib
+    assert lib.sdfl_groupnorm_workspace_bytes_ex(2, 320, 4096, 32, 0, cap.GN_SPLIT, 65536) == 2 * 32 * 1 * 8
+    plan = (C.c_int64 * 8)()
+    assert lib.sdfl_groupnorm_plan(2, 320, 4096, 32, 0, cap.GN_SPLIT, 65536, plan) == cap.OK
+    assert plan[0] == cap.GN_SPLIT and plan[3] == 1
+
+
+def test_multi_tensor_call_validates_without_a_device():
+    cap = load_package()._capi
+    lib = cap.lib
+    assert lib.sdfl_groupnorm_multi_workspace_bytes() >= 4096
+    A, B = 4096, 1 << 20
+    arr = (cap.GnTensor * 2)()
+    for k in range(2):
+        arr[k].in_, arr[k].out, arr[k].gamma, arr[k].beta = A + k * (1 << 22), B + k * (1 << 22), A, A
+        arr[k].batch, arr[k].channels, arr[k].hw, arr[k].num_groups, arr[k].eps = 1, 64, 256, 32, 1e-5
+    assert lib.sdfl_groupnorm_forward_multi(None, 2, 1, 0, None, 0, None) == cap.ERR_INVALID_POINTER
+    assert lib.sdfl_groupnorm_forward_multi(arr, 0, 1, 0, None, 0, None) == cap.OK
+    assert lib.sdfl_groupnorm_forward_multi(arr, 2, 1, 5, None, 0, None) == cap.ERR_INVALID_VALUE
+    assert lib.sdfl_groupnorm_forward_multi(arr, 2, 1, 0, A, 16, None) == cap.ERR_WORKSPACE
+    arr[1].channels = 30                                    # not divisible by the groups
+    assert lib.sdfl_groupnorm_forward_multi(arr, 2, 1, 0, None, 0, None) == cap.ERR_INVALID_VALUE
+    arr[1].channels = 64
+    arr[1].out = arr[0].out                                 # two tensors, one output buffer
+    assert lib.sdfl_groupnorm_forward_multi(arr, 2, 1, 0, None, 0, None) == cap.ERR_OVERLAP
+    arr[1].out = B + (1 << 22)
+    arr[1].hw = 9                                           # 9 * 4 bytes: not a multiple of 16
+    assert lib.sdfl_groupnorm_forward_multi(arr, 2, 1, 0, None, 0, None) == cap.ERR_UNSUPPORTED
+    arr[1].batch = 0                                        # an empty tensor is skipped, the other one is valid
+    arr[0].batch = 0
+    assert lib.sdfl_groupnorm_forward_multi(arr, 2, 1, 0, None, 0, None) == cap.OK
+
+
 def test_missing_library_is_a_loud_import_error(tmp_path):
     cap = load_package()._capi
     with pytest.raises(ImportError):
