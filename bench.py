@@ -384,7 +384,9 @@ def run_ours(args) -> None:
         for i in range(W):
             other_graphs[i % ring].replay()
         barrier()
-        other_ms = [a.elapsed_time(b) for a, b in timed_blocks(other_graphs, min(R, 7))]
+        other_evs = timed_blocks(other_graphs, min(R, 7))
+        barrier()
+        other_ms = [a.elapsed_time(b) for a, b in other_evs]
         del other_graphs
 
     def max_over_ranks(values):

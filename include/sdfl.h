@@ -244,6 +244,14 @@ int sdfl_groupnorm_concat_forward(const void *in1, int64_t channels1, const void
  * output == input allowed, as the reference's callers do. */
 int sdfl_softmax(const void *input, void *output, int64_t rows, int64_t chunk_size, int dtype, void *stream);
 
+/* K/multi_head_attention.cl:28-54 local_softmax(input, output, __local reductionSums) launched with one
+ * work-group of CONTEXT_LENGTH = 77 work-items per row over numHeads * 77 rows, in place
+ * (NN/MultiHeadAttention.cpp:213-225): the text encoder's attention softmax, after the causal mask
+ * (-inf above the diagonal) has been added.  Same function as sdfl_softmax, kept under the
+ * reference kernel's name; row_len is the work-group size of the reference launch.  Masked
+ * entries come out as exact zeros. */
+int sdfl_local_softmax(const void *input, void *output, int64_t rows, int64_t row_len, int dtype, void *stream);
+
 /* K/util.cl:136-148  chunkwise_add(A, chunk, C, chunk_size) over n work-items:
  * C[i] = A[i] + chunk[i / chunk_size]; C may be A (NN/ResBlock.cpp:188-191). */
 int sdfl_chunkwise_add(const void *A, const void *chunk, void *C, int64_t n, int64_t chunk_size,

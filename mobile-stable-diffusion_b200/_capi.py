@@ -71,6 +71,7 @@ SIGNATURES = {
     "sdfl_concat_buffer": (_i, [_p, _p, _p, _i64, _i64, _i64, _i, _p]),
     "sdfl_groupnorm_concat_forward": (_i, [_p, _i64, _p, _i64, _p, _p, _p, _i64, _i64, _i64, _f, _i, _i, _p, _sz, _p]),
     "sdfl_softmax": (_i, [_p, _p, _i64, _i64, _i, _p]),
+    "sdfl_local_softmax": (_i, [_p, _p, _i64, _i64, _i, _p]),
     "sdfl_chunkwise_add": (_i, [_p, _p, _p, _i64, _i64, _i, _p]),
     "sdfl_groupnorm_plan": (_i, [_i64, _i64, _i64, _i64, _i, _i, _i, C.POINTER(_i64)]),
     "sdfl_layernorm_forward": (_i, [_p, _p, _p, _p, _i64, _i64, _f, _i, _p]),

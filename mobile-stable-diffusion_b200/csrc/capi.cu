@@ -338,6 +338,10 @@ int sdfl_softmax(const void *input, void *output, int64_t rows, int64_t chunk_si
     return wrap(sdfl::softmax_launch(input, output, rows, chunk_size, dtype, as_stream(stream)));
 }
 
+int sdfl_local_softmax(const void *input, void *output, int64_t rows, int64_t row_len, int dtype, void *stream) {
+    return sdfl_softmax(input, output, rows, row_len, dtype, stream);
+}
+
 int sdfl_chunkwise_add(const void *A, const void *chunk, void *C, int64_t n, int64_t chunk_size,
                        int dtype, void *stream) {
     if (!dtype_ok(dtype) || n < 0 || chunk_size <= 0) return SDFL_ERR_INVALID_VALUE;

@@ -34,8 +34,9 @@
 // Exchange of the partial (n, mean, M2) results.  A gang is K plain CTAs of a grid that is
 // resident as a whole (at most the number of CTAs the device can hold at once), not a thread-block
 // cluster: clusters of 8 reach 264 of the 296 CTA slots of a B200 and cannot change their size from
-// item to item.  A CTA publishes its result in a global scratch (st.release.gpu of a token after
-// the values) and polls its team's (ld.acquire.gpu, bounded).  Tokens are launch-unique: all CTAs
+// item to item.  A CTA publishes its result in a global scratch as two 64-bit words that
+// carry the item's token beside the value, and polls its team's words until they show the token
+// (relaxed accesses at GPU scope, bounded).  Tokens are launch-unique: all CTAs
 // read a sequence word at start and the last CTA to leave (an arrival counter) advances it and
 // clears the item counter, so the scratch needs no clearing between launches; it has to be zero
 // before its first use only.  Launches that share a scratch must not overlap on the GPU.
@@ -64,14 +65,16 @@ static_assert(kOffPeer + kNumBufs * 32 * 16 <= kMultiHeader, "header layout");
 constexpr uint32_t kEndMark = 0xffffffffu;       // in a slot's item word: no more items for this CTA
 static_assert(kMultiHeader % 128 == 0, "header layout");
 
-struct ExchSlot { uint32_t token; float n, mean, m2; };
-struct GangTurn { uint32_t token, item; };
+// A CTA's result for one item: two 64-bit words, each the launch-unique token of the item in its upper
+// half and one value in its lower half.  A word is written and read whole, so a reader that finds the
+// token has the value with it and needs no fence or second round trip.
+struct ExchSlot { unsigned long long mean, m2; };
 struct ExchScratch {
     uint32_t seq;        // tokens of a launch are seq + 1 + turn
     uint32_t done;       // CTAs of the running launch that have finished
     // dynamic order: items handed out from the front of the list (low word) and from its back (high word)
     unsigned long long next;
-    GangTurn turn[kGnMultiMaxGangs][kNumBufs];     // the item of a gang's n-th turn, published by its first CTA
+    unsigned long long turn[kGnMultiMaxGangs][kNumBufs];   // (token << 32) | item of a gang's n-th turn, published by its first CTA
     uint32_t progress[kGnMultiMaxCtas];            // seq + number of turns a CTA has read
     ExchSlot slot[kGnMultiMaxCtas][kNumBufs];
 };
@@ -144,26 +147,18 @@ __device__ __forceinline__ unsigned long long global_timer() {
     return t;
 }
 
-__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t *p) {
-    uint32_t v;
-    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
 __device__ __forceinline__ uint32_t ld_relaxed_gpu(const uint32_t *p) {
     uint32_t v;
     asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
-__device__ __forceinline__ float ld_relaxed_gpu_f32(const float *p) {
-    float v;
-    asm volatile("ld.relaxed.gpu.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+__device__ __forceinline__ unsigned long long ld_relaxed_gpu_u64(const unsigned long long *p) {
+    unsigned long long v;
+    asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
     return v;
 }
-__device__ __forceinline__ void st_relaxed_gpu_f32(float *p, float v) {
-    asm volatile("st.relaxed.gpu.global.f32 [%0], %1;" ::"l"(p), "f"(v) : "memory");
-}
-__device__ __forceinline__ void st_release_gpu(uint32_t *p, uint32_t v) {
-    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+__device__ __forceinline__ void st_relaxed_gpu_u64(unsigned long long *p, unsigned long long v) {
+    asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
 
 // blockDim.x = 288: 256 consumer threads + the producer warp.  Chunks are 256 * NV vectors, so a full
@@ -244,7 +239,7 @@ gn_multi_kernel(const MultiArgs a) {
                 if (ngangs <= a.total_items) item = reversed ? a.total_items - 1u - (gang - nfront) : gang;
                 else if (gang < a.total_items) item = gang;
             } else if (a.dynamic) {
-                GangTurn *q = &a.x->turn[gang][turn % kNumBufs];
+                unsigned long long *q = &a.x->turn[gang][turn % kNumBufs];
                 const uint32_t token = base + turn + 1u;
                 if (rank == 0) {
                     // The entry is reused every kNumBufs turns: every CTA of the gang must have read
@@ -261,11 +256,11 @@ gn_multi_kernel(const MultiArgs a) {
                     uint32_t mine = kEndMark;
                     if (front + back < a.total_items)
                         mine = reversed ? a.total_items - 1u - static_cast<uint32_t>(back) : static_cast<uint32_t>(front);
-                    asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(&q->item), "r"(mine) : "memory");
-                    st_release_gpu(&q->token, token);
+                    st_relaxed_gpu_u64(q, (static_cast<unsigned long long>(token) << 32) | mine);
                 }
-                spin_until([&] { return ld_acquire_gpu(&q->token) == token; });
-                item = timed_out ? kEndMark : ld_relaxed_gpu(&q->item);
+                unsigned long long word = 0;
+                spin_until([&] { word = ld_relaxed_gpu_u64(q); return static_cast<uint32_t>(word >> 32) == token; });
+                item = timed_out ? kEndMark : static_cast<uint32_t>(word);
                 asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(&a.x->progress[blockIdx.x]), "r"(token) : "memory");
             } else if (turn < n_mine) {
                 item = item_at(turn);
@@ -386,10 +381,8 @@ gn_multi_kernel(const MultiArgs a) {
             c = warp_merge(c);
             if (lane == 0) {
                 ExchSlot *mine = &a.x->slot[blockIdx.x][buf];
-                st_relaxed_gpu_f32(&mine->n, c.n);
-                st_relaxed_gpu_f32(&mine->mean, c.mean);
-                st_relaxed_gpu_f32(&mine->m2, c.m2);
-                st_release_gpu(&mine->token, token);
+                st_relaxed_gpu_u64(&mine->mean, (static_cast<unsigned long long>(token) << 32) | __float_as_uint(c.mean));
+                st_relaxed_gpu_u64(&mine->m2, (static_cast<unsigned long long>(token) << 32) | __float_as_uint(c.m2));
             }
         }
 
@@ -408,19 +401,23 @@ gn_multi_kernel(const MultiArgs a) {
             float4 r = make_float4(0.f, 0.f, 0.f, 0.f);
             if (lane < g.k) {
                 const ExchSlot *ps = &a.x->slot[g.first_cta + lane][buf];
-                bool ok = ld_acquire_gpu(&ps->token) == token;
-                if (!ok) {
+                unsigned long long wm = ld_relaxed_gpu_u64(&ps->mean), w2 = ld_relaxed_gpu_u64(&ps->m2);
+                auto both = [&] { return static_cast<uint32_t>(wm >> 32) == token && static_cast<uint32_t>(w2 >> 32) == token; };
+                if (!both()) {
                     const long long t0 = clock64();
                     const long long limit = timed_out ? kWaitCyclesAfterTimeout : kWaitCycles;
-                    while (!(ok = ld_acquire_gpu(&ps->token) == token)) {
-                        if (clock64() - t0 > limit) break;
-                        __nanosleep(32);
-                    }
+                    do {
+                        if (clock64() - t0 > limit) { timed_out = true; break; }
+                        wm = ld_relaxed_gpu_u64(&ps->mean);
+                        w2 = ld_relaxed_gpu_u64(&ps->m2);
+                    } while (!both());
                 }
-                if (!ok) timed_out = true;
-                r.y = ld_relaxed_gpu_f32(&ps->n);
-                r.z = ld_relaxed_gpu_f32(&ps->mean);
-                r.w = ld_relaxed_gpu_f32(&ps->m2);
+                // peer `lane` owns vectors [q0, q1) of the slab
+                const uint32_t q0 = static_cast<uint32_t>((static_cast<uint64_t>(t.slab_vecs) * lane) / g.k);
+                const uint32_t q1 = static_cast<uint32_t>((static_cast<uint64_t>(t.slab_vecs) * (lane + 1)) / g.k);
+                r.y = static_cast<float>(q1 - q0) * VEC;
+                r.z = __uint_as_float(static_cast<uint32_t>(wm));
+                r.w = __uint_as_float(static_cast<uint32_t>(w2));
             }
             peer[buf * 32u + lane] = r;
             __syncwarp();
@@ -789,6 +786,16 @@ cudaError_t gn_multi_launch(const GnMultiTensor *ts_in, int n, int dtype, int ac
         }
     }
     if (!have) return cudaErrorInvalidConfiguration;
+    if (k_target == 0 && k_sized != 1) {
+        // One or two items per gang: the launch is a couple of waves and its length is that of the
+        // busiest gang; shares of 128 KB deal the work out more evenly than shares of 256 KB.
+        int64_t items = 0;
+        for (int64_t v : deal.items) items += v;
+        Deal fine;
+        if (items < 2 * static_cast<int64_t>(deal.gangs) &&
+            make_deal(&fine, deal.gang, true, 128 * 1024, dynamic, ctas, ts, slab_bytes))
+            deal = fine;
+    }
     const int team = deal.gang, gangs = deal.gangs, grid = deal.gangs * deal.gang;
     total_items = 0;
     for (int64_t v : deal.items) total_items += v;

@@ -18,7 +18,7 @@ __all__ = [
     "elemwise_add", "token_embedding", "timestep_embedding", "local_reduction_mean",
     "local_reduction_variance", "group_norm_apply", "layer_norm_apply", "device_status",
     "selftest_bounded_wait",
-    "launch_count", "HostPipeline", "GN_AUTO", "GN_RESIDENT", "GN_SPLIT", "GN_REGISTER", "groupnorm_nhwc", "permute_021", "permute_add", "softmax", "up_sample_nearest", "concat_channels", "groupnorm_concat",
+    "launch_count", "HostPipeline", "GN_AUTO", "GN_RESIDENT", "GN_SPLIT", "GN_REGISTER", "groupnorm_nhwc", "permute_021", "permute_add", "softmax", "local_softmax", "up_sample_nearest", "concat_channels", "groupnorm_concat",
 ]
 
 
@@ -281,6 +281,18 @@ def softmax(x: torch.Tensor, out: torch.Tensor | None = None, stream=None) -> to
     with torch.cuda.device(x.device):
         check(lib.sdfl_softmax(_dev(x, "x"), _dev(out, "out"), rows, dim, _dtype_code(x), _stream(stream)),
               "sdfl_softmax")
+    return out
+
+
+def local_softmax(x: torch.Tensor, out: torch.Tensor | None = None, stream=None) -> torch.Tensor:
+    """The text encoder's attention softmax (the reference's local_softmax kernel): rows = all
+    leading dimensions, -inf entries (the causal mask) give exact zeros; out may be x."""
+    out = torch.empty_like(x) if out is None else out
+    n = x.shape[-1] if x.dim() else 1
+    rows = x.numel() // n if n else 0
+    with torch.cuda.device(x.device):
+        check(lib.sdfl_local_softmax(_dev(x, "x"), _dev(out, "out"), rows, n, _dtype_code(x), _stream(stream)),
+              "sdfl_local_softmax")
     return out
 
 

@@ -31,9 +31,11 @@ _i64p = C.POINTER(C.c_int64)
 _sz = C.c_size_t
 
 
-def build(ref_root: str | None = "/root/reference") -> None:
-    """Compile the port, and the compiled reference when a reference checkout is present."""
+def build(ref_root: str | None = None) -> None:
+    """Compile the port, and the compiled reference when `ref_root` (default: the environment
+    variable SDFL_REFERENCE_ROOT) names a checkout of the reference project."""
     subprocess.run(["make", "-s", "-C", _HERE, "port"], check=True)
+    ref_root = ref_root or os.environ.get("SDFL_REFERENCE_ROOT")
     if ref_root and os.path.isdir(os.path.join(ref_root, "app/src/main/assets/kernel")):
         subprocess.run(["make", "-s", "-C", _HERE, "ref", f"REF={ref_root}"], check=True)
 
@@ -73,6 +75,7 @@ def port_lib():
         lib.oracle_chunkwise_add.argtypes = [_f32p, _f32p, _f32p, _sz, _sz]
         lib.oracle_permute3D__0_2_1.argtypes = [_f32p, _f32p, _sz, _sz, _sz]
         lib.oracle_softmax.argtypes = [_f32p, _f32p, _sz, _sz]
+        lib.oracle_local_softmax.argtypes = [_f32p, _f32p, _sz, _sz]
         lib.oracle_up_sample_nearest.argtypes = [_f32p, _f32p, _sz, _sz, _sz, _sz]
         lib.oracle_token_embedding.argtypes = [_i64p, _f32p, _f32p, _f32p, _sz, _sz, _sz, _sz]
         lib.oracle_token_embedding.restype = C.c_int
@@ -110,6 +113,7 @@ def ref_lib():
         lib.ref_chunkwise_add.argtypes = [_f32p, _f32p, _f32p, _sz, _sz]
         lib.ref_permute3D__0_2_1.argtypes = [_f32p, _f32p, _sz, _sz, _sz]
         lib.ref_softmax.argtypes = [_f32p, _f32p, _sz, _sz]
+        lib.ref_local_softmax.argtypes = [_f32p, _f32p, _sz, _sz]
         lib.ref_up_sample_nearest.argtypes = [_f32p, _f32p, _sz, _sz, _sz]
         _ref = lib
     return _ref
@@ -290,6 +294,18 @@ def softmax(x, backend: str = "port"):
     out = np.empty_like(x)
     fn = ref_lib().ref_softmax if backend == "ref" else port_lib().oracle_softmax
     fn(_fp(x), _fp(out), rows, chunk)
+    return out
+
+
+def local_softmax(x, backend: str = "port"):
+    """Row softmax the text encoder's way (multi_head_attention.cl local_softmax): one work-item per
+    element, halving reduction with a carry for odd row lengths; no maximum subtracted."""
+    x = _c32(x)
+    n = x.shape[-1]
+    rows = x.size // n if n else 0
+    out = np.empty_like(x)
+    fn = ref_lib().ref_local_softmax if backend == "ref" else port_lib().oracle_local_softmax
+    fn(_fp(x), _fp(out), rows, n)
     return out
 
 

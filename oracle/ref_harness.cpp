@@ -16,6 +16,7 @@
 //   app/src/main/cpp/modules/nn/ResBlock.cpp:136-142      silu launch
 //   app/src/main/cpp/modules/nn/ResidualAttentionBlock.cpp:146-153  gelu launch
 //   app/src/main/cpp/modules/TextEncoder.cpp:141-151      elemwise_add launch
+//   app/src/main/cpp/modules/nn/MultiHeadAttention.cpp:213-225  local_softmax launch
 
 #include "cl_shim.hpp"
 
@@ -48,6 +49,9 @@ namespace ref_util {
 }
 namespace ref_up {
 #include "up_sample.cl"
+}
+namespace ref_mha {
+#include "multi_head_attention.cl"
 }
 #pragma GCC diagnostic pop
 
@@ -305,6 +309,15 @@ void softmax_entry(void *p) {
     if (cache.size() < a->chunkSize) cache.resize(a->chunkSize);   // same for every fiber of the group
     ref_util::softmax(a->in, a->out, sums, cache.data(), a->chunkSize);
 }
+struct LocalSoftmaxArgs { const float *in; float *out; };
+// __local reductionSums[CONTEXT_LENGTH], as nn/MultiHeadAttention.cpp:215 sizes it (one float per work-item).
+void local_softmax_entry(void *p) {
+    static thread_local std::vector<float> sums;
+    auto *a = static_cast<LocalSoftmaxArgs *>(p);
+    const size_t local = get_local_size(0);
+    if (sums.size() < local) sums.resize(local);                   // same for every fiber of the group
+    ref_mha::local_softmax(a->in, a->out, sums.data());
+}
 void ln_mean_entry(void *p) {
     static thread_local float scratch[WORK_GROUP_SIZE];
     auto *a = static_cast<MeanArgs *>(p);
@@ -398,6 +411,13 @@ void ref_up_sample_nearest(const float *in, float *out, size_t channels, size_t 
 void ref_softmax(const float *in, float *out, size_t rows, size_t chunkSize) {
     SoftmaxArgs a{in, out, chunkSize};
     enqueue_1d_groups(rows * WORK_GROUP_SIZE, WORK_GROUP_SIZE, softmax_entry, &a);
+}
+
+// local_softmax as launched at nn/MultiHeadAttention.cpp:213-225: global size rows * row_len, one
+// work-group of row_len work-items per row (row_len = CONTEXT_LENGTH = 77 there, an odd size).
+void ref_local_softmax(const float *in, float *out, size_t rows, size_t row_len) {
+    LocalSoftmaxArgs a{in, out};
+    enqueue_1d_groups(rows * row_len, row_len, local_softmax_entry, &a);
 }
 
 // permute3D__0_2_1 as launched at nn/SpatialTransformer.cpp:131-134 / :154-157: global size {I, J, K}.

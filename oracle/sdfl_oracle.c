@@ -268,6 +268,34 @@ void oracle_softmax(const float *in, float *out, size_t rows, size_t chunk) {
     }
 }
 
+/* multi_head_attention.cl:28-54 local_softmax with one work-group of row_len work-items per row
+ * (nn/MultiHeadAttention.cpp:213-225, row_len = 77): item l holds exp(x[l]); the partial sums are
+ * folded by halving with a carry for odd sizes (offset = n/2; items below offset add the item
+ * `offset` above them, shifted by the remainder; the odd element in front joins the next round);
+ * every item then divides its own exponential by sums[0].  No maximum is subtracted. */
+void oracle_local_softmax(const float *in, float *out, size_t rows, size_t row_len) {
+#pragma omp parallel
+    {
+        float *sums = (float *)malloc(sizeof(float) * (row_len ? row_len : 1));
+        float *e = (float *)malloc(sizeof(float) * (row_len ? row_len : 1));
+#pragma omp for schedule(static)
+        for (long r = 0; r < (long)rows; ++r) {
+            const float *x = in + (size_t)r * row_len;
+            for (size_t l = 0; l < row_len; ++l) sums[l] = e[l] = expf(x[l]);
+            int remainder = (int)(row_len % 2);
+            for (int offset = (int)(row_len / 2); offset > 0; offset /= 2) {
+                for (int l = 0; l < offset; ++l) sums[l + remainder] += sums[l + offset + remainder];
+                offset += remainder;
+                remainder = offset % 2;
+            }
+            float *y = out + (size_t)r * row_len;
+            for (size_t l = 0; l < row_len; ++l) y[l] = e[l] / sums[0];
+        }
+        free(sums);
+        free(e);
+    }
+}
+
 /* util.cl:47-64 permute3D__0_2_1 with global size {I, J, K}: dst[i][k][j] = src[i][j][k]
  * (src_idx = i*J*K + j*K + k, dst_idx = i*K*J + k*J + j).  nn/SpatialTransformer.cpp:131-134
  * runs it with {1, C, HW} after the block's GroupNorm and :154-157 with {1, HW, C} before the

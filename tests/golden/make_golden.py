@@ -87,6 +87,14 @@ def main() -> None:
         x = (rng.standard_normal(shape) * 2.0).astype(np.float32)
         data[f"{name}.x"] = x
         data[f"{name}.y"] = oracle.softmax(x, backend="ref")
+    # the text encoder's attention softmax: 3 heads of 77 x 77 scores plus the causal mask (-inf above
+    # the diagonal), as local_softmax sees them (MultiHeadAttention.cpp:213-225), and an even row length
+    for name, shape in (("local_softmax_h3_77", (3, 77, 77)), ("local_softmax_r5_64", (5, 64))):
+        x = (rng.standard_normal(shape) * 2.0).astype(np.float32)
+        if x.ndim == 3:
+            x = x + np.triu(np.full(shape[1:], -np.inf, np.float32), 1)
+        data[f"{name}.x"] = x
+        data[f"{name}.y"] = oracle.local_softmax(x, backend="ref")
     np.savez_compressed(OUT, **data)
     print(f"wrote {OUT}: {len(data)} arrays, {os.path.getsize(OUT)} bytes")
 

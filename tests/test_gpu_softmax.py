@@ -50,3 +50,23 @@ def test_softmax_misaligned_and_errors(sdfl):
     want = oracle.softmax(x[1:].reshape(4, 64))
     assert_close(to_np(sdfl.ops.softmax(dx)), want, 1e-5, "misaligned softmax")
     assert sdfl.ops.softmax(torch.zeros((0, 77), device="cuda")).shape == (0, 77)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "float16"])
+def test_local_softmax_of_the_text_encoder(sdfl, dtype):
+    """sdfl_local_softmax against the reference's local_softmax kernel (multi_head_attention.cl:28-54) on
+    what the text encoder feeds it: [heads * 77, 77] scores with the causal mask, in place
+    (nn/MultiHeadAttention.cpp:213-225); sdfl_softmax on the same rows agrees."""
+    heads = 12
+    rng = rng_for(2, 77)
+    x = (rng.standard_normal((heads, 77, 77)) * 3.0).astype(np.float32).astype(dtype)
+    x = x + np.triu(np.full((77, 77), -np.inf, np.float32), 1).astype(dtype)
+    want = oracle.local_softmax(x.astype(np.float32))
+    buf = to_dev(x)
+    sdfl.ops.local_softmax(buf, out=buf)
+    got = to_np(buf)
+    assert_close(got, want, TOL[dtype], f"local_softmax {dtype}")
+    iu = np.triu_indices(77, 1)
+    assert np.all(got[:, iu[0], iu[1]] == 0)                       # masked scores: exact zeros
+    again = to_np(sdfl.ops.softmax(to_dev(x).view(heads * 77, 77)))
+    assert np.array_equal(again.reshape(got.shape), got)

@@ -61,3 +61,8 @@ def test_geglu_and_activations_match_reference_kernels(golden, oracle_mod):
     for name in ("softmax_r6_c77", "softmax_r3_c256"):
         assert_bit_equal(oracle_mod.softmax(golden[f"{name}.x"]), golden[f"{name}.y"], name)
         np.testing.assert_allclose(golden[f"{name}.y"].sum(-1), 1.0, rtol=1e-6)
+    for name in ("local_softmax_h3_77", "local_softmax_r5_64"):
+        assert_bit_equal(oracle_mod.local_softmax(golden[f"{name}.x"]), golden[f"{name}.y"], name)
+        np.testing.assert_allclose(golden[f"{name}.y"].sum(-1), 1.0, rtol=1e-6)
+    y = golden["local_softmax_h3_77.y"]
+    assert np.all(y[:, np.triu_indices(77, 1)[0], np.triu_indices(77, 1)[1]] == 0.0)   # the causal mask

@@ -154,6 +154,31 @@ def test_port_equals_compiled_reference_adjacent_kernels():
                          f"softmax {rows}x{chunk}")
 
 
+@needs_ref
+def test_port_equals_compiled_reference_local_softmax():
+    """multi_head_attention.cl local_softmax: rows of 77 (the odd work-group size of the text encoder)
+    with the causal mask, and a few other lengths for the carry logic of its reduction."""
+    rng = rng_for(2, 4244)
+    x = (rng.standard_normal((12, 77, 77)) * 3.0).astype(np.float32)
+    x += np.triu(np.full((77, 77), -np.inf, np.float32), 1)
+    assert_bit_equal(oracle.local_softmax(x, "port"), oracle.local_softmax(x, "ref"), "local_softmax 12x77x77 masked")
+    for n in (1, 2, 3, 5, 6, 7, 64, 100, 255):
+        x = (rng.standard_normal((9, n)) * 2.0).astype(np.float32)
+        assert_bit_equal(oracle.local_softmax(x, "port"), oracle.local_softmax(x, "ref"), f"local_softmax rows of {n}")
+
+
+def test_local_softmax_against_float64_and_softmax():
+    rng = rng_for(2, 4245)
+    x = (rng.standard_normal((8, 77, 77)) * 3.0).astype(np.float32)
+    x += np.triu(np.full((77, 77), -np.inf, np.float32), 1)
+    e = np.exp(x.astype(np.float64))
+    want = (e / e.sum(-1, keepdims=True)).astype(np.float32)
+    got = oracle.local_softmax(x)
+    assert_close(got, want, 1e-5, "local_softmax vs float64")
+    # the two reference softmax kernels compute the same function (different summation order)
+    assert_close(got, oracle.softmax(x.reshape(-1, 77)).reshape(x.shape), 1e-5, "local_softmax vs softmax")
+
+
 def test_softmax_against_float64():
     rng = rng_for(1, 4243)
     x = (rng.standard_normal((32, 77)) * 4.0).astype(np.float32)
