@@ -162,6 +162,9 @@ int sdfl_groupnorm_forward_multi_ex(const sdfl_gn_tensor *tensors, int count, in
  * up to 32 chunks per slab); larger problems return SDFL_ERR_WORKSPACE and touch nothing.
  * The first call on a device looks up the array's device address (once per device, with that
  * device current); make that first call before starting any stream capture on the device.
+ * The address is remembered per device ordinal for the life of the process: it belongs to the
+ * device's primary context, so do not call cudaDeviceReset between calls and do not use this
+ * entry point from another (driver-API) context on the same device.
  * All calls on a device share the one array and it keeps the previous call's values: nothing
  * in it needs clearing (each call overwrites every entry it later reads), but two calls whose
  * kernels can overlap on the GPU (different streams, no dependency) race on it -- order them.
@@ -336,6 +339,57 @@ int sdfl_quick_gelu(const void *src, void *dst, int64_t n, int dtype, void *stre
 
 /* K/util.cl:1-12  elemwise_add(A, B, C): C = A + B over n work-items. */
 int sdfl_elemwise_add(const void *A, const void *B, void *C, int64_t n, int dtype, void *stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Operator objects: the reference's classes as opaque C handles, for binders that cannot use the
+ * C++ wrapper of sdfl_operators.hpp (the reference side is JNI).
+ *   GroupNorm(ctx, queue, num_groups, num_channels, eps, weight_name, bias_name, kernel); init();
+ *   forward(in, out, n_wait, wait, event)                         NN/GroupNorm.h:15-29
+ *   LayerNorm(ctx, queue, dim, weight_name, bias_name, kernel)    NN/LayerNorm.h:16-28
+ *   GEGLU(ctx, queue, in_features, out_features, ...)             NN/GEGLU.h:18-36
+ * create = constructor + init(); *_op_forward = forward(); destroy = the destructor.  The OpenCL
+ * context / queue / kernel-holder arguments are gone and a stream replaces the event list.
+ * Ownership follows the reference: the caller owns input and output; gamma and beta are DEVICE
+ * arrays that the caller loads (the reference's .npy file names are app glue) and must keep alive
+ * as long as the handle; the handle owns its metadata and a scratch buffer that is allocated at
+ * create time for the stated maximum shape and never inside forward (the reference allocates and
+ * frees its mean / variance buffers in every forward call, NN/GroupNorm.cpp:95-103,164-165).
+ * A handle belongs to the device that was current at create time; forward with another device
+ * current, or with a shape beyond the stated maximum that needs more scratch than was reserved,
+ * returns SDFL_ERR_INVALID_VALUE / SDFL_ERR_WORKSPACE.  One handle may be used from one host thread
+ * at a time (calls on different streams would share its scratch).
+ * ---------------------------------------------------------------------------------------- */
+typedef struct sdfl_groupnorm sdfl_groupnorm;
+typedef struct sdfl_layernorm sdfl_layernorm;
+typedef struct sdfl_geglu sdfl_geglu;
+
+/* num_channels % num_groups != 0 -> SDFL_ERR_INVALID_VALUE (the reference throws at
+ * NN/GroupNorm.cpp:83-87).  max_batch / max_hw / max_dtype: the largest [batch, channels, hw] tensor
+ * of storage type max_dtype that forward will be given (sizes the scratch). */
+int sdfl_groupnorm_create(sdfl_groupnorm **op, int64_t num_groups, int64_t num_channels, float eps,
+                          const float *d_gamma, const float *d_beta, int fuse_silu, int64_t max_batch,
+                          int64_t max_hw, int max_dtype);
+/* in / out: [batch, num_channels, hw] device tensors; out may be in (NN/ResBlock.cpp:222). */
+int sdfl_groupnorm_op_forward(sdfl_groupnorm *op, const void *in, void *out, int64_t batch, int64_t hw,
+                              int dtype, void *stream);
+int sdfl_groupnorm_destroy(sdfl_groupnorm *op);
+
+int sdfl_layernorm_create(sdfl_layernorm **op, int64_t dim, float eps, const float *d_gamma,
+                          const float *d_beta);
+/* in / out: [rows, dim] device tensors; out may be in. */
+int sdfl_layernorm_op_forward(sdfl_layernorm *op, const void *in, void *out, int64_t rows, int dtype,
+                              void *stream);
+int sdfl_layernorm_destroy(sdfl_layernorm *op);
+
+/* The gelu_multiply stage of GEGLU::forward (NN/GEGLU.cpp:71-77); the Linear in front of it
+ * (NN/GEGLU.cpp:32-34) is a dense layer and stays with the caller.  weight_shape receives the
+ * reference's public weightShape member {2 * out_features, in_features} (NN/GEGLU.h:36). */
+int sdfl_geglu_create(sdfl_geglu **op, int64_t in_features, int64_t out_features);
+int sdfl_geglu_weight_shape(const sdfl_geglu *op, int64_t weight_shape[2]);
+/* projected: [rows, 2 * out_features]; out: [rows, out_features]. */
+int sdfl_geglu_op_forward(sdfl_geglu *op, const void *projected, void *out, int64_t rows, int dtype,
+                          void *stream);
+int sdfl_geglu_destroy(sdfl_geglu *op);
 
 /* ------------------------------------------------------------------------------------------
  * Device status and host-buffer convenience path

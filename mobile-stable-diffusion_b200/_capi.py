@@ -87,6 +87,16 @@ SIGNATURES = {
     "sdfl_silu": (_i, [_p, _p, _i64, _i, _p]),
     "sdfl_quick_gelu": (_i, [_p, _p, _i64, _i, _p]),
     "sdfl_elemwise_add": (_i, [_p, _p, _p, _i64, _i, _p]),
+    "sdfl_groupnorm_create": (_i, [C.POINTER(_p), _i64, _i64, _f, _p, _p, _i, _i64, _i64, _i]),
+    "sdfl_groupnorm_op_forward": (_i, [_p, _p, _p, _i64, _i64, _i, _p]),
+    "sdfl_groupnorm_destroy": (_i, [_p]),
+    "sdfl_layernorm_create": (_i, [C.POINTER(_p), _i64, _f, _p, _p]),
+    "sdfl_layernorm_op_forward": (_i, [_p, _p, _p, _i64, _i, _p]),
+    "sdfl_layernorm_destroy": (_i, [_p]),
+    "sdfl_geglu_create": (_i, [C.POINTER(_p), _i64, _i64]),
+    "sdfl_geglu_weight_shape": (_i, [_p, C.POINTER(_i64)]),
+    "sdfl_geglu_op_forward": (_i, [_p, _p, _p, _i64, _i, _p]),
+    "sdfl_geglu_destroy": (_i, [_p]),
     "sdfl_device_status": (_i, [C.POINTER(C.c_uint), _i, _p]),
     "sdfl_selftest_bounded_wait": (_i, [C.c_longlong, _p]),
     "sdfl_host_pipeline_create": (_i, [C.POINTER(_p), _sz, _i]),

@@ -79,22 +79,5 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
-def build_cpp_test() -> str:
-    """Compile tests/cpp/test_operators.cpp (the C++ operator classes against the CPU oracle)."""
-    src = os.path.join(ROOT, "tests", "cpp", "test_operators.cpp")
-    exe = os.path.join(ROOT, "tests", "cpp", "test_operators")
-    oracle_dir = os.path.join(ROOT, "oracle")
-    deps = [src, os.path.join(CSRC, "operators.hpp"), os.path.join(ROOT, "include", "sdfl.h")]
-    if _stale(exe, deps):
-        cmd = [_nvcc(), "-O2", "-std=c++17", src, "-o", exe, "-L" + LIBDIR, "-lsdfl",
-               "-L" + oracle_dir, "-lsdfl_oracle",
-               "-Xlinker", "-rpath,$ORIGIN/../../" + os.path.basename(PKG) + "/lib",
-               "-Xlinker", "-rpath,$ORIGIN/../../oracle"]
-        r = subprocess.run(cmd, capture_output=True, text=True)
-        if r.returncode != 0:
-            raise RuntimeError(f"C++ test build failed:\n{r.stdout}\n{r.stderr}")
-    return exe
-
-
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))

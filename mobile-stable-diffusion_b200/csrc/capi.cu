@@ -5,6 +5,7 @@
 #include "common.cuh"
 #include "kernels.h"
 
+#include <new>
 #include <vector>
 
 namespace sdfl {
@@ -65,7 +66,7 @@ int gn_forward(const void *in, void *out, const float *gamma, const float *beta,
     if (batch == 0 || hw == 0) return SDFL_OK;
     if (path < SDFL_GN_AUTO || path > SDFL_GN_REGISTER || cluster < 0) return SDFL_ERR_INVALID_VALUE;
     sdfl::GnShape s{batch, channels, hw, groups, dtype, eps,
-                    fuse_silu ? sdfl::kActSilu : sdfl::kActNone};
+                    fuse_silu ? sdfl::kActSilu : sdfl::kActNone, bias != nullptr};
     sdfl::GnPlan plan;
     cudaError_t e = sdfl::gn_make_plan(s, in, out, path, cluster, &plan);
     if (e == cudaErrorInvalidConfiguration || e == cudaErrorInvalidValue) return SDFL_ERR_UNSUPPORTED;
@@ -84,6 +85,27 @@ int unary(int act, const void *src, void *dst, int64_t n, int dtype, void *strea
 }
 
 }  // namespace
+
+struct sdfl_groupnorm {
+    int64_t num_groups, num_channels;
+    float eps;
+    const float *gamma, *beta;
+    int fuse_silu;
+    void *ws;
+    size_t ws_bytes;
+    int device;
+};
+
+struct sdfl_layernorm {
+    int64_t dim;
+    float eps;
+    const float *gamma, *beta;
+    int device;
+};
+
+struct sdfl_geglu {
+    int64_t in_features, out_features;
+};
 
 struct sdfl_host_pipeline {
     struct Slot {
@@ -527,6 +549,112 @@ int sdfl_device_status(unsigned int *value, int clear, void *stream) {
 
 int sdfl_selftest_bounded_wait(long long limit_cycles, void *stream) {
     return wrap(sdfl::gn_wait_selftest(limit_cycles, as_stream(stream)));
+}
+
+// ---- operator handles (NN/GroupNorm.h:15-29, NN/LayerNorm.h:16-28, NN/GEGLU.h:18-36) ------------------
+
+int sdfl_groupnorm_create(sdfl_groupnorm **op, int64_t num_groups, int64_t num_channels, float eps,
+                          const float *d_gamma, const float *d_beta, int fuse_silu, int64_t max_batch,
+                          int64_t max_hw, int max_dtype) {
+    if (!op) return SDFL_ERR_INVALID_POINTER;
+    *op = nullptr;
+    if (num_groups <= 0 || num_channels <= 0 || num_channels % num_groups != 0 || !(eps >= 0.f) ||
+        max_batch < 0 || max_hw < 0 || !dtype_ok(max_dtype))
+        return SDFL_ERR_INVALID_VALUE;
+    if (!d_gamma || !d_beta) return SDFL_ERR_INVALID_POINTER;
+    sdfl_groupnorm *p = new (std::nothrow) sdfl_groupnorm{num_groups, num_channels, eps, d_gamma, d_beta,
+                                                          fuse_silu ? 1 : 0, nullptr, 0, 0};
+    if (!p) return cuda_fail(cudaErrorMemoryAllocation);
+    cudaError_t e = cudaGetDevice(&p->device);
+    // scratch of the any-shape path for the largest tensor, in either storage type.  A smaller tensor
+    // is cut into more chunks per slab, but never into more than about 600 chunks beyond its slabs.
+    size_t need = static_cast<size_t>(600 + max_batch * num_groups) * 2 * sizeof(float);
+    if (need < 64 * 1024) need = 64 * 1024;
+    for (int dt = 0; dt <= max_dtype; ++dt) {
+        const size_t n = sdfl_groupnorm_workspace_bytes_ex(max_batch, num_channels, max_hw, num_groups, dt,
+                                                           SDFL_GN_SPLIT, 0);
+        if (n > need) need = n;
+    }
+    if (e == cudaSuccess) e = cudaMalloc(&p->ws, need);
+    if (e != cudaSuccess) { delete p; return cuda_fail(e); }
+    p->ws_bytes = need;
+    *op = p;
+    return SDFL_OK;
+}
+
+int sdfl_groupnorm_op_forward(sdfl_groupnorm *op, const void *in, void *out, int64_t batch, int64_t hw,
+                              int dtype, void *stream) {
+    if (!op) return SDFL_ERR_INVALID_POINTER;
+    int current = -1;
+    cudaError_t e = cudaGetDevice(&current);
+    if (e != cudaSuccess) return cuda_fail(e);
+    if (current != op->device) return SDFL_ERR_INVALID_VALUE;
+    return gn_forward(in, out, op->gamma, op->beta, batch, op->num_channels, hw, op->num_groups, op->eps,
+                      op->fuse_silu, dtype, op->ws, op->ws_bytes, SDFL_GN_AUTO, 0, as_stream(stream));
+}
+
+int sdfl_groupnorm_destroy(sdfl_groupnorm *op) {
+    if (!op) return SDFL_OK;
+    cudaError_t e = op->ws ? cudaFree(op->ws) : cudaSuccess;
+    delete op;
+    return wrap(e);
+}
+
+int sdfl_layernorm_create(sdfl_layernorm **op, int64_t dim, float eps, const float *d_gamma,
+                          const float *d_beta) {
+    if (!op) return SDFL_ERR_INVALID_POINTER;
+    *op = nullptr;
+    if (dim <= 0 || !(eps >= 0.f)) return SDFL_ERR_INVALID_VALUE;
+    if (!d_gamma || !d_beta) return SDFL_ERR_INVALID_POINTER;
+    sdfl_layernorm *p = new (std::nothrow) sdfl_layernorm{dim, eps, d_gamma, d_beta, 0};
+    if (!p) return cuda_fail(cudaErrorMemoryAllocation);
+    cudaError_t e = cudaGetDevice(&p->device);
+    if (e != cudaSuccess) { delete p; return cuda_fail(e); }
+    *op = p;
+    return SDFL_OK;
+}
+
+int sdfl_layernorm_op_forward(sdfl_layernorm *op, const void *in, void *out, int64_t rows, int dtype,
+                              void *stream) {
+    if (!op) return SDFL_ERR_INVALID_POINTER;
+    int current = -1;
+    cudaError_t e = cudaGetDevice(&current);
+    if (e != cudaSuccess) return cuda_fail(e);
+    if (current != op->device) return SDFL_ERR_INVALID_VALUE;
+    return sdfl_layernorm_forward(in, out, op->gamma, op->beta, rows, op->dim, op->eps, dtype, stream);
+}
+
+int sdfl_layernorm_destroy(sdfl_layernorm *op) {
+    delete op;
+    return SDFL_OK;
+}
+
+int sdfl_geglu_create(sdfl_geglu **op, int64_t in_features, int64_t out_features) {
+    if (!op) return SDFL_ERR_INVALID_POINTER;
+    *op = nullptr;
+    if (in_features <= 0 || out_features <= 0) return SDFL_ERR_INVALID_VALUE;
+    sdfl_geglu *p = new (std::nothrow) sdfl_geglu{in_features, out_features};
+    if (!p) return cuda_fail(cudaErrorMemoryAllocation);
+    *op = p;
+    return SDFL_OK;
+}
+
+int sdfl_geglu_weight_shape(const sdfl_geglu *op, int64_t weight_shape[2]) {
+    if (!op || !weight_shape) return SDFL_ERR_INVALID_POINTER;
+    weight_shape[0] = 2 * op->out_features;          // NN/GEGLU.cpp:36
+    weight_shape[1] = op->in_features;
+    return SDFL_OK;
+}
+
+int sdfl_geglu_op_forward(sdfl_geglu *op, const void *projected, void *out, int64_t rows, int dtype,
+                          void *stream) {
+    if (!op) return SDFL_ERR_INVALID_POINTER;
+    return sdfl_gelu_multiply(projected, out, rows, op->out_features, dtype, stream);
+}
+
+int sdfl_geglu_destroy(sdfl_geglu *op) {
+    delete op;
+    return SDFL_OK;
 }
 
 // ---- host-buffer pipeline ---------------------------------------------------------------------

@@ -12,6 +12,27 @@ constexpr int kF16 = 1;
 
 enum Act : int { kActNone = 0, kActSilu = 1, kActGelu = 2, kActQuickGelu = 3 };
 
+// Number of SMs of the current device, asked of the driver once per device (grids are sized in
+// multiples of it).  Without a usable device -- planning calls made on a machine that has none --
+// the answer is the B200's 148.
+inline int sm_count() {
+    static int cached[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+        (void)cudaGetLastError();
+        return 148;
+    }
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) {
+            (void)cudaGetLastError();
+            n = 148;
+        }
+        cached[dev] = n;        // racing threads write the same value
+    }
+    return cached[dev];
+}
+
 // ---------------------------------------------------------------------------------------------
 // 16-byte vectors of T <-> float lanes
 // ---------------------------------------------------------------------------------------------

@@ -15,7 +15,7 @@ inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 
 
 inline unsigned ew_grid(int64_t work_items) {
     int64_t blocks = (work_items + kEwThreads - 1) / kEwThreads;
-    const int64_t cap = 148 * 8 * 4;
+    const int64_t cap = sm_count() * 8 * 4;
     if (blocks > cap) blocks = cap;
     if (blocks < 1) blocks = 1;
     return static_cast<unsigned>(blocks);

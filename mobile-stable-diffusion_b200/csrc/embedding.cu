@@ -81,7 +81,7 @@ cudaError_t token_embedding_launch(const int64_t *ids, const void *table, const 
                                    int dtype, int *d_status, cudaStream_t stream) {
     const int64_t tokens = batch * t;
     if (tokens == 0 || d == 0) return cudaSuccess;
-    const unsigned grid = static_cast<unsigned>(tokens < 148 * 16 ? tokens : 148 * 16);
+    const unsigned grid = static_cast<unsigned>(tokens < sm_count() * 16 ? tokens : sm_count() * 16);
     const int64_t esz = dtype == kF16 ? 2 : 4;
     const bool vec_ok = (d * esz) % 16 == 0 && (reinterpret_cast<uintptr_t>(table) & 15u) == 0 &&
                         (reinterpret_cast<uintptr_t>(pos) & 15u) == 0 &&

@@ -18,8 +18,8 @@ inline int gn_ring_unroll(int threads, int chunk_vecs) {
     return chunk_vecs == 2048 ? 8 : chunk_vecs == 1024 ? 4 : 0;
 }
 // How many clusters of this size, block size and shared-memory footprint can be resident at once.
-cudaError_t gn_ring_active_clusters(int dtype, int cluster, int threads, size_t smem, int chunk_vecs,
-                                    int *active);
+cudaError_t gn_ring_active_clusters(int dtype, int act, bool bias, int cluster, int threads, size_t smem,
+                                    int chunk_vecs, int *active);
 cudaError_t gn_ring_launch(const GnShape &s, const GnPlan &plan, const void *in, void *out, const float *w,
                            const float *b, cudaStream_t stream, const void *bias, const void *in2, int64_t c1);
 

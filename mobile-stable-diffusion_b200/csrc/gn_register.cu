@@ -219,7 +219,7 @@ cudaError_t launch_register_nhwc(const RegArgs &a, unsigned grid, size_t smem, c
 template <typename T, int ACT, bool BIAS>
 cudaError_t launch_register_as(const RegArgs &a, bool nhwc, cudaStream_t stream) {
     const uint32_t per_thread = (a.slab_vecs + kRegThreads - 1) / kRegThreads;
-    const unsigned grid = a.units < 148u * 64u ? a.units : 148u * 64u;
+    const unsigned grid = a.units < static_cast<unsigned>(sm_count()) * 64u ? a.units : static_cast<unsigned>(sm_count()) * 64u;
     cudaError_t err;
     if (nhwc) {
         if (BIAS) return cudaErrorInvalidValue;

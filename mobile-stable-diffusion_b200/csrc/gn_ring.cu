@@ -327,8 +327,7 @@ gn_resident_kernel(const ResidentArgs a) {
             }
         }
         // Scale and shift of the first chunk of the normalise pass: fetched now, so that their L2
-        // round trip runs beside the exchange instead of behind it (1-2 % on every shape; fetching
-        // every chunk's pair one chunk ahead as well was 1-4 % slower than this, same GPU, same session).
+        // round trip runs beside the exchange instead of behind it.
         const uint32_t ch0 = (unit % a.groups) * a.cpg;
         const uint32_t c_first = a.vec_uniform ? a.hwv_div.div(v0 + (P - H) % P * cv) : 0u;
         const float w_first = __ldg(a.w + ch0 + c_first), b_first = __ldg(a.b + ch0 + c_first);
@@ -485,27 +484,39 @@ cudaError_t launch_resident(const ResidentArgs &a, const GnPlan &plan, cudaStrea
 }
 
 // How many clusters of this size, block size and shared-memory footprint can be resident at
-// once (a cluster must fit inside one GPC).  Asked of the driver once per (device, dtype,
-// cluster, threads, shared-memory size in KiB) and remembered.
-template <typename T, int NV>
-cudaError_t active_clusters_nv(cudaLaunchConfig_t *cfg, int *n) {
-    cudaError_t err = ensure_resident_attrs<T, kActSilu, false, NV>();
+// once (a cluster must fit inside one GPC).  Asked of the driver once per (device, kernel
+// instance, cluster, threads, shared-memory size in KiB) and remembered; the instance asked about
+// is the one that will be launched (activation and addend change its register count).
+template <typename T, int ACT, bool BIAS, int NV>
+cudaError_t active_clusters_of(cudaLaunchConfig_t *cfg, int *n) {
+    cudaError_t err = ensure_resident_attrs<T, ACT, BIAS, NV>();
     if (err != cudaSuccess) return err;
-    return cudaOccupancyMaxActiveClusters(n, gn_resident_kernel<T, kActSilu, false, NV>, cfg);
+    return cudaOccupancyMaxActiveClusters(n, gn_resident_kernel<T, ACT, BIAS, NV>, cfg);
+}
+
+template <typename T, int ACT, bool BIAS>
+cudaError_t active_clusters_nv(int nv, cudaLaunchConfig_t *cfg, int *n) {
+    switch (nv) {
+        case 8: return active_clusters_of<T, ACT, BIAS, 8>(cfg, n);
+        case 4: return active_clusters_of<T, ACT, BIAS, 4>(cfg, n);
+        default: return active_clusters_of<T, ACT, BIAS, 0>(cfg, n);
+    }
 }
 
 template <typename T>
-cudaError_t resident_active_clusters(int cluster, int threads, size_t smem, int chunk_vecs, int *active) {
+cudaError_t resident_active_clusters(int act, bool bias, int cluster, int threads, size_t smem, int chunk_vecs,
+                                     int *active) {
     static std::mutex mu;
     static std::map<uint64_t, int> cache;
     int dev = 0;
     cudaError_t err = cudaGetDevice(&dev);
     if (err != cudaSuccess) return err;
     const uint64_t kb = (smem + 1023) / 1024;
+    const int nv = plan_unroll(threads, chunk_vecs);
     const uint64_t key = (static_cast<uint64_t>(dev) << 48) | (static_cast<uint64_t>(sizeof(T)) << 40) |
                          (static_cast<uint64_t>(cluster) << 32) |
-                         (static_cast<uint64_t>(threads) << 16) | kb |
-                         (static_cast<uint64_t>(plan_unroll(threads, chunk_vecs)) << 56);
+                         (static_cast<uint64_t>(threads) << 16) | kb | (static_cast<uint64_t>(nv) << 56) |
+                         (static_cast<uint64_t>(act == kActSilu) << 60) | (static_cast<uint64_t>(bias) << 61);
     {
         std::lock_guard<std::mutex> lock(mu);
         auto it = cache.find(key);
@@ -515,11 +526,10 @@ cudaError_t resident_active_clusters(int cluster, int threads, size_t smem, int 
     cudaLaunchAttribute attr[1];
     cluster_config(&cfg, attr, static_cast<unsigned>(cluster), cluster, threads, smem, nullptr);
     int n = 0;
-    switch (plan_unroll(threads, chunk_vecs)) {
-        case 8: err = active_clusters_nv<T, 8>(&cfg, &n); break;
-        case 4: err = active_clusters_nv<T, 4>(&cfg, &n); break;
-        default: err = active_clusters_nv<T, 0>(&cfg, &n); break;
-    }
+    if (act == kActSilu)
+        err = bias ? active_clusters_nv<T, kActSilu, true>(nv, &cfg, &n) : active_clusters_nv<T, kActSilu, false>(nv, &cfg, &n);
+    else
+        err = bias ? active_clusters_nv<T, kActNone, true>(nv, &cfg, &n) : active_clusters_nv<T, kActNone, false>(nv, &cfg, &n);
     if (err != cudaSuccess) return err;
     *active = n;
     std::lock_guard<std::mutex> lock(mu);
@@ -529,10 +539,10 @@ cudaError_t resident_active_clusters(int cluster, int threads, size_t smem, int 
 
 }  // namespace
 
-cudaError_t gn_ring_active_clusters(int dtype, int cluster, int threads, size_t smem, int chunk_vecs,
-                                    int *active) {
-    return dtype == kF16 ? resident_active_clusters<__half>(cluster, threads, smem, chunk_vecs, active)
-                         : resident_active_clusters<float>(cluster, threads, smem, chunk_vecs, active);
+cudaError_t gn_ring_active_clusters(int dtype, int act, bool bias, int cluster, int threads, size_t smem,
+                                    int chunk_vecs, int *active) {
+    return dtype == kF16 ? resident_active_clusters<__half>(act, bias, cluster, threads, smem, chunk_vecs, active)
+                         : resident_active_clusters<float>(act, bias, cluster, threads, smem, chunk_vecs, active);
 }
 
 cudaError_t gn_ring_launch(const GnShape &s, const GnPlan &plan, const void *in, void *out, const float *w,

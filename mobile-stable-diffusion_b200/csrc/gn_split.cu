@@ -455,7 +455,7 @@ cudaError_t launch_nhwc_h8(const SplitArgs &a, const GnShape &s, cudaStream_t st
     constexpr size_t smem = 2 * TJ * (TK * 2 + 16) + TJ * sizeof(float2);
     const unsigned tiles_c = static_cast<unsigned>((s.channels + TJ - 1) / TJ), tiles_p = static_cast<unsigned>((s.hw + TK - 1) / TK);
     const unsigned long long total = static_cast<unsigned long long>(s.batch) * tiles_c * tiles_p;
-    const unsigned long long ctas = 148ull * 6;
+    const unsigned long long ctas = static_cast<unsigned long long>(sm_count()) * 6;
     const unsigned grid = static_cast<unsigned>(total < ctas ? total : ctas);
     gn_apply_nhwc_h8_kernel<ACT, TJ, TK><<<grid, dim3(32, 8), smem, stream>>>(a, static_cast<uint32_t>(s.hw), tiles_c, tiles_p, total);
     return cudaGetLastError();
@@ -665,7 +665,7 @@ cudaError_t gn_split_launch(const GnShape &s, const GnPlan &plan, const void *in
         const unsigned tiles_c = static_cast<unsigned>((s.channels + 63) / 64), tiles_p = static_cast<unsigned>((s.hw + 63) / 64);
         const unsigned long long total = static_cast<unsigned long long>(s.batch) * tiles_c * tiles_p;
         const size_t asmem = 2 * esz * 64 * (64 + (esz == 2 ? 2 : 1)) + 64 * sizeof(float4);
-        const unsigned agrid = static_cast<unsigned>(total < 148ull * 6 ? total : 148ull * 6);
+        const unsigned agrid = static_cast<unsigned>(total < static_cast<unsigned long long>(sm_count()) * 6 ? total : static_cast<unsigned long long>(sm_count()) * 6);
 #define SDFL_NHWC_APPLY(T, ACT)                                                              \
         do {                                                                                 \
             if (pairs) gn_apply_nhwc_async_kernel<T, ACT><<<agrid, tblock, asmem, stream>>>(a, hw32, tiles_c, tiles_p, total); \
@@ -764,7 +764,7 @@ cudaError_t stats_launch(const void *in, const float *mean, float *out, int64_t 
     if (gn_aligned16(in) && n % VEC == 0 && n >= VEC) {
         // cluster size: up to eight CTAs of 256 threads per SM, at least 8 vectors per thread
         int S = 1;
-        while (S < 8 && groups * S * 2 <= 8 * 148 && n / VEC / (S * 2) >= 8 * kStatsThreads) S *= 2;
+        while (S < 8 && groups * S * 2 <= 8 * sm_count() && n / VEC / (S * 2) >= 8 * kStatsThreads) S *= 2;
         cudaLaunchConfig_t cfg;
         cudaLaunchAttribute attr[1];
         cluster_config(&cfg, attr, static_cast<unsigned>(groups * S), S, kStatsThreads, 0, stream);
@@ -796,7 +796,7 @@ cudaError_t stats_var_launch(const void *in, const float *mean, float *out, int6
 
 static unsigned flat_grid(int64_t n, int threads) {
     int64_t blocks = (n + threads - 1) / threads;
-    const int64_t cap = 148 * 16;
+    const int64_t cap = sm_count() * 16;
     if (blocks > cap) blocks = cap;
     if (blocks < 1) blocks = 1;
     return static_cast<unsigned>(blocks);

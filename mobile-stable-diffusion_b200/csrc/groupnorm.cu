@@ -107,16 +107,16 @@ cudaError_t gn_make_plan(const GnShape &s, const void *in, const void *out, int 
         plan->path = kGnRegister;
         plan->cluster = 1;
         plan->threads = kRegThreads;
-        plan->nclusters = static_cast<int>(units < 148 * 64 ? units : 148 * 64);
+        plan->nclusters = static_cast<int>(units < sm_count() * 64 ? units : sm_count() * 64);
         plan->chunk_vecs = static_cast<int>((slab_bytes / 16 + kRegThreads - 1) / kRegThreads);
         return cudaSuccess;
     }
 
     if (resident_ok) {
-        // Ring geometry and cluster size, from sweeps on B200 (fp16 and fp32 behave alike per
-        // byte).  A small ring (3 slots of 16-32 KB, 8 consumer warps) with the second read
-        // served by L2 beats full shared-memory residency at every size tried: it keeps 2-4 CTAs
-        // on each SM, so one CTA's cluster exchange hides behind the others' traffic.  The
+        // Ring geometry and cluster size (fp16 and fp32 behave alike per byte).  A small ring
+        // (3 slots of 16-32 KB, 8 consumer warps) with the second read served by L2 rather than
+        // full shared-memory residency: it keeps 2-4 CTAs on each SM, so one CTA's cluster
+        // exchange hides behind the others' traffic.  The
         // cluster grows with the slab so that a CTA's share is about 256 KB: the slabs in flight
         // (256 CTAs x share = 64 MB) stay well inside L2; with few slabs it grows further so that
         // every SM still gets a CTA.
@@ -136,8 +136,8 @@ cudaError_t gn_make_plan(const GnShape &s, const void *in, const void *out, int 
             const int64_t part_vecs = (slab_vecs + c - 1) / c;
             const int64_t part_bytes = part_vecs * 16;
             // One slab per cluster at most (a single wave, e.g. one image per GPU): the launch is
-            // a fill / exchange / drain latency chain, where fewer, larger chunks and more
-            // consumer warps won in the sweeps, and shares up to 96 KB stay resident.
+            // a fill / exchange / drain latency chain: fewer, larger chunks, and shares up to
+            // 96 KB stay resident.
             const bool single_wave = units * c <= 2 * 128 && part_bytes >= 64 * 1024;
             const bool large = part_bytes >= 256 * 1024 || single_wave;
             int64_t chunk_vecs = k_chunk_kb > 0 ? k_chunk_kb * 64 : (large ? 2048 : 1024);
@@ -158,7 +158,7 @@ cudaError_t gn_make_plan(const GnShape &s, const void *in, const void *out, int 
             if (consumers > 480) consumers = 480;
             const int threads = consumers + 32;
             int active = 0;
-            cudaError_t err = gn_ring_active_clusters(s.dtype, c, threads, smem, static_cast<int>(chunk_vecs), &active);
+            cudaError_t err = gn_ring_active_clusters(s.dtype, s.act, s.bias != 0, c, threads, smem, static_cast<int>(chunk_vecs), &active);
             if (err != cudaSuccess) { (void)cudaGetLastError(); active = 0; }
             if (active <= 0) { if (k_cluster > 0) break; continue; }
             const int64_t waves = (units + active - 1) / active;
@@ -184,7 +184,7 @@ cudaError_t gn_make_plan(const GnShape &s, const void *in, const void *out, int 
     plan->smem = 0;
     plan->threads = kSplitThreads;
     // enough chunks for ~4 CTAs per SM across all slabs, at least 16K elements per chunk.
-    int64_t splits = (148 * 4 + units - 1) / units;
+    int64_t splits = (sm_count() * 4 + units - 1) / units;
     const int64_t max_splits = (slab_elems + 16383) / 16384;
     if (splits > max_splits) splits = max_splits;
     if (splits < 1) splits = 1;

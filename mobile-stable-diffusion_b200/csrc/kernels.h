@@ -41,6 +41,7 @@ struct GnShape {
     int dtype;         // kF32 / kF16
     float eps;
     int act;           // kActNone / kActSilu
+    int bias;          // a per-(image, channel) addend will be passed to gn_launch
 };
 
 // Decide the path.  `force_path` / `force_cluster` (0 = automatic) are for tests and sweeps.

@@ -115,10 +115,9 @@ constexpr int ln_min_blocks_r(int maxv, int rows_per_warp) {
 // reference's two steps (elemwise_add, then layer_norm on what was stored).
 // Scale and shift are fp32 (2 x 4 bytes per element against 2 bytes of fp16 data): read through
 // L1 for every row they saturate the L1 data path, so each CTA first copies them to shared
-// memory (dynamic, 2 * dim floats) and every row reads them from there.  (Tried: the copy as a
-// cp.async waited for, with a CTA barrier, only in front of each warp's first normalise step, so
-// that the first rows load beside it.  With the weights in L2 it was 1-6 % slower, same GPU, same
-// session: the barrier then sits behind the row loads and every warp waits for the slowest.)
+// memory (dynamic, 2 * dim floats) and every row reads them from there.  The copy is plain loads
+// and stores followed by one CTA barrier before the first row: a barrier placed behind the first
+// rows' loads instead makes every warp wait for the slowest.
 template <typename T, int MAXV, bool ADD, int R>
 __global__ void __launch_bounds__(kLnThreads, ln_min_blocks_r(MAXV, R))
 ln_warp_kernel(const T *in, const T *in2, T *sum_out, T *out, const float *__restrict__ gw,
@@ -220,10 +219,10 @@ void launch_warp(const void *in, const void *in2, void *sum_out, void *out, cons
                  const float *b, int64_t rows, int nvec, int dim, float eps, cudaStream_t stream) {
     // persistent grid: as many CTAs as fit the SMs at once, so the staged scale / shift are
     // reused for many rows.  Two rows per warp when the pairs still give every SM its warps.
-    const bool two = in2 == nullptr && MAXV <= 6 && rows >= 148 * kLnWarps * 4;
+    const bool two = in2 == nullptr && MAXV <= 6 && rows >= sm_count() * kLnWarps * 4;
     const int64_t rows_per_cta = kLnWarps * (two ? 2 : 1);
     int64_t blocks = (rows + rows_per_cta - 1) / rows_per_cta;
-    const int64_t cap = 148 * ln_min_blocks_r(MAXV, two ? 2 : 1);
+    const int64_t cap = sm_count() * ln_min_blocks_r(MAXV, two ? 2 : 1);
     if (blocks > cap) blocks = cap;
     const size_t smem = 2 * static_cast<size_t>(dim) * sizeof(float);
     const unsigned grid = static_cast<unsigned>(blocks);
@@ -272,7 +271,7 @@ cudaError_t ln_dispatch(const void *in, void *out, const float *w, const float *
                         int64_t dim, float eps, cudaStream_t stream) {
     cudaError_t err = ln_warp_dispatch<T>(in, nullptr, nullptr, out, w, b, rows, dim, eps, stream);
     if (err != cudaErrorNotSupported) return err;
-    int64_t blocks = rows < 148 * 8 ? rows : 148 * 8;
+    int64_t blocks = rows < sm_count() * 8 ? rows : sm_count() * 8;
     ln_block_kernel<T><<<static_cast<unsigned>(blocks), kLnThreads, 0, stream>>>(
         static_cast<const T *>(in), static_cast<T *>(out), w, b, rows, dim, eps);
     err = cudaGetLastError();

@@ -310,15 +310,22 @@ transpose_scalar_kernel(const T *__restrict__ src, const T *res, T *dst, long lo
 template <bool ADD, int TJ, int TK>
 cudaError_t launch_h8(const __half *s, const __half *r, __half *d, int64_t I, int64_t J, int64_t K, cudaStream_t stream) {
     constexpr size_t smem = 2 * (TJ * (TK * 2 + 16) + (ADD ? TK * (TJ * 2 + 16) : 0));
-    if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(transpose_h8_kernel<ADD, TJ, TK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             static_cast<int>(smem));
+    if (smem > 48 * 1024) {      // once per device and instantiation, not per launch
+        static std::atomic<bool> done[64];
+        int dev = 0;
+        cudaError_t e = cudaGetDevice(&dev);
         if (e != cudaSuccess) return e;
+        if (!(dev >= 0 && dev < 64 && done[dev].load(std::memory_order_acquire))) {
+            e = cudaFuncSetAttribute(transpose_h8_kernel<ADD, TJ, TK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     static_cast<int>(smem));
+            if (e != cudaSuccess) return e;
+            if (dev >= 0 && dev < 64) done[dev].store(true, std::memory_order_release);
+        }
     }
     const unsigned tiles_j = static_cast<unsigned>((J + TJ - 1) / TJ), tiles_k = static_cast<unsigned>((K + TK - 1) / TK);
     const unsigned long long total = static_cast<unsigned long long>(I) * tiles_j * tiles_k;
     const unsigned long long per_sm = 220 * 1024 / (smem + 1024) < 6 ? 220 * 1024 / (smem + 1024) : 6;
-    const unsigned long long ctas = 148ull * per_sm;
+    const unsigned long long ctas = static_cast<unsigned long long>(sm_count()) * per_sm;
     const unsigned grid = static_cast<unsigned>(total < ctas ? total : ctas);
     transpose_h8_kernel<ADD, TJ, TK><<<grid, dim3(32, 8), smem, stream>>>(s, r, d, static_cast<int>(J), static_cast<int>(K),
                                                                          tiles_j, tiles_k, total);
@@ -350,7 +357,7 @@ cudaError_t transpose_dispatch(const void *src, const void *res, void *dst, int6
             // (128 x 128 tiles: 71 % and 40 %).
             // Small tensors keep 64 x 64 tiles: with fewer tiles than two rounds of the persistent
             // grid the larger tiles leave SMs idle ([2,320,4096]: 5.5 against 5.0 us).
-            const bool enough = I * ((J + 63) / 64) * ((K + 63) / 64) >= 4 * 148 * 6;
+            const bool enough = I * ((J + 63) / 64) * ((K + 63) / 64) >= 4 * sm_count() * 6;
             const bool k_wide = enough && K % 128 == 0 && (J % 128 != 0 || K >= J);
             const bool j_wide = enough && !k_wide && J % 128 == 0;
             cudaError_t err = k_wide   ? launch_h8<ADD, 64, 128>(s, r, d, I, J, K, stream)
@@ -377,7 +384,7 @@ cudaError_t transpose_dispatch(const void *src, const void *res, void *dst, int6
                 if (dev >= 0 && dev < 64) done[dev].store(true, std::memory_order_release);
             }
         }
-        const unsigned long long ctas = 148ull * (200 * 1024 / smem < 6 ? 200 * 1024 / smem : 6);
+        const unsigned long long ctas = static_cast<unsigned long long>(sm_count()) * (200 * 1024 / smem < 6 ? 200 * 1024 / smem : 6);
         const unsigned grid = static_cast<unsigned>(total < ctas ? total : ctas);
         transpose_pairs_kernel<T, ADD><<<grid, dim3(32, 8), smem, stream>>>(s, r, d, static_cast<int>(J),
                                                                         static_cast<int>(K), tiles_j, tiles_k, total);

@@ -17,7 +17,7 @@ inline bool aligned_to(const void *p, uintptr_t a) { return (reinterpret_cast<ui
 
 inline unsigned rs_grid(int64_t items) {
     int64_t blocks = (items + kRsThreads - 1) / kRsThreads;
-    const int64_t cap = 148 * 8 * 4;
+    const int64_t cap = sm_count() * 8 * 4;
     return static_cast<unsigned>(blocks < 1 ? 1 : blocks > cap ? cap : blocks);
 }
 

@@ -264,7 +264,7 @@ cudaError_t softmax_dispatch(const void *in, void *out, int64_t rows, int64_t di
         const int per_lane = static_cast<int>((nvec + 31) / 32);
         const int64_t want = (rows + kSmWarps - 1) / kSmWarps;
         auto grid_for = [&](int min_blocks) {
-            const int64_t cap = 148ll * min_blocks;
+            const int64_t cap = static_cast<int64_t>(sm_count()) * min_blocks;
             return static_cast<unsigned>(want < cap ? want : cap);
         };
         if (per_lane <= 1) softmax_warp_kernel<T, 1><<<grid_for(sm_min_blocks(1)), kSmThreads, 0, stream>>>(x, y, rows, d);
@@ -273,16 +273,16 @@ cudaError_t softmax_dispatch(const void *in, void *out, int64_t rows, int64_t di
         else if (per_lane <= 8) softmax_warp_kernel<T, 8><<<grid_for(sm_min_blocks(8)), kSmThreads, 0, stream>>>(x, y, rows, d);
         else softmax_warp_kernel<T, 16><<<grid_for(sm_min_blocks(16)), kSmThreads, 0, stream>>>(x, y, rows, d);
     } else if (dim % VEC == 0 && aligned16(in) && aligned16(out) && nvec <= kSmThreads * 4) {
-        const unsigned grid = static_cast<unsigned>(rows < 148 * 4 ? rows : 148 * 4);
+        const unsigned grid = static_cast<unsigned>(rows < sm_count() * 4 ? rows : sm_count() * 4);
         softmax_cta_kernel<T><<<grid, kSmThreads, 0, stream>>>(x, y, rows, d);
     } else if (dim <= 256) {
         const int64_t want = (rows + kSmWarps - 1) / kSmWarps;
-        const unsigned grid = static_cast<unsigned>(want < 148 * 8 ? want : 148 * 8);
+        const unsigned grid = static_cast<unsigned>(want < sm_count() * 8 ? want : sm_count() * 8);
         if (dim <= 32) softmax_warp_scalar_kernel<T, 1><<<grid, kSmThreads, 0, stream>>>(x, y, rows, d);
         else if (dim <= 96) softmax_warp_scalar_kernel<T, 3><<<grid, kSmThreads, 0, stream>>>(x, y, rows, d);
         else softmax_warp_scalar_kernel<T, 8><<<grid, kSmThreads, 0, stream>>>(x, y, rows, d);
     } else {
-        const unsigned grid = static_cast<unsigned>(rows < 148 * 8 ? rows : 148 * 8);
+        const unsigned grid = static_cast<unsigned>(rows < sm_count() * 8 ? rows : sm_count() * 8);
         const size_t smem = static_cast<size_t>(dim) * sizeof(float);
         if (smem <= 40 * 1024)
             softmax_block_kernel<T, true><<<grid, kSmThreads, smem, stream>>>(x, y, rows, d);

@@ -49,14 +49,21 @@ def _stream(stream) -> int:
     return s.cuda_stream if hasattr(s, "cuda_stream") else int(s)
 
 
-_workspaces: dict[int, torch.Tensor] = {}
+_workspaces: dict[tuple[int, int], torch.Tensor] = {}
 
 
-def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
-    """A per-device scratch buffer, grown on demand and reused (stream-ordered by the caller)."""
-    key = device.index if device.index is not None else torch.cuda.current_device()
+def _workspace(device: torch.device, nbytes: int, stream=None) -> torch.Tensor:
+    """A scratch buffer per (device, stream), grown on demand and reused.  Launches on one stream
+    run in order, so they can share a buffer; launches on different streams may overlap and get
+    their own.  A buffer that is outgrown may still be in use by a kernel on its stream: it is
+    handed back to torch's allocator with that stream recorded, so that it is not reused earlier."""
+    handle = _stream(stream)
+    key = (device.index if device.index is not None else torch.cuda.current_device(), handle)
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:
+        if ws is not None:
+            ws.record_stream(torch.cuda.ExternalStream(handle, device=device) if handle else
+                             torch.cuda.default_stream(device))
         ws = torch.empty(max(nbytes, 1 << 16), dtype=torch.uint8, device=device)
         _workspaces[key] = ws
     return ws
@@ -102,7 +109,7 @@ def groupnorm(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor, num_grou
     code = _dtype_code(x)
     nbytes = lib.sdfl_groupnorm_workspace_bytes_ex(B, Cc, hw, num_groups, code, path,
                                                    cluster_or_splits)
-    ws = _workspace(x.device, nbytes)
+    ws = _workspace(x.device, nbytes, stream)
     with torch.cuda.device(x.device):
         check(lib.sdfl_groupnorm_forward_ex(
             _dev(x, "x"), _dev(out, "out"), _f32(gamma, "gamma"), _f32(beta, "beta"), B, Cc, hw,
@@ -178,7 +185,7 @@ def groupnorm_bias(x: torch.Tensor, channel_bias: torch.Tensor, gamma: torch.Ten
     hw = x.numel() // (B * Cc) if B * Cc else 0
     code = _dtype_code(x)
     ws = _workspace(x.device, lib.sdfl_groupnorm_workspace_bytes_ex(B, Cc, hw, num_groups, code, path,
-                                                                    cluster_or_splits))
+                                                                    cluster_or_splits), stream)
     with torch.cuda.device(x.device):
         check(lib.sdfl_groupnorm_bias_forward_ex(
             _dev(x, "x"), _dev(channel_bias, "channel_bias"), _dev(out, "out"), _f32(gamma, "gamma"),
@@ -198,7 +205,7 @@ def groupnorm_nhwc(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor, num
     if out.numel() != x.numel() or out.dtype != x.dtype:
         raise ValueError("out must have x's element count and dtype")
     code = _dtype_code(x)
-    ws = _workspace(x.device, lib.sdfl_groupnorm_nhwc_workspace_bytes(B, Cc, hw, num_groups, code))
+    ws = _workspace(x.device, lib.sdfl_groupnorm_nhwc_workspace_bytes(B, Cc, hw, num_groups, code), stream)
     with torch.cuda.device(x.device):
         check(lib.sdfl_groupnorm_nhwc_forward(
             _dev(x, "x"), _dev(out, "out"), _f32(gamma, "gamma"), _f32(beta, "beta"), B, Cc, hw,
@@ -264,7 +271,7 @@ def groupnorm_concat(a: torch.Tensor, b: torch.Tensor, gamma: torch.Tensor, beta
     hw = a.numel() // (B * C1) if B * C1 else 0
     out = torch.empty((B, C1 + C2, *a.shape[2:]), dtype=a.dtype, device=a.device) if out is None else out
     code = _dtype_code(a)
-    ws = _workspace(a.device, lib.sdfl_groupnorm_workspace_bytes(B, C1 + C2, hw, num_groups, code))
+    ws = _workspace(a.device, lib.sdfl_groupnorm_workspace_bytes(B, C1 + C2, hw, num_groups, code), stream)
     with torch.cuda.device(a.device):
         check(lib.sdfl_groupnorm_concat_forward(
             _dev(a, "a"), C1, _dev(b, "b"), C2, _dev(out, "out"), _f32(gamma, "gamma"), _f32(beta, "beta"),

@@ -1,4 +1,5 @@
-// C++ parity test of the operator classes (operators.hpp over libsdfl.so) against the CPU
+// C++ parity test of the operator classes (include/sdfl_operators.hpp) and of the C operator handles
+// they wrap (sdfl_groupnorm_create / _op_forward / _destroy ... of include/sdfl.h) against the CPU
 // oracle (oracle/libsdfl_oracle.so, linked here as the checker).  Run on a machine with a GPU:
 //     tests/cpp/test_operators      -> prints "ok" and exits 0, or the first mismatch and 1.
 // Tolerance: |got - want| <= tol + tol * |want| with tol = 1e-5 (fp32 storage).
@@ -9,7 +10,7 @@
 #include <stdexcept>
 #include <vector>
 
-#include "../../mobile-stable-diffusion_b200/csrc/operators.hpp"
+#include "../../include/sdfl_operators.hpp"
 
 extern "C" {
 int oracle_group_norm(const float *in, float *out, const float *w, const float *b, size_t batch, size_t C,
@@ -92,6 +93,52 @@ int main() {
         cuda_check(cudaMemcpy(got.data(), dout.get(), got.size() * 4, cudaMemcpyDeviceToHost), "D2H");
         ok &= close(got, want, 1e-5f, "GEGLU gate");
         ok &= ge.weightShape[0] == 2 * D && ge.weightShape[1] == 320;
+    }
+    // The C handles directly: an unaligned fp32 tensor (the path that needs scratch) inside and outside
+    // the maximum shape stated at create time; forward must not allocate.
+    {
+        const size_t B = 2, C = 64, HW = 15 * 15;            // 225 elements per channel: not a multiple of 4
+        auto x = randn(B * C * HW + 1, 8, 0.f, 1.f), w = randn(C, 9, 1.f, 0.1f), b = randn(C, 10, 0.f, 0.1f);
+        std::vector<float> want(B * C * HW), got(B * C * HW);
+        oracle_group_norm(x.data() + 1, want.data(), w.data(), b.data(), B, C, HW, 32, 1e-5f, 0, nullptr, nullptr);
+        DeviceBuffer dx, dw, db, dy;
+        dx.upload(x); dw.upload(w); db.upload(b);
+        dy.reserve(got.size() * 4);
+        sdfl_groupnorm *op = nullptr;
+        ok &= sdfl_groupnorm_create(&op, 32, 30, 1e-5f, (const float *)dw.get(), (const float *)db.get(), 0, 2, 225, SDFL_F32) == SDFL_ERR_INVALID_VALUE;
+        ok &= op == nullptr;
+        ok &= sdfl_groupnorm_create(&op, 32, C, 1e-5f, (const float *)dw.get(), (const float *)db.get(), 0, B, HW, SDFL_F32) == SDFL_OK;
+        size_t free0 = 0, free1 = 0, total = 0;
+        const float *xin = static_cast<const float *>(dx.get()) + 1;      // 4-byte aligned only
+        // first call: the driver loads the kernels' code on first use; the second call is measured
+        int rc = sdfl_groupnorm_op_forward(op, xin, dy.get(), B, HW, SDFL_F32, nullptr);
+        cuda_check(cudaDeviceSynchronize(), "sync");
+        ok &= rc == SDFL_OK;
+        cuda_check(cudaMemGetInfo(&free0, &total), "cudaMemGetInfo");
+        rc = sdfl_groupnorm_op_forward(op, xin, dy.get(), B, HW, SDFL_F32, nullptr);
+        cuda_check(cudaDeviceSynchronize(), "sync");
+        cuda_check(cudaMemGetInfo(&free1, &total), "cudaMemGetInfo");
+        ok &= rc == SDFL_OK && free0 == free1;
+        if (free0 != free1) std::printf("forward changed free device memory: %zu -> %zu\n", free0, free1);
+        cuda_check(cudaMemcpy(got.data(), dy.get(), got.size() * 4, cudaMemcpyDeviceToHost), "D2H");
+        ok &= close(got, want, 1e-5f, "GroupNorm handle, unaligned");
+        // far beyond the stated maximum on the scratch path: refused, nothing launched
+        rc = sdfl_groupnorm_op_forward(op, xin, dy.get(), 400000, 1, SDFL_F32, nullptr);
+        if (rc != SDFL_ERR_WORKSPACE) std::printf("beyond the maximum shape: status %d\n", rc);
+        ok &= rc == SDFL_ERR_WORKSPACE;
+        ok &= sdfl_groupnorm_destroy(op) == SDFL_OK && sdfl_groupnorm_destroy(nullptr) == SDFL_OK;
+
+        sdfl_geglu *ge = nullptr;
+        int64_t shape[2] = {0, 0};
+        ok &= sdfl_geglu_create(&ge, 320, 1280) == SDFL_OK && sdfl_geglu_weight_shape(ge, shape) == SDFL_OK;
+        ok &= shape[0] == 2560 && shape[1] == 320;
+        ok &= sdfl_geglu_destroy(ge) == SDFL_OK;
+        sdfl_layernorm *ln = nullptr;
+        ok &= sdfl_layernorm_create(&ln, 0, 1e-5f, (const float *)dw.get(), (const float *)db.get()) == SDFL_ERR_INVALID_VALUE;
+        ok &= sdfl_layernorm_create(&ln, 64, 1e-5f, (const float *)dw.get(), nullptr) == SDFL_ERR_INVALID_POINTER;
+        ok &= sdfl_layernorm_create(&ln, 64, 1e-5f, (const float *)dw.get(), (const float *)db.get()) == SDFL_OK;
+        ok &= sdfl_layernorm_destroy(ln) == SDFL_OK;
+        std::printf("%-28s %s\n", "C operator handles", ok ? "ok" : "FAILED");
     }
     std::printf(ok ? "ok\n" : "FAILED\n");
     return ok ? 0 : 1;

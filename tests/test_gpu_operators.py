@@ -125,8 +125,9 @@ def test_a_wait_that_cannot_be_satisfied_ends_by_itself_and_is_reported(sdfl):
 
 
 def test_cpp_operator_classes_against_the_oracle():
-    """operators.hpp (the C++ mirror of the reference's GroupNorm / LayerNorm / GEGLU classes)
-    compiled into tests/cpp/test_operators by __graft_entry__.build()."""
+    """include/sdfl_operators.hpp (the C++ mirror of the reference's GroupNorm / LayerNorm / GEGLU
+    classes) and the C operator handles under it, compiled into tests/cpp/test_operators by
+    tests/cpp/build.py (__graft_entry__.build() runs it)."""
     import os
     import subprocess
     exe = os.path.join(os.path.dirname(__file__), "cpp", "test_operators")
@@ -134,6 +135,46 @@ def test_cpp_operator_classes_against_the_oracle():
         pytest.skip("tests/cpp/test_operators not built (run __graft_entry__.build())")
     r = subprocess.run([exe], capture_output=True, text=True, timeout=120)
     assert r.returncode == 0 and r.stdout.strip().endswith("ok"), r.stdout + r.stderr
+
+
+def test_c_operator_handles_through_ctypes(sdfl):
+    """sdfl_groupnorm_create / _op_forward / _destroy and the LayerNorm / GEGLU handles as a non-C++
+    binder sees them; the results are those of the flat entry points."""
+    import ctypes as C
+    lib = sdfl._capi.lib
+    s = torch.cuda.current_stream().cuda_stream
+    x, gamma, beta = gn_inputs(rng_for(3, 900), (2, 320, 32, 32), "float16")
+    dx, dg, db = to_dev(x), to_dev(gamma), to_dev(beta)
+    op = C.c_void_p()
+    assert lib.sdfl_groupnorm_create(C.byref(op), 32, 320, 1e-5, dg.data_ptr(), db.data_ptr(), 1, 2, 1024, 1) == 0
+    y = torch.empty_like(dx)
+    assert lib.sdfl_groupnorm_op_forward(op, dx.data_ptr(), y.data_ptr(), 2, 1024, 1, s) == 0
+    assert_close(to_np(y), oracle_group_norm(x, gamma, beta, 32, 1e-5, True), TOL["float16"], "GroupNorm handle")
+    assert torch.equal(y, sdfl.ops.groupnorm(dx, dg, db, 32, 1e-5, True))
+    assert lib.sdfl_groupnorm_op_forward(None, dx.data_ptr(), y.data_ptr(), 2, 1024, 1, s) == sdfl._capi.ERR_INVALID_POINTER
+    assert lib.sdfl_groupnorm_destroy(op) == 0
+
+    rng = rng_for(2, 901)
+    xl = rng.standard_normal((154, 768)).astype(np.float32)
+    gl = (1 + 0.1 * rng.standard_normal(768)).astype(np.float32)
+    bl = (0.1 * rng.standard_normal(768)).astype(np.float32)
+    dgl, dbl, dxl = to_dev(gl), to_dev(bl), to_dev(xl)
+    ln = C.c_void_p()
+    assert lib.sdfl_layernorm_create(C.byref(ln), 768, 1e-5, dgl.data_ptr(), dbl.data_ptr()) == 0
+    assert lib.sdfl_layernorm_op_forward(ln, dxl.data_ptr(), dxl.data_ptr(), 154, 0, s) == 0     # in place
+    assert_close(to_np(dxl), oracle.layer_norm(xl, gl, bl), 1e-5, "LayerNorm handle")
+    assert lib.sdfl_layernorm_destroy(ln) == 0
+
+    ab = rng.standard_normal((64, 2560)).astype(np.float32)
+    dab = to_dev(ab)
+    out = torch.empty((64, 1280), device="cuda")
+    ge = C.c_void_p()
+    assert lib.sdfl_geglu_create(C.byref(ge), 320, 1280) == 0
+    shape = (C.c_int64 * 2)()
+    assert lib.sdfl_geglu_weight_shape(ge, shape) == 0 and list(shape) == [2560, 320]
+    assert lib.sdfl_geglu_op_forward(ge, dab.data_ptr(), out.data_ptr(), 64, 0, s) == 0
+    assert_close(to_np(out), oracle.gelu_multiply(ab), 1e-5, "GEGLU handle")
+    assert lib.sdfl_geglu_destroy(ge) == 0
 
 
 def test_host_pipeline_async_queue_of_tensors(sdfl):

@@ -61,6 +61,22 @@ def test_noalloc_matches_split_entry_point_twice_in_a_row(sdfl, dtype):
         assert_close(to_np(got), ref, TOL[dtype], f"call {call} vs oracle")
 
 
+def test_noalloc_call_leaves_device_memory_as_it_found_it(sdfl):
+    """What the entry point is for: with the output supplied by the caller, a call changes neither
+    the device's free memory nor the bytes torch's allocator holds.  Measured around the second
+    call, because the driver loads a kernel's code the first time it is launched."""
+    x, gamma, beta = gn_inputs(rng_for(1, 905), (2, 320, 64, 64), "float16")
+    dx, dg, db = to_dev(x), to_dev(gamma), to_dev(beta)
+    out = torch.empty_like(dx)
+    assert _call_noalloc(sdfl, dx, dg, db, out, 32, 1e-5, True) == 0
+    torch.cuda.synchronize()
+    free0, allocated0, reserved0 = torch.cuda.mem_get_info()[0], torch.cuda.memory_allocated(), torch.cuda.memory_reserved()
+    assert _call_noalloc(sdfl, dx, dg, db, out, 32, 1e-5, True) == 0
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free0
+    assert torch.cuda.memory_allocated() == allocated0 and torch.cuda.memory_reserved() == reserved0
+
+
 def test_noalloc_in_place_and_wrapper(sdfl):
     x, gamma, beta = gn_inputs(rng_for(1, 910), (1, 128, 16, 16), "float32")
     buf = to_dev(x)
