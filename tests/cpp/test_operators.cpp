@@ -122,10 +122,18 @@ int main() {
         if (free0 != free1) std::printf("forward changed free device memory: %zu -> %zu\n", free0, free1);
         cuda_check(cudaMemcpy(got.data(), dy.get(), got.size() * 4, cudaMemcpyDeviceToHost), "D2H");
         ok &= close(got, want, 1e-5f, "GroupNorm handle, unaligned");
-        // far beyond the stated maximum on the scratch path: refused, nothing launched
-        rc = sdfl_groupnorm_op_forward(op, xin, dy.get(), 400000, 1, SDFL_F32, nullptr);
-        if (rc != SDFL_ERR_WORKSPACE) std::printf("beyond the maximum shape: status %d\n", rc);
-        ok &= rc == SDFL_ERR_WORKSPACE;
+        // beyond the stated maximum on the scratch path (300 images: 9600 slabs need 75 KB of pairs, the
+        // handle reserved 64 KB for its 2-image maximum): refused, nothing launched, nothing allocated
+        {
+            const size_t B2 = 300;
+            DeviceBuffer big_in, big_out;
+            big_in.reserve((B2 * C * HW + 1) * 4);
+            big_out.reserve(B2 * C * HW * 4);
+            rc = sdfl_groupnorm_op_forward(op, static_cast<const float *>(big_in.get()) + 1, big_out.get(), B2, HW,
+                                           SDFL_F32, nullptr);
+            if (rc != SDFL_ERR_WORKSPACE) std::printf("beyond the maximum shape: status %d\n", rc);
+            ok &= rc == SDFL_ERR_WORKSPACE;
+        }
         ok &= sdfl_groupnorm_destroy(op) == SDFL_OK && sdfl_groupnorm_destroy(nullptr) == SDFL_OK;
 
         sdfl_geglu *ge = nullptr;
