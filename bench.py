@@ -47,8 +47,9 @@ PEAK_FALLBACK_GBS = 6650.0
 # shapes (inputs larger than L2, within the size an ncu capture may have).  Traffic grows in
 # proportion to the slabs processed, so the per-launch figure reported is this ratio times the
 # launch's algorithmic bytes; None until a capture exists.
-NCU_TRAFFIC_RATIO_MULTI = None
-NCU_TRAFFIC_SOURCE = None
+NCU_TRAFFIC_RATIO_MULTI = 0.934
+NCU_TRAFFIC_SOURCE = ("ncu capture of the same kernel and plan on the 4-GPU shard of the step (batch 2, 486.55 MB: "
+                      "268.3 MB read + 186.0 MB written), scaled by algorithmic bytes; measured for that launch only")
 
 
 def algorithmic_bytes(batch: int, C: int, H: int, esz: int = 2) -> int:
@@ -602,6 +603,19 @@ def op_cases(torch, ops, dev):
     gn("profiling size GN+SiLU f16 [4,128,512,512]", 4, 128, 512, f16, 1e-6)
     gn("GN+SiLU f32 [8,256,256,256]", 8, 256, 256, f32, 1e-6)
 
+    def gn_step(name, B):
+        """The benchmark's step (the four VAE tensors) as ONE launch, at the shard size of 8 / B GPUs."""
+        def make():
+            xs = [rnd((B, C, H, H), f16) for C, H in SHAPES]
+            ys = [torch.empty_like(x) for x in xs]
+            gs = [1 + 0.1 * rnd((C,), f32) for C, H in SHAPES]
+            bs = [0.1 * rnd((C,), f32) for C, H in SHAPES]
+            return lambda: ops.groupnorm_multi(xs, gs, bs, 32, 1e-6, True, outs=ys)
+        cases.append((name, sum(algorithmic_bytes(B, C, H) for C, H in SHAPES), make, ("gnstep", B)))
+
+    for B in (8, 4, 2, 1):
+        gn_step(f"cfg5 step GN+SiLU f16 batch {B}, four shapes in one launch", B)
+
     def gn_split(name, B, C, H, dtype, eps):
         esz = 2 if dtype == f16 else 4
 
@@ -859,6 +873,14 @@ def cpu_reference_case(spec) -> dict:
         g, b = np.ones(C, np.float32), np.zeros(C, np.float32)
         t = timed(lambda: oracle.group_norm(x, g, b, 32, eps, True, backend=backend), reps=2)
         scale, note = float(B), f"one image x {B}"
+    elif kind == "gnstep":
+        B = spec[1]
+        t = 0.0
+        for C, H in SHAPES:
+            x = rng.standard_normal((1, C, H, H), dtype=np.float32)
+            g, b = np.ones(C, np.float32), np.zeros(C, np.float32)
+            t += timed(lambda: oracle.group_norm(x, g, b, 32, 1e-6, True, backend=backend), reps=1)
+        scale, note = float(B), f"one image of each shape x {B}"
     elif kind == "gnbias":
         _, B, C, H, eps = spec
         x = rng.standard_normal((C, H, H), dtype=np.float32)
