@@ -9,8 +9,7 @@
 // range the two agree to a few ulp (the parity tests run there).
 //
 // Rows whose bytes are a multiple of 16 and fit 16 vectors per lane live in one warp's
-// registers: one read, one write.  Short rows of any other length (the 77 keys of cross-attention)
-// go through shared memory in blocks of rows that are whole 16-byte vectors.  Other rows take a CTA each, with the row's exponentials
+// registers: one read, one write.  Other rows take a CTA each, with the row's exponentials
 // cached in shared memory as the reference does (`cache`), or re-read when too long for that.
 #include "common.cuh"
 #include "kernels.h"
@@ -252,65 +251,6 @@ softmax_block_kernel(const T *in, T *out, long long rows, int dim) {
     }
 }
 
-// Short rows whose bytes are not a multiple of 16 (the 77 keys of cross-attention: 154 or 308 bytes
-// per row): a CTA takes blocks of R consecutive rows, R chosen so that a full block is a whole number
-// of 16-byte vectors and starts on a 16-byte boundary.  The block is copied to shared memory with
-// 16-byte loads, every warp normalises rows in place there (element accesses stay in shared
-// memory), and the block leaves with 16-byte stores: global memory only sees full-width,
-// coalesced traffic, where the element-wise kernel's 2-byte accesses to 154-byte rows waste most
-// of every sector.  The last, shorter block copies its odd tail element by element.
-template <typename T, int MAXE>
-__global__ void __launch_bounds__(kSmThreads)
-softmax_rowblock_kernel(const T *__restrict__ in, T *out, long long rows, int dim, int rows_per_block) {
-    extern __shared__ uint4 block_smem[];
-    T *s = reinterpret_cast<T *>(block_smem);
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const long long nblocks = (rows + rows_per_block - 1) / rows_per_block;
-    for (long long blk = blockIdx.x; blk < nblocks; blk += gridDim.x) {
-        const long long r0 = blk * rows_per_block;
-        const int nr = static_cast<int>(rows - r0 < rows_per_block ? rows - r0 : rows_per_block);
-        const int nelem = nr * dim;
-        const int nvec = static_cast<int>(nelem * sizeof(T) / 16);
-        const T *src = in + r0 * dim;
-        T *dst = out + r0 * dim;
-        const uint4 *src4 = reinterpret_cast<const uint4 *>(src);
-        for (int i = tid; i < nvec; i += kSmThreads) block_smem[i] = ld_stream(src4 + i);
-        for (int i = nvec * static_cast<int>(16 / sizeof(T)) + tid; i < nelem; i += kSmThreads) s[i] = src[i];
-        __syncthreads();
-        for (int row = warp; row < nr; row += kSmWarps) {
-            T *x = s + row * dim;
-            float e[MAXE];
-            float m = -INFINITY;
-#pragma unroll
-            for (int i = 0; i < MAXE; ++i) {
-                const int idx = lane + 32 * i;
-                e[i] = idx < dim ? to_float<T>(x[idx]) : -INFINITY;
-                m = fmaxf(m, e[i]);
-            }
-            m = warp_max(m);
-            const float shift = m * kLog2e;
-            float sum = 0.f;
-#pragma unroll
-            for (int i = 0; i < MAXE; ++i) {
-                e[i] = lane + 32 * i < dim ? ex2_approx(fmaf(e[i], kLog2e, -shift)) : 0.f;     // exp(x - max)
-                sum += e[i];
-            }
-            sum = warp_sum(sum);
-            const float inv = 1.0f / sum;
-#pragma unroll
-            for (int i = 0; i < MAXE; ++i) {
-                const int idx = lane + 32 * i;
-                if (idx < dim) x[idx] = from_float<T>(e[i] * inv);
-            }
-        }
-        __syncthreads();
-        uint4 *dst4 = reinterpret_cast<uint4 *>(dst);
-        for (int i = tid; i < nvec; i += kSmThreads) st_stream(dst4 + i, block_smem[i]);
-        for (int i = nvec * static_cast<int>(16 / sizeof(T)) + tid; i < nelem; i += kSmThreads) dst[i] = s[i];
-        __syncthreads();                       // the next block overwrites the shared-memory copy
-    }
-}
-
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 template <typename T>
@@ -335,21 +275,6 @@ cudaError_t softmax_dispatch(const void *in, void *out, int64_t rows, int64_t di
     } else if (dim % VEC == 0 && aligned16(in) && aligned16(out) && nvec <= kSmThreads * 4) {
         const unsigned grid = static_cast<unsigned>(rows < sm_count() * 4 ? rows : sm_count() * 4);
         softmax_cta_kernel<T><<<grid, kSmThreads, 0, stream>>>(x, y, rows, d);
-    } else if (dim <= 256 && aligned16(in) && aligned16(out) && rows >= 64) {
-        // rows per block: a multiple of the smallest count that makes a block a whole number of vectors,
-        // about 12 KB per block (several CTAs per SM, each with its block in shared memory)
-        const int64_t row_bytes = dim * static_cast<int64_t>(sizeof(T));
-        int64_t g = row_bytes, h = 16;
-        while (h) { const int64_t t = g % h; g = h; h = t; }           // gcd(row_bytes, 16)
-        const int64_t r_min = 16 / g;
-        int64_t R = r_min * ((12 * 1024 + r_min * row_bytes - 1) / (r_min * row_bytes));
-        const size_t smem = static_cast<size_t>(R * row_bytes);
-        const int64_t nblocks = (rows + R - 1) / R;
-        const unsigned grid = static_cast<unsigned>(nblocks < sm_count() * 8 ? nblocks : sm_count() * 8);
-        const int rpb = static_cast<int>(R);
-        if (dim <= 32) softmax_rowblock_kernel<T, 1><<<grid, kSmThreads, smem, stream>>>(x, y, rows, d, rpb);
-        else if (dim <= 96) softmax_rowblock_kernel<T, 3><<<grid, kSmThreads, smem, stream>>>(x, y, rows, d, rpb);
-        else softmax_rowblock_kernel<T, 8><<<grid, kSmThreads, smem, stream>>>(x, y, rows, d, rpb);
     } else if (dim <= 256) {
         const int64_t want = (rows + kSmWarps - 1) / kSmWarps;
         const unsigned grid = static_cast<unsigned>(want < sm_count() * 8 ? want : sm_count() * 8);
