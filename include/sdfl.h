@@ -117,7 +117,10 @@ int sdfl_groupnorm_plan(int64_t batch, int64_t channels, int64_t hw, int64_t num
  * counter lives there.  With NULL a buffer inside the library is used, shared by all such calls
  * on the device: pass an own workspace per stream when two of these launches could overlap on the
  * GPU.  The grid is sized to be resident as a whole (its CTAs wait for each other, every wait
- * bounded): run it on a device that is not oversubscribed by other long-running kernels. */
+ * bounded): run it on a device that is not oversubscribed by other long-running kernels.  If a wait
+ * does run out, sdfl_device_status() reports bit 0 and the launch's output is not valid; clearing the
+ * status also resets the library's own buffer, and a caller's workspace must be zero-filled again
+ * before its next use. */
 enum { SDFL_GN_MULTI_MAX = 8 };
 typedef struct sdfl_gn_tensor {
     const void *in;

@@ -379,7 +379,12 @@ gn_multi_kernel(const MultiArgs a) {
             // warp_m alternates between two sets: a warp can be at most one F phase ahead of warp 0
             Moments c = lane < kCWarps ? warp_m[(it & 1u) * kCWarps + lane] : Moments{0.f, 0.f, 0.f};
             c = warp_merge(c);
-            if (lane == 0) {
+            if (g.k == 1) {
+                // a team of one: the slab's moments are this CTA's, nothing to exchange
+                peer[buf * 32u + lane] = lane == 0 ? make_float4(0.f, c.n, c.mean, c.m2) : make_float4(0.f, 0.f, 0.f, 0.f);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_addr(&stat_bar[buf]));
+            } else if (lane == 0) {
                 ExchSlot *mine = &a.x->slot[blockIdx.x][buf];
                 st_relaxed_gpu_u64(&mine->mean, (static_cast<unsigned long long>(token) << 32) | __float_as_uint(c.mean));
                 st_relaxed_gpu_u64(&mine->m2, (static_cast<unsigned long long>(token) << 32) | __float_as_uint(c.m2));
@@ -396,7 +401,7 @@ gn_multi_kernel(const MultiArgs a) {
         const uint32_t c_first = hwv_div.div(g.v0 + (g.P - g.H) % g.P * cv);
         const float w_first = __ldg(wp + c_first), b_first = __ldg(bp + c_first);
         if (TRACE && tid == 0) stamp = global_timer();
-        if (warp == 0) {
+        if (warp == 0 && g.k > 1) {
             // collect the team's results from global memory into shared memory
             float4 r = make_float4(0.f, 0.f, 0.f, 0.f);
             if (lane < g.k) {
@@ -866,6 +871,11 @@ cudaError_t gn_multi_read_status(unsigned int *value, bool clear, cudaStream_t s
         const unsigned int zero = 0;
         err = cudaMemcpyToSymbolAsync(g_multi_status, &zero, sizeof(unsigned int), 0,
                                       cudaMemcpyHostToDevice, stream);
+        // A launch that gave up a wait may have left the library's own scratch (sequence word, arrival
+        // and item counters) half-way: start it afresh.  A caller's workspace is the caller's to clear.
+        void *p = nullptr;
+        if (err == cudaSuccess) err = scratch_address(&p);
+        if (err == cudaSuccess) err = cudaMemsetAsync(p, 0, sizeof(ExchScratch), stream);
         if (err == cudaSuccess) err = cudaStreamSynchronize(stream);
     }
     return err;
