@@ -509,7 +509,8 @@ def run_ours(args) -> None:
         if args.chain:
             kernel = ("gn_resident_kernel<__half, silu> / gn_register_kernel (one launch per tensor): " +
                       ", ".join(f"[{p['shape'][0]},{p['shape'][1]},{p['shape'][2]},{p['shape'][3]}] {p['path']}"
-                                + (f" cluster {p['cluster']} x {p['nclusters']}" if p["path"] == "cluster ring" else "")
+                                + (f" cluster {p['cluster']} x {p['nclusters']}"
+                                   if p["path"] == "cluster ring" or p["cluster"] > 1 else "")
                                 for p in per_shape))
         else:
             teams = [(multi_plan[2] >> (8 * k)) & 0xff for k in range(len(SHAPES))] if multi_plan else []

@@ -540,10 +540,11 @@ int sdfl_elemwise_add(const void *A, const void *B, void *C, int64_t n, int dtyp
 
 int sdfl_device_status(unsigned int *value, int clear, void *stream) {
     if (!value) return SDFL_ERR_INVALID_POINTER;
-    unsigned int ring = 0, multi = 0;
+    unsigned int ring = 0, multi = 0, reg = 0;
     cudaError_t e = sdfl::gn_read_status(&ring, clear != 0, as_stream(stream));
     if (e == cudaSuccess) e = sdfl::gn_multi_read_status(&multi, clear != 0, as_stream(stream));
-    *value = ring | multi;
+    if (e == cudaSuccess) e = sdfl::gn_register_read_status(&reg, clear != 0, as_stream(stream));
+    *value = ring | multi | reg;
     return wrap(e);
 }
 

@@ -27,6 +27,7 @@ cudaError_t gn_ring_launch(const GnShape &s, const GnPlan &plan, const void *in,
 constexpr int kGnRegThreads = 512;
 constexpr int kGnRegMaxVecs = 24;                    // per thread: slabs up to 512 * 24 * 16 B = 192 KB
 constexpr size_t kGnRegMaxStageBytes = 200 * 1024;   // shared-memory staging of the channels-last store
+constexpr int kGnRegMaxCluster = 8;                  // CTAs that may share one slab (portable cluster size)
 cudaError_t gn_register_launch(const GnShape &s, const GnPlan &plan, const void *in, void *out,
                                const float *w, const float *b, cudaStream_t stream, const void *bias,
                                const void *in2, int64_t c1);

@@ -20,6 +20,9 @@ constexpr int kRegMaxVecs = kGnRegMaxVecs;
 // group has at most this many channels: fetched after the statistics instead, their DRAM round
 // trip (cold weights: every layer has its own) was 10-20 % of a small launch.
 constexpr uint32_t kRegStagedChannels = 256;
+constexpr int kRegMaxCluster = kGnRegMaxCluster;
+
+__device__ unsigned int g_reg_status;   // sticky; bit 0: a bounded wait for the cluster's moments ran out
 
 struct RegArgs {
     const void *in;
@@ -40,23 +43,52 @@ struct RegArgs {
     // input as two tensors concatenated along the channels (see ResidentArgs); needs vec_uniform
     const void *in2;
     uint32_t c1;
+    // CLU: a cluster of `cluster` CTAs per slab, each holding `share_vecs` consecutive vectors of it
+    uint32_t cluster, share_vecs;
 };
 
 // NHWC: the result is written channels-last, out[n][p][c] (the permute3D__0_2_1 that follows the
 // norm of a SpatialTransformer block, SpatialTransformer.cpp:127-140, fused into the store).  The
 // normalised slab [cpg][hw] goes through shared memory with a 4-byte skew per channel row and
 // leaves as runs of cpg consecutive channels per pixel.
-template <typename T, int ACT, bool BIAS, int NVT, bool NHWC>
-__global__ void __launch_bounds__(kRegThreads, NVT <= 4 ? 2 : 1)
+//
+// CLU: the slab is shared by a thread-block cluster, CTA r holding vectors [r * share, (r + 1) * share)
+// of it, so that slabs of 64-240 KB are pulled by 2-8 SMs instead of one.  Each CTA pushes its
+// (n, mean, M2) into every CTA of the cluster (distributed shared memory) and signals that CTA's
+// mbarrier; everybody folds the same values in the same order, so all CTAs of a slab normalise with
+// bit-identical statistics.
+template <typename T, int ACT, bool BIAS, int NVT, bool NHWC, bool CLU>
+__global__ void __launch_bounds__(kRegThreads, (NVT <= 4 || (CLU && NVT <= 8)) ? 2 : 1)
 gn_register_kernel(const RegArgs a) {
+    static_assert(!(NHWC && CLU), "the channels-last store needs the whole slab in one CTA");
     constexpr int VEC = VecOf<T>::N;
     constexpr bool HALF = sizeof(T) == 2;
     __shared__ Moments warp_m[kRegThreads / 32];
     __shared__ float s_w[kRegStagedChannels], s_b[kRegStagedChannels];
+    __shared__ __align__(16) float4 cl_m[2][kRegMaxCluster];  // CLU: (n, mean, M2, -) of every CTA of the cluster
+    __shared__ __align__(8) uint64_t cl_bar[2];               // CLU: one arrival per CTA of the cluster
     extern __shared__ __align__(16) unsigned char tsm[];      // NHWC only: cpg rows of row_bytes
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     const bool staged = a.cpg <= kRegStagedChannels;
-    for (uint32_t unit = blockIdx.x; unit < a.units; unit += gridDim.x) {
+    uint32_t rank = 0;
+    if (CLU) {
+        asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+        if (tid == 0) {
+            mbar_init(smem_addr(&cl_bar[0]), a.cluster);
+            mbar_init(smem_addr(&cl_bar[1]), a.cluster);
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        }
+        // Every CTA of the cluster has started and set up its barriers once this completes; it
+        // is waited for only before the first push, behind the slab's loads.
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    }
+    const uint32_t lo = CLU ? rank * a.share_vecs : 0u;
+    const uint32_t hi = CLU ? min(lo + a.share_vecs, a.slab_vecs) : a.slab_vecs;
+    const uint32_t first = CLU ? blockIdx.x / a.cluster : blockIdx.x;
+    const uint32_t stride = CLU ? gridDim.x / a.cluster : gridDim.x;
+    bool timed_out = false;
+    uint32_t it = 0;
+    for (uint32_t unit = first; unit < a.units; unit += stride, ++it) {
         const uint32_t ch0 = (unit % a.groups) * a.cpg;
         float w_mine = 0.f, b_mine = 0.f;
         if (staged && tid < a.cpg) {             // in flight together with the slab's loads
@@ -82,8 +114,8 @@ gn_register_kernel(const RegArgs a) {
         uint4 v[NVT];
 #pragma unroll
         for (int k = 0; k < NVT; ++k) {
-            const uint32_t idx = tid + k * kRegThreads;
-            if (idx < a.slab_vecs) v[k] = ld_stream((idx < split ? src : src2) + idx);
+            const uint32_t idx = lo + tid + k * kRegThreads;
+            if (idx < hi) v[k] = ld_stream((idx < split ? src : src2) + idx);
         }
         if (staged && tid < a.cpg) {             // visible after the barrier that follows the moments
             s_w[tid] = w_mine;
@@ -93,15 +125,15 @@ gn_register_kernel(const RegArgs a) {
         float s[2] = {0.f, 0.f}, q[2] = {0.f, 0.f};
         float shift = 0.f;
         uint32_t mine = 0;
-        if (tid < a.slab_vecs) {
+        if (lo + tid < hi) {
             shift = HALF ? __half2float(__ushort_as_half(static_cast<unsigned short>(v[0].x & 0xffffu)))
                          : __uint_as_float(v[0].x);
-            if (BIAS) shift += to_float<T>(erow[a.hw_div.div(tid * VEC)]);
+            if (BIAS) shift += to_float<T>(erow[a.hw_div.div((lo + tid) * VEC)]);
         }
 #pragma unroll
         for (int k = 0; k < NVT; ++k) {
-            const uint32_t idx = tid + k * kRegThreads;
-            if (idx < a.slab_vecs) {
+            const uint32_t idx = lo + tid + k * kRegThreads;
+            if (idx < hi) {
                 if (!BIAS) {
                     stats_vec<T>(v[k], shift, s, q);
                 } else if (a.vec_uniform) {
@@ -133,13 +165,32 @@ gn_register_kernel(const RegArgs a) {
         // every warp folds the 16 per-warp moments itself, in the same order
         Moments t = lane < kRegThreads / 32 ? warp_m[lane] : Moments{0.f, 0.f, 0.f};
         t = warp_merge(t);
+        if (CLU) {
+            const uint32_t par = it & 1u;
+            if (it == 0) asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+            if (warp == 0) {
+                const float bn = __shfl_sync(0xffffffffu, t.n, 0), bmean = __shfl_sync(0xffffffffu, t.mean, 0),
+                            bm2 = __shfl_sync(0xffffffffu, t.m2, 0);
+                if (lane < a.cluster) {
+                    const uint32_t dst_m = map_to_rank(smem_addr(&cl_m[par][rank]), lane);
+                    st_peer_f32x2(dst_m, bn, bmean);
+                    st_peer_f32x2(dst_m + 8u, bm2, 0.f);
+                    mbar_arrive_peer(map_to_rank(smem_addr(&cl_bar[par]), lane));
+                }
+            }
+            if (!mbar_wait_cluster_bounded(smem_addr(&cl_bar[par]), (it >> 1) & 1u,
+                                           timed_out ? kWaitCyclesAfterTimeout : kWaitCycles))
+                timed_out = true;
+            const float4 pm = lane < a.cluster ? cl_m[par][lane] : make_float4(0.f, 0.f, 0.f, 0.f);
+            t = warp_merge(Moments{pm.x, pm.y, pm.z});
+        }
         const float mean = __shfl_sync(0xffffffffu, t.mean, 0);
         const float var = __shfl_sync(0xffffffffu, t.m2, 0) / static_cast<float>(a.slab_elems);   // biased
         const float rstd = 1.0f / sqrtf(var + a.eps);
 #pragma unroll
         for (int k = 0; k < NVT; ++k) {
-            const uint32_t idx = tid + k * kRegThreads;
-            if (idx < a.slab_vecs) {
+            const uint32_t idx = lo + tid + k * kRegThreads;
+            if (idx < hi) {
                 if (a.vec_uniform) {
                     const uint32_t cl = a.hwv_div.div(idx), c = ch0 + cl;
                     const float mc = BIAS ? mean - to_float<T>(erow[cl]) : mean;
@@ -195,6 +246,7 @@ gn_register_kernel(const RegArgs a) {
             __syncthreads();   // the next slab overwrites the staging rows
         }
     }
+    if (CLU && timed_out && tid == 0) atomicOr(&g_reg_status, 1u);
 }
 
 constexpr size_t kRegMaxStageBytes = kGnRegMaxStageBytes;
@@ -206,18 +258,39 @@ cudaError_t launch_register_nhwc(const RegArgs &a, unsigned grid, size_t smem, c
     cudaError_t err = cudaGetDevice(&dev);
     if (err != cudaSuccess) return err;
     if (!(dev >= 0 && dev < kMaxDevices && done[dev].load(std::memory_order_acquire))) {
-        err = cudaFuncSetAttribute(gn_register_kernel<T, ACT, false, NVT, true>,
+        err = cudaFuncSetAttribute(gn_register_kernel<T, ACT, false, NVT, true, false>,
                                    cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    static_cast<int>(kRegMaxStageBytes));
         if (err != cudaSuccess) return err;
         if (dev >= 0 && dev < kMaxDevices) done[dev].store(true, std::memory_order_release);
     }
-    gn_register_kernel<T, ACT, false, NVT, true><<<grid, kRegThreads, smem, stream>>>(a);
+    gn_register_kernel<T, ACT, false, NVT, true, false><<<grid, kRegThreads, smem, stream>>>(a);
     return cudaGetLastError();
+}
+
+template <typename T, int ACT, bool BIAS, int NVT>
+cudaError_t launch_register_cluster(const RegArgs &a, unsigned grid, cudaStream_t stream) {
+    cudaLaunchConfig_t cfg;
+    cudaLaunchAttribute attr[1];
+    cluster_config(&cfg, attr, grid, static_cast<int>(a.cluster), kRegThreads, 0, stream);
+    return cudaLaunchKernelEx(&cfg, gn_register_kernel<T, ACT, BIAS, NVT, false, true>, a);
 }
 
 template <typename T, int ACT, bool BIAS>
 cudaError_t launch_register_as(const RegArgs &a, bool nhwc, cudaStream_t stream) {
+    if (a.cluster > 1) {
+        if (nhwc) return cudaErrorInvalidValue;
+        const uint32_t per_thread = (a.share_vecs + kRegThreads - 1) / kRegThreads;
+        // whole clusters only; a persistent grid beyond what the device holds would only queue
+        const unsigned max_clusters = static_cast<unsigned>(sm_count()) * 64u / a.cluster;
+        const unsigned grid = (a.units < max_clusters ? a.units : max_clusters) * a.cluster;
+        cudaError_t err = per_thread <= 4    ? launch_register_cluster<T, ACT, BIAS, 4>(a, grid, stream)
+                          : per_thread <= 8  ? launch_register_cluster<T, ACT, BIAS, 8>(a, grid, stream)
+                          : per_thread <= 12 ? launch_register_cluster<T, ACT, BIAS, 12>(a, grid, stream)
+                                             : launch_register_cluster<T, ACT, BIAS, kRegMaxVecs>(a, grid, stream);
+        if (err == cudaSuccess) g_launches.fetch_add(1);
+        return err;
+    }
     const uint32_t per_thread = (a.slab_vecs + kRegThreads - 1) / kRegThreads;
     const unsigned grid = a.units < static_cast<unsigned>(sm_count()) * 64u ? a.units : static_cast<unsigned>(sm_count()) * 64u;
     cudaError_t err;
@@ -229,11 +302,11 @@ cudaError_t launch_register_as(const RegArgs &a, bool nhwc, cudaStream_t stream)
                                  : launch_register_nhwc<T, ACT, kRegMaxVecs>(a, grid, smem, stream);
     } else {
         if (per_thread <= 4)
-            gn_register_kernel<T, ACT, BIAS, 4, false><<<grid, kRegThreads, 0, stream>>>(a);
+            gn_register_kernel<T, ACT, BIAS, 4, false, false><<<grid, kRegThreads, 0, stream>>>(a);
         else if (per_thread <= 12)
-            gn_register_kernel<T, ACT, BIAS, 12, false><<<grid, kRegThreads, 0, stream>>>(a);
+            gn_register_kernel<T, ACT, BIAS, 12, false, false><<<grid, kRegThreads, 0, stream>>>(a);
         else
-            gn_register_kernel<T, ACT, BIAS, kRegMaxVecs, false><<<grid, kRegThreads, 0, stream>>>(a);
+            gn_register_kernel<T, ACT, BIAS, kRegMaxVecs, false, false><<<grid, kRegThreads, 0, stream>>>(a);
         err = cudaGetLastError();
     }
     if (err == cudaSuccess) g_launches.fetch_add(1);
@@ -276,6 +349,9 @@ cudaError_t gn_register_launch(const GnShape &s, const GnPlan &plan, const void 
     a.out_div = FastDiv::make(static_cast<uint32_t>(a.pair ? cpg / 2 : cpg));
     a.in2 = in2;
     a.c1 = static_cast<uint32_t>(c1);
+    a.cluster = static_cast<uint32_t>(plan.cluster > 1 ? plan.cluster : 1);
+    if (a.cluster > static_cast<uint32_t>(kRegMaxCluster)) return cudaErrorInvalidValue;
+    a.share_vecs = (a.slab_vecs + a.cluster - 1) / a.cluster;
     if (in2 != nullptr && !gn_concat_fused_ok(s, plan, in, in2, c1)) return cudaErrorInvalidValue;
     const bool nhwc = plan.nhwc != 0;
     if (s.dtype == kF16)
@@ -283,6 +359,21 @@ cudaError_t gn_register_launch(const GnShape &s, const GnPlan &plan, const void 
                                  : launch_register<__half, kActNone>(a, nhwc, stream);
     return s.act == kActSilu ? launch_register<float, kActSilu>(a, nhwc, stream)
                              : launch_register<float, kActNone>(a, nhwc, stream);
+}
+
+cudaError_t gn_register_read_status(unsigned int *value, bool clear, cudaStream_t stream) {
+    cudaError_t err = cudaMemcpyFromSymbolAsync(value, g_reg_status, sizeof(unsigned int), 0,
+                                                cudaMemcpyDeviceToHost, stream);
+    if (err != cudaSuccess) return err;
+    err = cudaStreamSynchronize(stream);
+    if (err != cudaSuccess) return err;
+    if (clear && *value != 0) {
+        const unsigned int zero = 0;
+        err = cudaMemcpyToSymbolAsync(g_reg_status, &zero, sizeof(unsigned int), 0,
+                                      cudaMemcpyHostToDevice, stream);
+        if (err == cudaSuccess) err = cudaStreamSynchronize(stream);
+    }
+    return err;
 }
 
 }  // namespace sdfl

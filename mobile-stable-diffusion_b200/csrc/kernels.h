@@ -108,6 +108,8 @@ cudaError_t gn_launch_static_scratch(const GnShape &s, const GnPlan &plan, const
 // Sticky device-side status word of the GroupNorm kernels (bit 0: a bounded wait on a bulk
 // copy ran out).  Reads it, optionally clears it.
 cudaError_t gn_read_status(unsigned int *value, bool clear, cudaStream_t stream);
+// The same word of the register kernel's cluster variant (a wait for the cluster's moments).
+cudaError_t gn_register_read_status(unsigned int *value, bool clear, cudaStream_t stream);
 
 // Enqueues a one-warp kernel whose bounded wait is bound to run out (nothing completes its
 // barrier): the wait ends after `limit_cycles` clock cycles and raises bit 0 of the status word.

@@ -34,7 +34,7 @@ def test_config1_fp32_every_path_and_cluster_size(sdfl):
     x, gamma, beta = gn_inputs(rng_for(1, 0), (1, 320, 64, 64), "float32")
     want = oracle_group_norm(x, gamma, beta, 32, 1e-5, True)
     plan = sdfl.ops.groupnorm_plan(1, 320, 4096, 32, torch.float32)
-    assert plan["path"] == sdfl.ops.GN_RESIDENT and plan["workspace"] == 0
+    assert plan["path"] == sdfl.ops.GN_REGISTER and plan["cluster"] == 4 and plan["workspace"] == 0
     assert_close(run_gn(sdfl, x, gamma, beta, 32, 1e-5, True), want, 1e-5, "auto")
     for cluster in (1, 2, 3, 4, 5, 7, 8, 12, 16):
         try:
@@ -79,7 +79,8 @@ def test_config5_vae_shapes_fp16(sdfl, shape):
     x, gamma, beta = gn_inputs(rng_for(5, shape[1]), shape, "float16")
     want = oracle_group_norm(x, gamma, beta, 32, 1e-6, True)
     plan = sdfl.ops.groupnorm_plan(shape[0], shape[1], shape[2] * shape[3], 32, torch.float16)
-    want_path = sdfl.ops.GN_REGISTER if shape[2] == 64 else sdfl.ops.GN_RESIDENT    # 128 KB slabs fit registers
+    # 128 KB slabs fit one CTA's registers, 32 slabs of 512 KB a cluster of 8 CTAs' registers
+    want_path = sdfl.ops.GN_REGISTER if shape[2] <= 128 else sdfl.ops.GN_RESIDENT
     assert plan["path"] == want_path, plan
     got = run_gn(sdfl, x, gamma, beta, 32, 1e-6, True)
     assert_close(got, want, TOL["float16"], f"{shape} automatic path {plan}")
@@ -336,6 +337,66 @@ def test_register_path_one_cta_per_slab(sdfl, shape, G, dtype):
                                 out=out.tensor, **kw)
         out.check()
         assert_close(to_np(out.tensor), want, TOL[dtype], f"register+bias {shape} silu={silu}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "float16"])
+@pytest.mark.parametrize("shape,G", [
+    ((2, 640, 64, 64), 32),    # 64 slabs of 160 KB (fp16): the automatic plan's cluster of 4
+    ((1, 512, 64, 64), 32),    # 32 slabs of 128 KB (fp16)
+    ((2, 96, 20, 20), 32),     # 150 vectors (fp16) per slab: shares of 19 vectors, the last CTA short
+    ((3, 12, 6, 6), 3),        # vectors straddle channels; fewer vectors than CTAs x threads
+    ((2, 8, 2, 2), 2),         # one or two vectors per slab: most CTAs of the cluster hold nothing
+    ((40, 64, 8, 8), 32),      # more slabs than clusters in a wave
+])
+def test_register_path_cluster_per_slab(sdfl, shape, G, dtype):
+    """A thread-block cluster of 2, 4 or 8 CTAs per slab, each CTA's share in its registers and the
+    moments exchanged through distributed shared memory: same results as the oracle, with and
+    without the fused per-channel addend, also in place."""
+    rng = rng_for(6, 1500 + sum(shape))
+    x, gamma, beta = gn_inputs(rng, shape, dtype)
+    e = (rng.standard_normal(shape[:2]) * 0.8).astype(np.float32).astype(x.dtype)
+    want = oracle_group_norm(x, gamma, beta, G, 1e-5, True)
+    want_bias = oracle_bias_group_norm(x, e, gamma, beta, G, 1e-5, False)
+    for cluster in (2, 4, 8):
+        kw = dict(path=sdfl.ops.GN_REGISTER, cluster_or_splits=cluster)
+        plan = sdfl.ops.groupnorm_plan(shape[0], shape[1], shape[2] * shape[3], G, getattr(torch, dtype),
+                                       sdfl.ops.GN_REGISTER, cluster)
+        assert plan["path"] == sdfl.ops.GN_REGISTER and plan["cluster"] == cluster
+        out = Guarded(shape, getattr(torch, dtype))
+        sdfl.ops.groupnorm(to_dev(x), to_dev(gamma), to_dev(beta), G, 1e-5, True, out=out.tensor, **kw)
+        out.check()
+        assert_close(to_np(out.tensor), want, TOL[dtype], f"register cluster {cluster} {shape}")
+        buf = to_dev(x)
+        sdfl.ops.groupnorm(buf, to_dev(gamma), to_dev(beta), G, 1e-5, True, out=buf, **kw)
+        assert_close(to_np(buf), want, TOL[dtype], f"register cluster {cluster} in place {shape}")
+        out = Guarded(shape, getattr(torch, dtype))
+        sdfl.ops.groupnorm_bias(to_dev(x), to_dev(e), to_dev(gamma), to_dev(beta), G, 1e-5, False,
+                                out=out.tensor, **kw)
+        out.check()
+        assert_close(to_np(out.tensor), want_bias, TOL[dtype], f"register cluster {cluster} + bias {shape}")
+    assert sdfl.ops.device_status() == 0
+
+
+def test_register_cluster_is_the_automatic_plan_for_few_medium_slabs(sdfl):
+    """At most 64 slabs of 100-512 KB: a cluster per slab on the register path; results as the oracle's,
+    also for the input given as two tensors to concatenate."""
+    cases = [((2, 640, 64, 64), torch.float16, 4), ((2, 960, 64, 64), torch.float16, 4),
+             ((1, 320, 64, 64), torch.float32, 4), ((1, 512, 128, 128), torch.float16, 8),
+             ((2, 320, 64, 64), torch.float16, 1), ((8, 512, 64, 64), torch.float16, 1)]
+    for shape, dt, cluster in cases:
+        plan = sdfl.ops.groupnorm_plan(shape[0], shape[1], shape[2] * shape[3], 32, dt)
+        assert plan["path"] == sdfl.ops.GN_REGISTER and plan["cluster"] == cluster, (shape, plan)
+    # not a power of two, or beyond the portable cluster size: refused
+    for bad in (3, 16):
+        with pytest.raises(sdfl.SdflError):
+            sdfl.ops.groupnorm_plan(2, 640, 4096, 32, torch.float16, sdfl.ops.GN_REGISTER, bad)
+    rng = rng_for(6, 1601)
+    a, gamma, beta = gn_inputs(rng, (2, 640, 64, 64), "float16")
+    want = oracle_group_norm(a, gamma, beta, 32, 1e-5, True)
+    got = sdfl.ops.groupnorm_concat(to_dev(a[:, :320]).contiguous(), to_dev(a[:, 320:]).contiguous(),
+                                    to_dev(gamma), to_dev(beta), 32, 1e-5, True)
+    assert_close(to_np(got), want, TOL["float16"], "concat, cluster of 4 per slab")
+    assert sdfl.ops.device_status() == 0
 
 
 def test_register_path_refuses_large_slabs(sdfl):
