@@ -77,8 +77,9 @@ int sdfl_groupnorm_forward(const void *in, void *out, const float *gamma, const 
 size_t sdfl_groupnorm_workspace_bytes(int64_t batch, int64_t channels, int64_t hw,
                                       int64_t num_groups, int dtype);
 
-/* Same, with the device path and cluster size (resident) / chunk count (split) forced;
- * 0 = automatic.  A forced path that cannot run the shape returns SDFL_ERR_UNSUPPORTED.
+/* Same, with the device path and cluster size (resident; register: 1, 2, 4 or 8 CTAs per
+ * slab) / chunk count (split) forced; 0 = automatic.  A forced path that cannot run the shape
+ * returns SDFL_ERR_UNSUPPORTED.
  * The workspace must then hold sdfl_groupnorm_workspace_bytes_ex() bytes. */
 int sdfl_groupnorm_forward_ex(const void *in, void *out, const float *gamma, const float *beta,
                               int64_t batch, int64_t channels, int64_t hw, int64_t num_groups,

@@ -702,9 +702,12 @@ bool make_deal(Deal *d, int K, bool sized, int64_t target, bool dynamic, int cta
     d->gangs = ctas / K;
     if (d->gangs > total) d->gangs = static_cast<int>(total);
     if (d->gangs < 1) return false;
-    for (size_t k = 0; k < ts.size(); ++k)
-        if (static_cast<double>(d->gangs) * (K / d->team[k]) * static_cast<double>(slab_bytes[k]) > kMaxInFlightBytes)
-            return false;
+    for (size_t k = 0; k < ts.size(); ++k) {
+        // slabs of this tensor that can be between their two reads at once: no more than it has
+        const int64_t slabs = ts[k].batch * ts[k].groups;
+        const int64_t at_once = std::min<int64_t>(static_cast<int64_t>(d->gangs) * (K / d->team[k]), slabs);
+        if (static_cast<double>(at_once) * static_cast<double>(slab_bytes[k]) > kMaxInFlightBytes) return false;
+    }
     d->cost = dynamic ? deal_cost_dynamic(*d, slab_bytes) : deal_cost(*d, slab_bytes);
     return true;
 }
