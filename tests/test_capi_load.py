@@ -101,6 +101,26 @@ def test_forced_split_count_with_zero_low_bits_is_clamped():
     assert plan[0] == cap.GN_SPLIT and plan[3] == 1
 
 
+def test_register_path_cluster_plan_without_a_device():
+    """At most 64 slabs of 100-512 KB get a cluster of CTAs per slab on the register path; a forced
+    cluster size must be a power of two up to 8."""
+    cap = load_package()._capi
+    lib = cap.lib
+    plan = (C.c_int64 * 8)()
+    for shape, dtype, want in [((2, 640, 4096), 1, 4), ((2, 960, 4096), 1, 4), ((1, 320, 4096), 0, 4),
+                               ((1, 512, 16384), 1, 8), ((2, 320, 4096), 1, 1), ((8, 512, 4096), 1, 1)]:
+        assert lib.sdfl_groupnorm_plan(*shape, 32, dtype, cap.GN_AUTO, 0, plan) == cap.OK
+        assert (plan[0], plan[1], plan[5]) == (cap.GN_REGISTER, want, 0), (shape, list(plan))
+    for forced in (2, 4, 8):
+        assert lib.sdfl_groupnorm_plan(2, 640, 4096, 32, 1, cap.GN_REGISTER, forced, plan) == cap.OK
+        assert plan[1] == forced and plan[6] == 64
+    for forced in (3, 5, 16):
+        assert lib.sdfl_groupnorm_plan(2, 640, 4096, 32, 1, cap.GN_REGISTER, forced, plan) == cap.ERR_UNSUPPORTED
+    # a slab that fits the registers of 8 CTAs but not of one
+    assert lib.sdfl_groupnorm_plan(1, 32, 256 * 256, 32, 0, cap.GN_REGISTER, 0, plan) == cap.ERR_UNSUPPORTED
+    assert lib.sdfl_groupnorm_plan(1, 32, 256 * 256, 32, 0, cap.GN_REGISTER, 8, plan) == cap.OK
+
+
 def test_multi_tensor_call_validates_without_a_device():
     cap = load_package()._capi
     lib = cap.lib
