@@ -117,6 +117,60 @@ def test_multi_fp32_mixed_shapes_and_eps(sdfl):
     assert ops.device_status() == 0
 
 
+@pytest.mark.parametrize("seed", range(12))
+def test_multi_random_lists_and_plans(sdfl, seed):
+    """Seeded random lists of 1-8 tensors (ragged batch / group / channel / pixel counts, both dtypes,
+    with and without SiLU) under random plan knobs (gang size, team rule, static or dynamic order,
+    reversed upper half, chunk size, ring slots): every tensor equals the oracle's result, whatever
+    the deal of slabs to gangs and teams."""
+    ops = sdfl.ops
+    rng = rng_for(9, seed)
+    dtype = "float16" if seed % 2 else "float32"
+    vec = 8 if dtype == "float16" else 4
+    n = int(rng.integers(1, 9))
+    silu = bool(rng.integers(0, 2))
+    xs, gs, bs, groups, epss, wants = [], [], [], [], [], []
+    for k in range(n):
+        G = int(rng.choice([1, 2, 3, 4, 8, 32]))
+        cpg = int(rng.choice([1, 2, 3, 5, 8, 16]))
+        B = int(rng.integers(1, 6))
+        # hw a multiple of the vector, the slab at least 512 bytes (32 vectors); up to ~1 MB slabs
+        hw = vec * int(rng.choice([4, 9, 32, 50, 128, 333, 1024, 4096]))
+        while cpg * hw < 32 * vec:
+            hw *= 2
+        if B * G * cpg * hw > (1 << 21):
+            B = 1
+        shape = (B, G * cpg, hw)
+        x = (rng.standard_normal(shape) * float(rng.uniform(0.5, 3)) + float(rng.uniform(-2, 2))).astype(np.float32)
+        x = x.astype(np.float16) if dtype == "float16" else x
+        g = (1 + 0.2 * rng.standard_normal(shape[1])).astype(np.float32)
+        b = (0.2 * rng.standard_normal(shape[1])).astype(np.float32)
+        eps = float(rng.choice([1e-6, 1e-5, 1e-3]))
+        xs.append(to_dev(x)); gs.append(to_dev(g)); bs.append(to_dev(b)); groups.append(G); epss.append(eps)
+        wants.append(oracle.group_norm(x.astype(np.float32), g, b, G, eps, silu))
+    tol = TOL[dtype]
+    for trial in range(4):
+        K = int(rng.choice([0, 1, 2, 3, 4, 6, 8, 12, 16]))
+        knobs = (K | (int(rng.integers(0, 3)) << 8) | (int(rng.integers(0, 2)) << 11) |
+                 (int(rng.integers(0, 4)) << 12) | (int(rng.integers(0, 3)) << 14) |
+                 (int(rng.choice([0, 16, 32])) << 16) | (int(rng.choice([0, 2, 3, 4])) << 24))
+        if (knobs >> 16) & 0xff in (0, 32) and (knobs >> 24) & 0xf == 4:
+            knobs &= ~(0xf << 24)                # 4 slots of 32 KB: larger than the ring may be
+        outs = [torch.full_like(x, float("nan")) for x in xs]
+        plan = []
+        try:
+            ops.groupnorm_multi(xs, gs, bs, groups, epss, silu, outs=outs, knobs=knobs, plan=plan)
+        except sdfl.SdflError as e:
+            # a forced gang size that no team rule can serve for these slabs is refused, not run
+            assert e.status == sdfl._capi.ERR_UNSUPPORTED and K > 0, (seed, trial, hex(knobs), e)
+            continue
+        for k in range(n):
+            e = worst_error(outs[k], wants[k], tol)
+            assert e <= 1.0, (f"seed {seed} trial {trial} tensor {k} {tuple(xs[k].shape)} G={groups[k]} "
+                              f"knobs {knobs:#x} plan {plan}: {e:.3f} x ({tol})")
+    assert ops.device_status() == 0
+
+
 def test_multi_repeated_launches_share_the_library_scratch(sdfl):
     """Back-to-back launches on one stream through the library's own scratch (workspace NULL) and
     through a caller's zero-filled workspace give the same bits every time."""
