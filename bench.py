@@ -308,6 +308,8 @@ def run_ours(args) -> None:
     # ring of buffer sets so that a buffer is reused only after > 4x L2 of other traffic
     step_bytes = sum(algorithmic_bytes(b_local, C, H) for C, H in SHAPES)
     ring = max(1, -(-4 * L2_BYTES // max(step_bytes, 1)))
+    while K % ring != 0:             # a block of K steps walks the ring a whole number of times
+        ring += 1
     gen = torch.Generator(device=dev).manual_seed(5000 + rank)
     sets = []
     for _ in range(ring):
@@ -339,34 +341,30 @@ def run_ours(args) -> None:
         torch.cuda.synchronize(dev)
 
     def capture(fn):
-        graphs = []
+        """One CUDA graph of a block: K steps back to back, step i on buffer set i mod ring."""
         for s in sets:                      # first calls: attribute set-up, plan cache, workspace
             fn(s)
         stream.synchronize()
-        for s in sets:                      # one CUDA graph per buffer set
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, stream=stream):
-                fn(s)
-            graphs.append(g)
-        return graphs
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            for i in range(K):
+                fn(sets[i % ring])
+        return g
 
-    def timed_blocks(graphs, blocks):
-        """`blocks` blocks of K graph replays each, every block between its own pair of events;
-        returns the per-block device times in ms (this rank)."""
+    def timed_blocks(graph, blocks):
+        """`blocks` replays of the K-step graph, each between its own pair of events; returns the
+        event pairs (this rank)."""
         evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(blocks)]
-        i = 0
         for a, b in evs:
             a.record(stream)
-            for _ in range(K):
-                graphs[i % ring].replay()
-                i += 1
+            graph.replay()
             b.record(stream)
         return evs
 
     with torch.cuda.stream(stream):
         graphs = capture(step)
-        for i in range(W):
-            graphs[i % ring].replay()
+        for _ in range(-(-W // K)):         # at least W untimed steps
+            graphs.replay()
         stream.synchronize()
 
         sampler = ClockSampler(local_rank, period=0.005)
@@ -382,8 +380,8 @@ def run_ours(args) -> None:
         # the other way of launching the step, same buffers, outside the headline region
         other = step_multi if args.chain else step_chain
         other_graphs = capture(other)
-        for i in range(W):
-            other_graphs[i % ring].replay()
+        for _ in range(-(-W // K)):
+            other_graphs.replay()
         barrier()
         other_evs = timed_blocks(other_graphs, min(R, 7))
         barrier()
@@ -412,7 +410,7 @@ def run_ours(args) -> None:
     if rank == 0 and not args.no_parity_check:
         import oracle
         with torch.cuda.stream(stream):
-            graphs[0].replay()
+            graphs.replay()                  # the timed graph once more: its step 0 wrote sets[0]
             stream.synchronize()
         worst = 0.0
         for (C, H), (x, gamma, beta, y) in zip(SHAPES, sets[0]):
@@ -529,10 +527,10 @@ def run_ours(args) -> None:
                        "sharding": f"{BATCH // world if BATCH % world == 0 else 'ragged'} images per GPU, no collective",
                        "l2": f"in+out per step per GPU {step_bytes / 1e6:.0f} MB, ring of {ring} buffer "
                              f"set(s): a buffer is reused after >= {ring * step_bytes / 1e6:.0f} MB of other traffic (L2 126 MB)",
-                       "launch": f"one CUDA graph per step ({launches_per_step} kernel node(s))"},
+                       "launch": f"one CUDA graph per block of {K} steps ({K * launches_per_step} kernel nodes)"},
             "timing": {"blocks": R, "steps_per_block": K,
                        "block_ms": {"min": round(min(block_ms), 4), "median": round(ms_med, 4), "max": round(max(block_ms), 4)},
-                       "how": "every block of K graph replays between its own CUDA events on the launching stream, "
+                       "how": "every block (one replay of the K-step graph) between its own CUDA events on the launching stream, "
                               "max over ranks per block, median over blocks; value and ms_per_step are the median block's"},
             "elements_per_s": round(value * 1e9 / 4, 0),
             "e2e": {"value": round(e2e_value, 2), "unit": UNIT, "steps": e2e_steps,
