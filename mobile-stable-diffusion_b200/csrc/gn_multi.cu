@@ -702,11 +702,25 @@ bool make_deal(Deal *d, int K, bool sized, int64_t target, bool dynamic, int cta
     d->gangs = ctas / K;
     if (d->gangs > total) d->gangs = static_cast<int>(total);
     if (d->gangs < 1) return false;
-    for (size_t k = 0; k < ts.size(); ++k) {
-        // slabs of this tensor that can be between their two reads at once: no more than it has
-        const int64_t slabs = ts[k].batch * ts[k].groups;
-        const int64_t at_once = std::min<int64_t>(static_cast<int64_t>(d->gangs) * (K / d->team[k]), slabs);
-        if (static_cast<double>(at_once) * static_cast<double>(slab_bytes[k]) > kMaxInFlightBytes) return false;
+    {
+        // Bytes between their two reads at once: every gang holds one item; the worst case is the
+        // `gangs` largest items of the list (a tensor contributes no more items than it has).
+        std::vector<std::pair<double, int64_t>> by_size;      // (bytes of one item, number of such items)
+        for (size_t k = 0; k < ts.size(); ++k) {
+            const int64_t slabs = ts[k].batch * ts[k].groups;
+            const int64_t per_item = std::min<int64_t>(K / d->team[k], slabs);
+            by_size.emplace_back(static_cast<double>(per_item) * static_cast<double>(slab_bytes[k]), d->items[k]);
+        }
+        std::sort(by_size.begin(), by_size.end(), [](const auto &x, const auto &y) { return x.first > y.first; });
+        double in_flight = 0;
+        int64_t left = d->gangs;
+        for (const auto &e : by_size) {
+            const int64_t n = std::min(left, e.second);
+            in_flight += e.first * static_cast<double>(n);
+            left -= n;
+            if (left == 0) break;
+        }
+        if (in_flight > kMaxInFlightBytes) return false;
     }
     d->cost = dynamic ? deal_cost_dynamic(*d, slab_bytes) : deal_cost(*d, slab_bytes);
     return true;
