@@ -347,6 +347,7 @@ def test_register_path_one_cta_per_slab(sdfl, shape, G, dtype):
     ((3, 12, 6, 6), 3),        # vectors straddle channels; fewer vectors than CTAs x threads
     ((2, 8, 2, 2), 2),         # one or two vectors per slab: most CTAs of the cluster hold nothing
     ((40, 64, 8, 8), 32),      # more slabs than clusters in a wave
+    ((80, 64, 8, 8), 32),      # 2560 slabs: more than the persistent grid has clusters, so clusters take a second slab
 ])
 def test_register_path_cluster_per_slab(sdfl, shape, G, dtype):
     """A thread-block cluster of 2, 4 or 8 CTAs per slab, each CTA's share in its registers and the
